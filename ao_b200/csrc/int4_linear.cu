@@ -1,0 +1,28 @@
+// Dispatcher of the int4 tensor_core_tiled linear: decode shapes go to the GEMV kernel.
+#include "common.cuh"
+
+extern "C" size_t ao_int4_tinygemm_linear_workspace_bytes(int64_t M, int64_t N, int64_t K, int group,
+                                                          int inner_k_tiles) {
+    return ao_int4_gemv_workspace_bytes(M > 16 ? 16 : M, N, K, group, inner_k_tiles);
+}
+
+extern "C" int ao_int4_tinygemm_linear(const void* x_bf16, int64_t x_row_stride, int64_t x_cols,
+                                       const int32_t* packed, const void* scale_and_zero, int64_t M, int64_t N,
+                                       int64_t K, int group, int inner_k_tiles, void* y_bf16, void* workspace,
+                                       size_t workspace_bytes, ao_stream_t stream) {
+    if (M < 0 || N < 0) return AO_ERR_SHAPE;
+    if (M <= 16)
+        return ao_int4_gemv(x_bf16, x_row_stride, x_cols, packed, scale_and_zero, M, N, K, group, inner_k_tiles, y_bf16,
+                            workspace, workspace_bytes, stream);
+    // row blocks of 16 through the same kernel, back to back on the stream
+    const auto* x = static_cast<const __nv_bfloat16*>(x_bf16);
+    auto* y = static_cast<__nv_bfloat16*>(y_bf16);
+    for (int64_t m0 = 0; m0 < M; m0 += 16) {
+        const int64_t mb = M - m0 < 16 ? M - m0 : 16;
+        // every block uses the 16-row plan's workspace layout only if mb == 16; smaller tails need less
+        int rc = ao_int4_gemv(x + m0 * x_row_stride, x_row_stride, x_cols, packed, scale_and_zero, mb, N, K, group,
+                              inner_k_tiles, y + m0 * N, workspace, workspace_bytes, stream);
+        if (rc) return rc;
+    }
+    return AO_OK;
+}

@@ -1,0 +1,474 @@
+// Affine quantization primitives: choose_qparams_affine / quantize_affine / dequantize_affine.
+//
+// Two families:
+//  * general kernels: any contiguous n-d tensor with any block_size the reference accepts, any
+//    of the supported dtype combinations; arithmetic follows eager PyTorch step by step (compute
+//    in fp32, round to the dtype PyTorch's type promotion gives that step) so results are
+//    bit-identical to torchao/quantization/quant_primitives.py:134-367.
+//  * the int4 weight-only fast path (bf16 weight, groups of 32..256 along K, float zero point):
+//    128-bit loads, sub-warp shuffle min/max, one pass.
+#include "common.cuh"
+
+namespace ao {
+
+struct BlockView {
+    int ndim;
+    int rowblock;  // blocks are contiguous runs of block_elems elements
+    int64_t size[AO_MAX_DIMS], block[AO_MAX_DIMS], nblk[AO_MAX_DIMS], stride[AO_MAX_DIMS];
+    int64_t numel, nblocks, block_elems;
+};
+
+static int make_view(int ndim, const int64_t* sizes, const int64_t* block, BlockView* v) {
+    if (ndim < 1 || ndim > AO_MAX_DIMS) return AO_ERR_SHAPE;
+    v->ndim = ndim;
+    v->numel = 1;
+    v->nblocks = 1;
+    v->block_elems = 1;
+    for (int i = ndim - 1; i >= 0; --i) {
+        if (sizes[i] < 1 || block[i] < 1 || sizes[i] % block[i] != 0) return AO_ERR_SHAPE;
+        v->size[i] = sizes[i];
+        v->block[i] = block[i];
+        v->nblk[i] = sizes[i] / block[i];
+        v->stride[i] = v->numel;
+        v->numel *= sizes[i];
+        v->nblocks *= v->nblk[i];
+        v->block_elems *= block[i];
+    }
+    // contiguous blocks: block == 1 up to some dim j, anything at j, full size after j
+    int j = 0;
+    while (j < ndim && block[j] == 1) ++j;
+    bool rb = true;
+    for (int i = j + 1; i < ndim; ++i) rb = rb && (block[i] == sizes[i]);
+    v->rowblock = rb ? 1 : 0;
+    return AO_OK;
+}
+
+// offset of element e of block b
+__device__ __forceinline__ int64_t element_offset(const BlockView& v, int64_t b, int64_t e) {
+    if (v.rowblock) return b * v.block_elems + e;
+    int64_t off = 0;
+    for (int i = v.ndim - 1; i >= 0; --i) {
+        int64_t bi = b % v.nblk[i];
+        b /= v.nblk[i];
+        int64_t ei = e % v.block[i];
+        e /= v.block[i];
+        off += (bi * v.block[i] + ei) * v.stride[i];
+    }
+    return off;
+}
+
+// block index of the element at linear offset i
+__device__ __forceinline__ int64_t block_of(const BlockView& v, int64_t i) {
+    if (v.rowblock) return i / v.block_elems;
+    int64_t b = 0, mul = 1;
+    for (int d = v.ndim - 1; d >= 0; --d) {
+        int64_t c = i % v.size[d];
+        i /= v.size[d];
+        b += (c / v.block[d]) * mul;
+        mul *= v.nblk[d];
+    }
+    return b;
+}
+
+struct QParamsArgs {
+    int in_dt, mapping, scale_dt, zp_dt, preserve_zero, zp_domain;
+    float qmin, qmax, eps, mid, sym_div, asym_div, sym_zp;
+};
+
+// one warp per block
+__global__ void __launch_bounds__(256) choose_qparams_kernel(const void* __restrict__ x, BlockView v,
+                                                             QParamsArgs a, void* __restrict__ scale_out,
+                                                             void* __restrict__ zp_out) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warps_per_grid = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
+    for (int64_t b = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); b < v.nblocks;
+         b += warps_per_grid) {
+        float mn = INFINITY, mx = -INFINITY;
+        for (int64_t e = lane; e < v.block_elems; e += 32) {
+            float f = load_as_f32(x, a.in_dt, element_offset(v, b, e));
+            mn = fminf(mn, f);
+            mx = fmaxf(mx, f);
+        }
+        mn = warp_min(mn, 32);
+        mx = warp_max(mx, 32);
+        if (lane != 0) continue;
+        float mnn = mn, mxp = mx;
+        if (a.preserve_zero) {
+            mnn = fminf(mn, 0.f);
+            mxp = fmaxf(mx, 0.f);
+        }
+        float scale, zp;
+        if (a.mapping == AO_MAP_SYMMETRIC) {
+            mxp = fmaxf(-mnn, mxp);
+            scale = round_to(a.in_dt, __fdiv_rn(mxp, a.sym_div));
+            zp = round_to(a.in_dt, a.sym_zp);
+        } else {
+            float d = round_to(a.in_dt, __fsub_rn(mxp, mnn));
+            scale = round_to(a.in_dt, __fdiv_rn(d, a.asym_div));
+            if (a.preserve_zero) {
+                float q = rintf(round_to(a.in_dt, __fdiv_rn(mnn, scale)));
+                zp = round_to(a.in_dt, __fsub_rn(a.qmin, q));
+                zp = fminf(fmaxf(zp, a.qmin), a.qmax);
+            } else {
+                float sm = round_to(a.in_dt, __fmul_rn(scale, a.mid));
+                zp = round_to(a.in_dt, __fadd_rn(mnn, sm));
+            }
+        }
+        scale = fmaxf(scale, a.eps);
+        store_from_f32(scale_out, a.scale_dt, b, round_to(a.scale_dt, scale));
+        store_from_f32(zp_out, a.zp_dt, b, is_float_dtype(a.zp_dt) ? round_to(a.zp_dt, zp) : truncf(zp));
+    }
+}
+
+struct QuantArgs {
+    int in_dt, scale_dt, zp_dt, zp_domain, out_dt, has_zp;
+    float qmin, qmax, mid;
+};
+
+__global__ void __launch_bounds__(256) quantize_kernel(const void* __restrict__ x, BlockView v, QuantArgs a,
+                                                       const void* __restrict__ scale,
+                                                       const void* __restrict__ zp, void* __restrict__ out) {
+    const int64_t step = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    const int p1 = promote_dtype(a.in_dt, a.scale_dt);
+    const int p2 = is_float_dtype(a.zp_dt) ? promote_dtype(p1, a.zp_dt) : p1;
+    const int pm = promote_dtype(is_float_dtype(a.zp_dt) ? a.zp_dt : a.scale_dt, a.scale_dt);
+    const int p3 = promote_dtype(a.in_dt, pm);
+    const int p4 = promote_dtype(p3, a.scale_dt);
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < v.numel; i += step) {
+        const int64_t b = block_of(v, i);
+        const float s = load_as_f32(scale, a.scale_dt, b);
+        const float z = load_as_f32(zp, a.zp_dt, b);
+        const float xv = load_as_f32(x, a.in_dt, i);
+        float r;
+        if (a.zp_domain == AO_ZP_INT) {
+            const float inv = round_to(a.scale_dt, __fdiv_rn(1.0f, s));
+            r = rintf(round_to(p1, __fmul_rn(xv, inv)));
+            r = round_to(p2, __fadd_rn(r, z));
+        } else {
+            const float sm = round_to(a.scale_dt, __fmul_rn(s, a.mid));
+            const float minv = round_to(pm, __fsub_rn(z, sm));
+            r = round_to(p3, __fsub_rn(xv, minv));
+            r = rintf(round_to(p4, __fdiv_rn(r, s)));
+        }
+        r = fminf(fmaxf(r, a.qmin), a.qmax);
+        store_from_f32(out, a.out_dt, i, r);
+    }
+}
+
+__global__ void __launch_bounds__(256) dequantize_kernel(const void* __restrict__ q, int q_dt, BlockView v,
+                                                         QuantArgs a, const void* __restrict__ scale,
+                                                         const void* __restrict__ zp, void* __restrict__ out) {
+    const int64_t step = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < v.numel; i += step) {
+        const int64_t b = block_of(v, i);
+        const float s = load_as_f32(scale, a.scale_dt, b);
+        const int32_t qi = load_as_i32(q, q_dt, i);
+        float r;
+        if (a.zp_domain == AO_ZP_INT) {
+            const int32_t zi = a.has_zp ? load_as_i32(zp, a.zp_dt, b) : 0;
+            r = round_to(a.out_dt, static_cast<float>(qi - zi));
+            r = round_to(a.out_dt, __fmul_rn(r, s));
+        } else {
+            r = round_to(a.out_dt, __fsub_rn(static_cast<float>(qi), a.mid));
+            r = round_to(a.out_dt, __fmul_rn(r, s));
+            if (a.has_zp) r = round_to(a.out_dt, __fadd_rn(r, load_as_f32(zp, a.zp_dt, b)));
+        }
+        store_from_f32(out, a.out_dt, i, r);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// int4 weight-only fast path
+// ---------------------------------------------------------------------------------------------
+struct Int4Params {
+    float s, zp, minv;
+};
+
+// the int4_weight_only parameter set: asymmetric, qmin 0, qmax 15, mid 8, eps 1e-6 (as bf16),
+// zero point in the float domain, everything bf16
+__device__ __forceinline__ Int4Params int4_qparams_bf16(float mn, float mx) {
+    Int4Params p;
+    const float d = round_bf16(__fsub_rn(mx, mn));
+    const float s0 = round_bf16(__fdiv_rn(d, 15.0f));
+    p.zp = round_bf16(__fadd_rn(mn, round_bf16(__fmul_rn(s0, 8.0f))));  // uses the unclamped scale
+    p.s = fmaxf(s0, __uint_as_float(0x35860000u));                      // bf16(1e-6)
+    p.minv = round_bf16(__fsub_rn(p.zp, round_bf16(__fmul_rn(p.s, 8.0f))));
+    return p;
+}
+
+__device__ __forceinline__ int int4_code_bf16(float x, const Int4Params& p) {
+    float r = round_bf16(__fsub_rn(x, p.minv));
+    r = rintf(round_bf16(__fdiv_rn(r, p.s)));
+    return static_cast<int>(fminf(fmaxf(r, 0.f), 15.f));
+}
+
+__device__ __forceinline__ void unpack8_bf16(const uint4& v, float (&f)[8]) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        f[2 * i] = __uint_as_float(w[i] << 16);
+        f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+}
+
+// G/8 lanes share a group; each lane owns 8 consecutive elements (one 128-bit load).
+template <int G>
+__global__ void __launch_bounds__(256) int4_groupwise_quantize_kernel(const uint4* __restrict__ w, int64_t n_vec,
+                                                                      __nv_bfloat16* __restrict__ scale_out,
+                                                                      __nv_bfloat16* __restrict__ zero_out,
+                                                                      int32_t* __restrict__ codes_i32,
+                                                                      uint8_t* __restrict__ codes_u8) {
+    constexpr int L = G / 8;  // lanes per group: 4, 8, 16, 32
+    const int64_t step = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    // n_vec is a multiple of L and blockDim a multiple of 32, so whole sub-warps stay together
+    const int64_t n_round = (n_vec + 31) / 32 * 32;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n_round; i += step) {
+        const bool live = i < n_vec;
+        float f[8];
+        if (live) {
+            unpack8_bf16(__ldg(w + i), f);
+        } else {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) f[k] = 0.f;
+        }
+        float mn = f[0], mx = f[0];
+#pragma unroll
+        for (int k = 1; k < 8; ++k) {
+            mn = fminf(mn, f[k]);
+            mx = fmaxf(mx, f[k]);
+        }
+        mn = warp_min(mn, L);
+        mx = warp_max(mx, L);
+        if (!live) continue;
+        const Int4Params p = int4_qparams_bf16(mn, mx);
+        if ((i % L) == 0) {
+            if (scale_out) scale_out[i / L] = __float2bfloat16_rn(p.s);
+            if (zero_out) zero_out[i / L] = __float2bfloat16_rn(p.zp);
+        }
+        int c[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) c[k] = int4_code_bf16(f[k], p);
+        if (codes_i32) {
+            int4* o = reinterpret_cast<int4*>(codes_i32) + 2 * i;
+            o[0] = make_int4(c[0], c[1], c[2], c[3]);
+            o[1] = make_int4(c[4], c[5], c[6], c[7]);
+        }
+        if (codes_u8) {
+            uint2 o;
+            o.x = c[0] | (c[1] << 8) | (c[2] << 16) | (c[3] << 24);
+            o.y = c[4] | (c[5] << 8) | (c[6] << 16) | (c[7] << 24);
+            reinterpret_cast<uint2*>(codes_u8)[i] = o;
+        }
+    }
+}
+
+// Fused W -> tensor_core_tiled packed weight + interleaved scale/zero.  One CTA owns one tile of
+// 8 rows x kChunk columns: codes go to shared memory, then every thread assembles packed words.
+constexpr int kPackChunk = 1024;
+
+template <int G>
+__global__ void __launch_bounds__(256) int4_quantize_pack_kernel(const __nv_bfloat16* __restrict__ w, int64_t N,
+                                                                 int64_t K, int ikt, int32_t* __restrict__ packed,
+                                                                 __nv_bfloat16* __restrict__ scale_and_zero) {
+    constexpr int L = G / 8;
+    __shared__ uint8_t codes[8][kPackChunk + 16];
+    const int64_t nt = blockIdx.y;
+    const int64_t k0 = static_cast<int64_t>(blockIdx.x) * kPackChunk;
+    const int chunk = static_cast<int>(min(static_cast<int64_t>(kPackChunk), K - k0));  // multiple of 16*ikt and G
+    const int vec_per_row = chunk / 8;
+    const int n_vec = 8 * vec_per_row;  // multiple of 32 because chunk is a multiple of 32
+    for (int i = threadIdx.x; i < n_vec; i += blockDim.x) {
+        const int row = i / vec_per_row, col = (i % vec_per_row) * 8;
+        const int64_t n = nt * 8 + row;
+        float f[8];
+        unpack8_bf16(__ldg(reinterpret_cast<const uint4*>(w + n * K + k0 + col)), f);
+        float mn = f[0], mx = f[0];
+#pragma unroll
+        for (int k = 1; k < 8; ++k) {
+            mn = fminf(mn, f[k]);
+            mx = fmaxf(mx, f[k]);
+        }
+        mn = warp_min(mn, L);
+        mx = warp_max(mx, L);
+        const Int4Params p = int4_qparams_bf16(mn, mx);
+        if ((i % L) == 0) {
+            const int64_t g = (k0 + col) / G;
+            __nv_bfloat162 sz;
+            sz.x = __float2bfloat16_rn(p.s);
+            sz.y = __float2bfloat16_rn(p.zp);
+            reinterpret_cast<__nv_bfloat162*>(scale_and_zero)[g * N + n] = sz;
+        }
+        uint32_t lo = 0, hi = 0;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            lo |= static_cast<uint32_t>(int4_code_bf16(f[k], p)) << (8 * k);
+            hi |= static_cast<uint32_t>(int4_code_bf16(f[k + 4], p)) << (8 * k);
+        }
+        *reinterpret_cast<uint2*>(&codes[row][col]) = make_uint2(lo, hi);
+    }
+    __syncthreads();
+    // packed words of this tile: [ko_local][lane][ikt/2]
+    const int half = ikt / 2;
+    const int outer = chunk / (ikt * 16);
+    const int n_words = outer * 32 * half;
+    const int64_t KO = K / (ikt * 16);
+    const int64_t ko0 = k0 / (ikt * 16);
+    int32_t* dst = packed + ((nt * KO + ko0) * 32) * half;
+    for (int wi = threadIdx.x; wi < n_words; wi += blockDim.x) {
+        const int j = wi % half, t = (wi / half) % 32, ko = wi / (half * 32);
+        const int row = t >> 2, c = t & 3;
+        const int kA = (ko * ikt + 2 * j) * 16 + 2 * c, kB = kA + 16;
+        const uint8_t* r = codes[row];
+        const uint32_t word = r[kA] | (r[kA + 8] << 4) | (r[kB] << 8) | (r[kB + 8] << 12) | (r[kA + 1] << 16) |
+                              (r[kA + 9] << 20) | (r[kB + 1] << 24) | (static_cast<uint32_t>(r[kB + 9]) << 28);
+        dst[wi] = static_cast<int32_t>(word);
+    }
+}
+
+static int grid_for(int64_t work_items, int threads) {
+    int64_t g = (work_items + threads - 1) / threads;
+    const int64_t cap = static_cast<int64_t>(kNumSMs) * 16;
+    if (g > cap) g = cap;
+    if (g < 1) g = 1;
+    return static_cast<int>(g);
+}
+
+}  // namespace ao
+
+using namespace ao;
+
+extern "C" int ao_choose_qparams_affine(const void* input, int input_dtype, int ndim, const int64_t* sizes,
+                                        const int64_t* block_size, int mapping_type, int64_t quant_min,
+                                        int64_t quant_max, int has_eps, double eps, int scale_dtype,
+                                        int zero_point_dtype, int preserve_zero, int zero_point_domain,
+                                        void* scale_out, void* zero_point_out, ao_stream_t stream) {
+    if (!is_float_dtype(input_dtype) || !is_float_dtype(scale_dtype)) return AO_ERR_DTYPE;
+    if (zero_point_dtype < AO_F32 || zero_point_dtype > AO_I16) return AO_ERR_DTYPE;
+    if (mapping_type != AO_MAP_SYMMETRIC && mapping_type != AO_MAP_ASYMMETRIC) return AO_ERR_ARG;
+    if (mapping_type == AO_MAP_SYMMETRIC && (!preserve_zero || zero_point_domain != AO_ZP_INT)) return AO_ERR_ARG;
+    if (mapping_type == AO_MAP_ASYMMETRIC && !preserve_zero && zero_point_domain != AO_ZP_FLOAT) return AO_ERR_ARG;
+    BlockView v;
+    int rc = make_view(ndim, sizes, block_size, &v);
+    if (rc) return rc;
+    QParamsArgs a;
+    a.in_dt = input_dtype;
+    a.mapping = mapping_type;
+    a.scale_dt = scale_dtype;
+    a.zp_dt = zero_point_dtype;
+    a.preserve_zero = preserve_zero;
+    a.zp_domain = zero_point_domain;
+    a.qmin = static_cast<float>(quant_min);
+    a.qmax = static_cast<float>(quant_max);
+    float e = has_eps ? static_cast<float>(eps)
+                      : (input_dtype == AO_BF16 ? 0.0078125f : input_dtype == AO_F16 ? 0.0009765625f : 1.1920928955078125e-07f);
+    // clamp(min=eps) compares in the tensor's dtype
+    if (input_dtype == AO_BF16) e = __bfloat162float(__float2bfloat16_rn(e));
+    if (input_dtype == AO_F16) e = __half2float(__float2half_rn(e));
+    a.eps = e;
+    a.mid = static_cast<float>(static_cast<double>(quant_max + quant_min + 1) / 2.0);
+    a.sym_div = static_cast<float>(static_cast<double>(quant_max - quant_min) / 2.0);
+    a.asym_div = static_cast<float>(quant_max - quant_min);
+    a.sym_zp = static_cast<float>(static_cast<int64_t>(static_cast<double>(quant_max + quant_min + 1) / 2.0));
+    const int grid = grid_for(v.nblocks * 32, 256);
+    choose_qparams_kernel<<<grid, 256, 0, as_stream(stream)>>>(input, v, a, scale_out, zero_point_out);
+    return launch_status();
+}
+
+static int fill_quant_args(QuantArgs* a, int in_dt, int scale_dt, int zp_dt, int zp_domain, int out_dt,
+                           const void* zp, int64_t qmin, int64_t qmax) {
+    if (!is_float_dtype(scale_dt)) return AO_ERR_DTYPE;
+    if (zp_domain != AO_ZP_INT && zp_domain != AO_ZP_FLOAT) return AO_ERR_ARG;
+    a->in_dt = in_dt;
+    a->scale_dt = scale_dt;
+    a->zp_dt = zp_dt;
+    a->zp_domain = zp_domain;
+    a->out_dt = out_dt;
+    a->has_zp = zp != nullptr;
+    a->qmin = static_cast<float>(qmin);
+    a->qmax = static_cast<float>(qmax);
+    a->mid = static_cast<float>(static_cast<double>(qmax + qmin + 1) / 2.0);
+    return AO_OK;
+}
+
+extern "C" int ao_quantize_affine(const void* input, int input_dtype, int ndim, const int64_t* sizes,
+                                  const int64_t* block_size, const void* scale, int scale_dtype,
+                                  const void* zero_point, int zero_point_dtype, int64_t quant_min,
+                                  int64_t quant_max, int zero_point_domain, void* out, int out_dtype,
+                                  ao_stream_t stream) {
+    if (!is_float_dtype(input_dtype)) return AO_ERR_DTYPE;
+    if (is_float_dtype(out_dtype) || out_dtype > AO_I16) return AO_ERR_DTYPE;
+    if (zero_point == nullptr) return AO_ERR_ARG;
+    BlockView v;
+    int rc = make_view(ndim, sizes, block_size, &v);
+    if (rc) return rc;
+    QuantArgs a;
+    rc = fill_quant_args(&a, input_dtype, scale_dtype, zero_point_dtype, zero_point_domain, out_dtype, zero_point,
+                         quant_min, quant_max);
+    if (rc) return rc;
+    quantize_kernel<<<grid_for(v.numel, 256), 256, 0, as_stream(stream)>>>(input, v, a, scale, zero_point, out);
+    return launch_status();
+}
+
+extern "C" int ao_dequantize_affine(const void* input, int input_dtype, int ndim, const int64_t* sizes,
+                                    const int64_t* block_size, const void* scale, int scale_dtype,
+                                    const void* zero_point, int zero_point_dtype, int64_t quant_min,
+                                    int64_t quant_max, int zero_point_domain, void* out, int out_dtype,
+                                    ao_stream_t stream) {
+    if (is_float_dtype(input_dtype) || input_dtype > AO_I16) return AO_ERR_DTYPE;
+    if (!is_float_dtype(out_dtype)) return AO_ERR_DTYPE;
+    BlockView v;
+    int rc = make_view(ndim, sizes, block_size, &v);
+    if (rc) return rc;
+    QuantArgs a;
+    rc = fill_quant_args(&a, AO_F32, scale_dtype, zero_point_dtype, zero_point_domain, out_dtype, zero_point,
+                         quant_min, quant_max);
+    if (rc) return rc;
+    dequantize_kernel<<<grid_for(v.numel, 256), 256, 0, as_stream(stream)>>>(input, input_dtype, v, a, scale,
+                                                                               zero_point, out);
+    return launch_status();
+}
+
+extern "C" int ao_int4_groupwise_quantize(const void* w_bf16, int64_t N, int64_t K, int group, void* scale_out,
+                                          void* zero_out, int32_t* codes_i32_out, uint8_t* codes_u8_out,
+                                          ao_stream_t stream) {
+    if (N < 1 || K < 1 || K % group != 0) return AO_ERR_SHAPE;
+    if (!aligned(w_bf16, 16) || (codes_i32_out && !aligned(codes_i32_out, 16)) ||
+        (codes_u8_out && !aligned(codes_u8_out, 8)))
+        return AO_ERR_ALIGN;
+    const int64_t n_vec = N * K / 8;
+    const int grid = grid_for(n_vec, 256);
+    auto* s = static_cast<__nv_bfloat16*>(scale_out);
+    auto* z = static_cast<__nv_bfloat16*>(zero_out);
+    const uint4* w = static_cast<const uint4*>(w_bf16);
+    cudaStream_t st = as_stream(stream);
+    switch (group) {
+        case 32: int4_groupwise_quantize_kernel<32><<<grid, 256, 0, st>>>(w, n_vec, s, z, codes_i32_out, codes_u8_out); break;
+        case 64: int4_groupwise_quantize_kernel<64><<<grid, 256, 0, st>>>(w, n_vec, s, z, codes_i32_out, codes_u8_out); break;
+        case 128: int4_groupwise_quantize_kernel<128><<<grid, 256, 0, st>>>(w, n_vec, s, z, codes_i32_out, codes_u8_out); break;
+        case 256: int4_groupwise_quantize_kernel<256><<<grid, 256, 0, st>>>(w, n_vec, s, z, codes_i32_out, codes_u8_out); break;
+        default: return AO_ERR_UNSUPPORTED;
+    }
+    return launch_status();
+}
+
+extern "C" int ao_int4_quantize_pack_tinygemm(const void* w_bf16, int64_t N, int64_t K, int group, int inner_k_tiles,
+                                              int32_t* packed_out, void* scale_and_zero_out, ao_stream_t stream) {
+    if (!(inner_k_tiles == 2 || inner_k_tiles == 4 || inner_k_tiles == 8)) return AO_ERR_ARG;
+    if (N < 8 || N % 8 != 0 || K < 1 || K % group != 0 || K % (inner_k_tiles * 16) != 0 || K % 32 != 0)
+        return AO_ERR_SHAPE;
+    if (kPackChunk % group != 0) return AO_ERR_UNSUPPORTED;
+    if (!aligned(w_bf16, 16) || !aligned(scale_and_zero_out, 4) || !aligned(packed_out, 4)) return AO_ERR_ALIGN;
+    if (N / 8 > 65535) return AO_ERR_SHAPE;
+    dim3 grid(static_cast<unsigned>((K + kPackChunk - 1) / kPackChunk), static_cast<unsigned>(N / 8));
+    const auto* w = static_cast<const __nv_bfloat16*>(w_bf16);
+    auto* sz = static_cast<__nv_bfloat16*>(scale_and_zero_out);
+    cudaStream_t st = as_stream(stream);
+    switch (group) {
+        case 32: int4_quantize_pack_kernel<32><<<grid, 256, 0, st>>>(w, N, K, inner_k_tiles, packed_out, sz); break;
+        case 64: int4_quantize_pack_kernel<64><<<grid, 256, 0, st>>>(w, N, K, inner_k_tiles, packed_out, sz); break;
+        case 128: int4_quantize_pack_kernel<128><<<grid, 256, 0, st>>>(w, N, K, inner_k_tiles, packed_out, sz); break;
+        case 256: int4_quantize_pack_kernel<256><<<grid, 256, 0, st>>>(w, N, K, inner_k_tiles, packed_out, sz); break;
+        default: return AO_ERR_UNSUPPORTED;
+    }
+    return launch_status();
+}

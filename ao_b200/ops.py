@@ -1,0 +1,138 @@
+"""Operator layer: thin wrappers that allocate outputs with torch and call the C ABI.
+
+Covers the operators the reference reaches through the PyTorch dispatcher on this path:
+  * aten::_convert_weight_to_int4pack / aten::_weight_int4pack_mm (PyTorch's tinygemm ops, called at
+    torchao/dtypes/affine_quantized_tensor.py:461, 631) -> convert_weight_to_int4pack, weight_int4pack_mm
+  * torchao::quant_llm_linear (torchao/ops.py:15-55) -> quant_llm_linear / fp6_llm_linear
+  * the fp6 pre-packer (torchao/prototype/quant_llm/quant_llm.py:90-130) -> prepack_fp6_weight
+CUDA tensors only; errors surface as exceptions, never as a silent dense fallback.
+"""
+import torch
+from torch import Tensor
+
+from . import _cabi
+
+
+def _stream(t):
+    return _cabi.stream_ptr(t.device)
+
+
+# ---------------------------------------------------------------------------------------------
+# int4 tensor_core_tiled ("tinygemm") operators
+# ---------------------------------------------------------------------------------------------
+def convert_weight_to_int4pack(int_data: Tensor, inner_k_tiles: int = 8) -> Tensor:
+    """int32 codes [N][K] (values 0..15) -> int32 [N/8][K/(inner_k_tiles*16)][32][inner_k_tiles/2]."""
+    _cabi.require_cuda(int_data)
+    torch._check(int_data.dim() == 2, lambda: "int_data must be 2-D [n][k]")
+    torch._check(inner_k_tiles in (2, 4, 8), lambda: "innerKTiles must be 2, 4, or 8")
+    codes = int_data.to(torch.int32).contiguous()
+    N, K = codes.shape
+    torch._check(N % 8 == 0, lambda: f"expect N to be a multiple of 8, got {N}")
+    torch._check(K % (inner_k_tiles * 16) == 0, lambda: f"expect K to be a multiple of {inner_k_tiles * 16}, got {K}")
+    out = torch.empty((N // 8, K // (inner_k_tiles * 16), 32, inner_k_tiles // 2), dtype=torch.int32,
+                      device=codes.device)
+    with torch.cuda.device(codes.device):
+        rc = _cabi.lib().ao_pack_tinygemm_int4(_cabi.ptr(codes), N, K, inner_k_tiles, _cabi.ptr(out), _stream(codes))
+    _cabi.check(rc, "convert_weight_to_int4pack")
+    return out
+
+
+def unpack_int4pack(packed: Tensor) -> Tensor:
+    """Inverse of convert_weight_to_int4pack: int32 codes [N][K]."""
+    _cabi.require_cuda(packed)
+    torch._check(packed.dim() == 4 and packed.shape[2] == 32 and packed.dtype == torch.int32,
+                 lambda: "expected an int32 [N/8][K/(ikt*16)][32][ikt/2] tensor")
+    packed = packed.contiguous()
+    ikt = packed.shape[3] * 2
+    N, K = packed.shape[0] * 8, packed.shape[1] * ikt * 16
+    out = torch.empty((N, K), dtype=torch.int32, device=packed.device)
+    with torch.cuda.device(packed.device):
+        rc = _cabi.lib().ao_unpack_tinygemm_int4(_cabi.ptr(packed), N, K, ikt, _cabi.ptr(out), _stream(packed))
+    _cabi.check(rc, "unpack_int4pack")
+    return out
+
+
+def weight_int4pack_mm(x: Tensor, packed: Tensor, group_size: int, scale_and_zero: Tensor, x_cols=None) -> Tensor:
+    """y[M][N] = x[M][K] @ dequant(W)^T for a tensor_core_tiled weight; bf16 in, bf16 out.
+
+    x may have fewer columns than the (padded) weight: the missing ones count as zero."""
+    _cabi.require_cuda(x, packed, scale_and_zero)
+    torch._check(x.dim() == 2 and x.dtype == torch.bfloat16, lambda: "x must be a 2-D bfloat16 tensor")
+    torch._check(packed.dim() == 4 and packed.dtype == torch.int32 and packed.shape[2] == 32,
+                 lambda: "packed weight must be int32 [N/8][K/(ikt*16)][32][ikt/2]")
+    torch._check(scale_and_zero.dim() == 3 and scale_and_zero.shape[2] == 2 and scale_and_zero.dtype == torch.bfloat16,
+                 lambda: "scale_and_zero must be bfloat16 [K/group][N][2]")
+    ikt = packed.shape[3] * 2
+    N, K = packed.shape[0] * 8, packed.shape[1] * ikt * 16
+    M = x.shape[0]
+    torch._check(x.shape[1] <= K, lambda: f"x has {x.shape[1]} columns, the weight only {K}")
+    torch._check(scale_and_zero.shape[0] == K // group_size and scale_and_zero.shape[1] == N,
+                 lambda: f"scale_and_zero shape {tuple(scale_and_zero.shape)} does not match K/group={K // group_size}, N={N}")
+    if x.stride(1) != 1 or x.stride(0) % 2 != 0 or x.data_ptr() % 4 != 0 or x.shape[1] % 2 != 0:
+        x = torch.nn.functional.pad(x, (0, x.shape[1] % 2)).contiguous()
+    packed = packed.contiguous()
+    scale_and_zero = scale_and_zero.contiguous()
+    y = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    if M == 0:
+        return y
+    lib = _cabi.lib()
+    nbytes = lib.ao_int4_tinygemm_linear_workspace_bytes(M, N, K, group_size, ikt)
+    torch._check(nbytes > 0, lambda: f"unsupported int4 linear shape M={M} N={N} K={K} group={group_size}")
+    with torch.cuda.device(x.device):
+        ws = _cabi.workspace(nbytes, x.device)
+        rc = lib.ao_int4_tinygemm_linear(_cabi.ptr(x), x.stride(0), x.shape[1], _cabi.ptr(packed),
+                                         _cabi.ptr(scale_and_zero), M, N, K, group_size, ikt, _cabi.ptr(y),
+                                         _cabi.ptr(ws), ws.numel(), _stream(x))
+    _cabi.check(rc, "weight_int4pack_mm")
+    return y
+
+
+def int4_quantize_pack(weight: Tensor, group_size: int, inner_k_tiles: int = 8):
+    """bf16 W [N][K] -> (tensor_core_tiled int32 weight, scale_and_zero bf16 [K/g][N][2]) in one pass."""
+    _cabi.require_cuda(weight)
+    torch._check(weight.dim() == 2 and weight.dtype == torch.bfloat16, lambda: "weight must be 2-D bfloat16")
+    w = weight.contiguous()
+    N, K = w.shape
+    packed = torch.empty((N // 8, K // (inner_k_tiles * 16), 32, inner_k_tiles // 2), dtype=torch.int32, device=w.device)
+    sz = torch.empty((K // group_size, N, 2), dtype=torch.bfloat16, device=w.device)
+    with torch.cuda.device(w.device):
+        rc = _cabi.lib().ao_int4_quantize_pack_tinygemm(_cabi.ptr(w), N, K, group_size, inner_k_tiles, _cabi.ptr(packed),
+                                                        _cabi.ptr(sz), _stream(w))
+    _cabi.check(rc, "int4_quantize_pack")
+    return packed, sz
+
+
+def int4_groupwise_quantize(weight: Tensor, group_size: int, want_codes=torch.int32):
+    """bf16 W [N][K] -> (scale bf16 [N][K/g], zero bf16 [N][K/g], codes [N][K] int32 or uint8)."""
+    _cabi.require_cuda(weight)
+    torch._check(weight.dim() == 2 and weight.dtype == torch.bfloat16, lambda: "weight must be 2-D bfloat16")
+    w = weight.contiguous()
+    N, K = w.shape
+    scale = torch.empty((N, K // group_size), dtype=torch.bfloat16, device=w.device)
+    zero = torch.empty_like(scale)
+    codes = torch.empty((N, K), dtype=want_codes, device=w.device)
+    i32 = _cabi.ptr(codes) if want_codes == torch.int32 else None
+    u8 = _cabi.ptr(codes) if want_codes == torch.uint8 else None
+    with torch.cuda.device(w.device):
+        rc = _cabi.lib().ao_int4_groupwise_quantize(_cabi.ptr(w), N, K, group_size, _cabi.ptr(scale), _cabi.ptr(zero),
+                                                    i32, u8, _stream(w))
+    _cabi.check(rc, "int4_groupwise_quantize")
+    return scale, zero, codes
+
+
+# ---------------------------------------------------------------------------------------------
+# fp6 (e3m2) operators
+# ---------------------------------------------------------------------------------------------
+def prepack_fp6_weight(codes: Tensor) -> Tensor:
+    """One e3m2 code per byte, uint8 [N][K] -> tensor-core pre-packed uint8 [N][K*6/8]
+    (pack_tc_fpx(codes, 6), torchao/prototype/quant_llm/quant_llm.py:90-113)."""
+    _cabi.require_cuda(codes)
+    assert codes.ndim == 2 and codes.dtype == torch.uint8
+    M, N = codes.shape
+    assert (M % 64 == 0) and (N % 64 == 0)
+    codes = codes.contiguous()
+    out = torch.empty((M, N * 6 // 8), dtype=torch.uint8, device=codes.device)
+    with torch.cuda.device(codes.device):
+        rc = _cabi.lib().ao_pack_tc_fp6(_cabi.ptr(codes), M, N, _cabi.ptr(out), _stream(codes))
+    _cabi.check(rc, "prepack_fp6_weight")
+    return out

@@ -1,0 +1,189 @@
+/*
+ * ao_b200 — C ABI of the B200 (sm_100a) weight-only quantized-linear path.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream, enqueues
+ * its kernels on that stream and returns a status code.  Nothing here allocates,
+ * synchronises or throws; the caller owns every buffer, including workspaces whose
+ * size comes from the matching *_workspace_bytes query.  Calls are thread-safe as
+ * long as concurrent calls use distinct output / workspace buffers.
+ *
+ * Each declaration cites the reference (torchao 0.3.1) interface it stands in for,
+ * by the file's path inside the reference project.
+ */
+#ifndef AO_B200_H
+#define AO_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* CUDA stream handle (cudaStream_t) passed as an opaque pointer. */
+typedef void* ao_stream_t;
+
+/* status codes */
+enum {
+    AO_OK = 0,
+    AO_ERR_SHAPE = 1,       /* a size / divisibility requirement is not met          */
+    AO_ERR_ALIGN = 2,       /* a pointer is not aligned as the kernel requires        */
+    AO_ERR_DTYPE = 3,       /* unsupported dtype code or dtype combination            */
+    AO_ERR_LAUNCH = 4,      /* the CUDA runtime rejected a launch (see cudaGetLastError) */
+    AO_ERR_TIMEOUT = 5,     /* a bounded device-side wait ran out                     */
+    AO_ERR_UNSUPPORTED = 6, /* valid request that this build has no kernel for        */
+    AO_ERR_WORKSPACE = 7,   /* workspace missing or too small                         */
+    AO_ERR_ARG = 8          /* an argument the reference would reject (ValueError)    */
+};
+
+/* dtype codes */
+enum { AO_F32 = 0, AO_F16 = 1, AO_BF16 = 2, AO_I32 = 3, AO_I64 = 4, AO_I8 = 5, AO_U8 = 6, AO_I16 = 7 };
+
+/* MappingType / ZeroPointDomain (torchao/quantization/quant_primitives.py:24-47) */
+enum { AO_MAP_SYMMETRIC = 0, AO_MAP_ASYMMETRIC = 1 };
+enum { AO_ZP_INT = 0, AO_ZP_FLOAT = 1 };
+
+#define AO_MAX_DIMS 8
+
+const char* ao_status_string(int status);
+int ao_abi_version(void);
+
+/* ------------------------------------------------------------------------------------------
+ * Affine quantization primitives.  Tensors are contiguous, described by `ndim` sizes and a
+ * block_size of the same rank (block[i] divides sizes[i]); scale / zero_point hold one value
+ * per block in the row-major order of (sizes[i] / block[i]).
+ * ---------------------------------------------------------------------------------------- */
+
+/* choose_qparams_affine — torchao/quantization/quant_primitives.py:278-367.
+ * Returns AO_ERR_ARG for the combinations the reference raises on (symmetric without
+ * preserve_zero, symmetric with a FLOAT zero point, asymmetric non-preserving INT domain). */
+int ao_choose_qparams_affine(const void* input, int input_dtype, int ndim, const int64_t* sizes,
+                             const int64_t* block_size, int mapping_type, int64_t quant_min,
+                             int64_t quant_max, int has_eps, double eps, int scale_dtype,
+                             int zero_point_dtype, int preserve_zero, int zero_point_domain,
+                             void* scale_out, void* zero_point_out, ao_stream_t stream);
+
+/* quantize_affine — torchao/quantization/quant_primitives.py:134-206. */
+int ao_quantize_affine(const void* input, int input_dtype, int ndim, const int64_t* sizes,
+                       const int64_t* block_size, const void* scale, int scale_dtype,
+                       const void* zero_point, int zero_point_dtype, int64_t quant_min,
+                       int64_t quant_max, int zero_point_domain, void* out, int out_dtype,
+                       ao_stream_t stream);
+
+/* dequantize_affine — torchao/quantization/quant_primitives.py:208-276.
+ * zero_point may be NULL. */
+int ao_dequantize_affine(const void* input, int input_dtype, int ndim, const int64_t* sizes,
+                         const int64_t* block_size, const void* scale, int scale_dtype,
+                         const void* zero_point, int zero_point_dtype, int64_t quant_min,
+                         int64_t quant_max, int zero_point_domain, void* out, int out_dtype,
+                         ao_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
+ * int4 weight-only fast path (asymmetric uint4, groups of `group` along K, bf16 scale and
+ * float zero point) — what int4_weight_only() configures,
+ * torchao/quantization/quant_api.py:362-387 and
+ * AffineQuantizedTensor.from_float, torchao/dtypes/affine_quantized_tensor.py:184-229.
+ * ---------------------------------------------------------------------------------------- */
+
+/* One pass over W bf16 [N][K]: per-group scale / zero (bf16 [N][K/group]) and codes.
+ * Any of scale_out, zero_out, codes_i32_out (int32 [N][K]), codes_u8_out (uint8 [N][K]) may be
+ * NULL.  group in {32, 64, 128, 256}, K % group == 0, W 16-byte aligned.
+ * Replaces choose_qparams_affine + quantize_affine as called at
+ * affine_quantized_tensor.py:212-213 with the int4_weight_only parameter set. */
+int ao_int4_groupwise_quantize(const void* w_bf16, int64_t N, int64_t K, int group, void* scale_out,
+                               void* zero_out, int32_t* codes_i32_out, uint8_t* codes_u8_out,
+                               ao_stream_t stream);
+
+/* W bf16 [N][K] -> tensor_core_tiled weight int32 [N/8][K/(ikt*16)][32][ikt/2] and
+ * scale_and_zero bf16 [K/group][N][2] in one pass (no int32 codes are materialised).
+ * N % 8 == 0, K % (ikt*16) == 0, K % group == 0, group in {32,64,128,256}.
+ * Replaces from_float + TensorCoreTiledAQTLayout.from_plain,
+ * affine_quantized_tensor.py:212-213, 460-465. */
+int ao_int4_quantize_pack_tinygemm(const void* w_bf16, int64_t N, int64_t K, int group,
+                                   int inner_k_tiles, int32_t* packed_out, void* scale_and_zero_out,
+                                   ao_stream_t stream);
+
+/* aten::_convert_weight_to_int4pack as the reference calls it (int32 codes [N][K]),
+ * affine_quantized_tensor.py:461.  out: int32 [N/8][K/(ikt*16)][32][ikt/2]. */
+int ao_pack_tinygemm_int4(const int32_t* codes, int64_t N, int64_t K, int inner_k_tiles,
+                          int32_t* packed_out, ao_stream_t stream);
+
+/* Inverse of the above: what TensorCoreTiledAQTLayout.get_plain needs,
+ * affine_quantized_tensor.py:509-537. */
+int ao_unpack_tinygemm_int4(const int32_t* packed, int64_t N, int64_t K, int inner_k_tiles,
+                            int32_t* codes_out, ao_stream_t stream);
+
+/* pack_tinygemm_scales_and_zeros / unpack — torchao/quantization/utils.py:310-328.
+ * scale, zero: bf16 [N][G]; scale_and_zero: bf16 [G][N][2]. */
+int ao_pack_tinygemm_scales_and_zeros(const void* scale, const void* zero, int64_t N, int64_t G,
+                                      void* scale_and_zero_out, ao_stream_t stream);
+int ao_unpack_tinygemm_scales_and_zeros(const void* scale_and_zero, int64_t N, int64_t G,
+                                        void* scale_out, void* zero_out, ao_stream_t stream);
+
+/* pack_2xint4 — torchao/prototype/hqq/mixed_mm.py:13-33.  t: uint8 [R][C] -> uint8 [R/2][C],
+ * row 2r in the low nibble, row 2r+1 in the high nibble. */
+int ao_pack_2xint4(const uint8_t* t, int64_t R, int64_t C, uint8_t* out, ao_stream_t stream);
+
+/* Codes uint8 [N][K] (one per byte, row-major) -> the HQQ operand layout uint8 [K/2][N]
+ * (pack_2xint4 applied to the transpose, as test/hqq/test_triton_mm.py:100-106 prepares it). */
+int ao_pack_hqq_int4_from_rowmajor(const uint8_t* codes, int64_t N, int64_t K, uint8_t* out,
+                                   ao_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
+ * FPx (e3m2 and friends) codec and the FP6 tensor-core pre-packed layout.
+ * ---------------------------------------------------------------------------------------- */
+
+/* _f32_to_fpx_unpacked / _fpx_unpacked_to_f32 — torchao/prototype/custom_fp_utils.py:27-140, 145-229 */
+int ao_f32_to_fpx_unpacked(const float* x, int64_t n, int ebits, int mbits, uint8_t* out,
+                           ao_stream_t stream);
+int ao_fpx_unpacked_to_f32(const uint8_t* codes, int64_t n, int ebits, int mbits, float* out,
+                           ao_stream_t stream);
+
+/* pack_tc_fpx(codes, 6) / unpack_tc_fpx(packed, 6) — torchao/prototype/quant_llm/quant_llm.py:90-113,
+ * 172-200.  codes: uint8 [M][N] (low 6 bits used); packed: uint8 [M][N*6/8]. */
+int ao_pack_tc_fp6(const uint8_t* codes, int64_t M, int64_t N, uint8_t* packed_out, ao_stream_t stream);
+int ao_unpack_tc_fp6(const uint8_t* packed, int64_t M, int64_t N, uint8_t* codes_out, ao_stream_t stream);
+
+/* to_scaled_tc_fpx(w, 3, 2) — quant_llm.py:116-130: per-row absmax/28 scale (fp16 out),
+ * e3m2 encode, pre-pack.  w dtype F32 / F16 / BF16, [M][N]. */
+int ao_to_scaled_tc_fp6(const void* w, int w_dtype, int64_t M, int64_t N, uint8_t* packed_out,
+                        void* scale_f16_out, ao_stream_t stream);
+
+/* from_scaled_tc_fpx(packed, 3, 2, scale) — quant_llm.py:203-208.  scale_f16 may be NULL. */
+int ao_from_scaled_tc_fp6(const uint8_t* packed, int64_t M, int64_t N, const void* scale_f16,
+                          float* out, ao_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Mixed-precision linears.
+ * ---------------------------------------------------------------------------------------- */
+
+/* aten::_weight_int4pack_mm as the reference calls it — affine_quantized_tensor.py:631.
+ * x bf16 [M][K] (row stride x_row_stride elements; columns >= x_cols are read as zero, which
+ * stands in for the reference's per-call zero padding of the activation to the padded K,
+ * affine_quantized_tensor.py:625-627), packed int32 tensor_core_tiled (inner_k_tiles 8/4/2),
+ * scale_and_zero bf16 [K/group][N][2] -> y bf16 [M][N] contiguous.
+ * M <= 16 runs the HBM-bound split-K GEMV kernel; larger M is processed in row blocks.
+ *
+ * Workspace: ao_int4_tinygemm_linear_workspace_bytes(...) bytes, 256-byte aligned.  It holds a
+ * status word (int at offset 0: AO_OK, or the code of a device-side failure such as a copy
+ * that never completed), split-K completion counters and partial-sum slots.  It must be
+ * zero-filled once before its first use; every call that completes leaves it ready for the
+ * next one.  Calls that may overlap on the GPU need workspaces of their own. */
+size_t ao_int4_tinygemm_linear_workspace_bytes(int64_t M, int64_t N, int64_t K, int group,
+                                               int inner_k_tiles);
+int ao_int4_tinygemm_linear(const void* x_bf16, int64_t x_row_stride, int64_t x_cols,
+                            const int32_t* packed, const void* scale_and_zero, int64_t M, int64_t N,
+                            int64_t K, int group, int inner_k_tiles, void* y_bf16, void* workspace,
+                            size_t workspace_bytes, ao_stream_t stream);
+
+/* The GEMV kernel alone (1 <= M <= 16), same arguments and workspace rules. */
+size_t ao_int4_gemv_workspace_bytes(int64_t M, int64_t N, int64_t K, int group, int inner_k_tiles);
+int ao_int4_gemv(const void* x_bf16, int64_t x_row_stride, int64_t x_cols, const int32_t* packed,
+                 const void* scale_and_zero, int64_t M, int64_t N, int64_t K, int group,
+                 int inner_k_tiles, void* y_bf16, void* workspace, size_t workspace_bytes,
+                 ao_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AO_B200_H */

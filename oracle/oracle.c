@@ -207,7 +207,7 @@ void orc_quantize(const float* x, int64_t nb, int64_t be, int in_dt, const float
             }
         } else {                                                               /* :195-203 */
             const float sm = rnd(scale_dt, s * mid);
-            const int pm = promote(zp_dt, scale_dt);
+            const int pm = is_float_dt(zp_dt) ? promote(zp_dt, scale_dt) : scale_dt;
             const float minv = rnd(pm, z - sm);
             const int p3 = promote(in_dt, pm);
             const int p4 = promote(p3, scale_dt);
