@@ -12,7 +12,7 @@ import re
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "lib", "libao_b200.so")
+LIB_PATH = os.environ.get("AO_B200_LIB") or os.path.join(_HERE, "lib", "libao_b200.so")
 HEADER_PATH = os.path.join(os.path.dirname(_HERE), "include", "ao_b200.h")
 
 AO_OK = 0

@@ -39,10 +39,25 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
-// Bounded wait: returns false if the phase did not complete within `limit` polls.
+// try_wait that lets the hardware suspend the thread for up to hint_ns before it reports failure
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(hint_ns)
+        : "memory");
+    return ok != 0;
+}
+
+// Bounded wait: returns false if the phase did not complete within `limit` polls.  Each poll may
+// suspend the thread (no issue slots used) for up to ~0.1 ms, so the bound is limit * 0.1 ms.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, int limit) {
+    if (mbar_try_wait(bar, parity)) return true;
     for (int i = 0; i < limit; ++i) {
-        if (mbar_try_wait(bar, parity)) return true;
+        if (mbar_try_wait_hint(bar, parity, 100000u)) return true;
     }
     return false;
 }
@@ -53,6 +68,46 @@ __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst_smem, const void* src
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst_smem),
                  "l"(src_gmem), "r"(bytes), "r"(bar)
                  : "memory");
+}
+
+// 2-D tiled TMA load (no multicast): box at element coordinates (x, y) of the tensor map -> shared memory.
+// x * element size must be a multiple of 16 bytes.
+__device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const void* tensor_map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+            dst_smem),
+        "l"(tensor_map), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+
+// (a & b) | c in one logic instruction; b and c should be runtime values so that they stay in registers
+__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+// 16-byte asynchronous copy global -> shared through the load/store path (not the TMA engine); copies
+// src_bytes (0 or 16) bytes and zero-fills the rest of the 16
+__device__ __forceinline__ void cp_async_16(uint32_t dst_smem, const void* src_gmem, uint32_t src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst_smem), "l"(src_gmem), "r"(src_bytes) : "memory");
+}
+
+// the mbarrier receives one arrival from this thread once all of its earlier cp.async copies have landed;
+// the arrival must be part of the barrier's expected count (.noinc)
+__device__ __forceinline__ void cp_async_mbar_arrive_noinc(uint32_t bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void prefetch_l2(const void* p) {
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+}
+
+// high 32 bits of a * b: with b = 2^(32-s) this is a >> s, computed on the FMA pipe
+__device__ __forceinline__ uint32_t mulhi(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("mul.hi.u32 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
 }
 
 // same, with an L2 eviction-priority policy (weights are streamed once: evict_first)
@@ -94,6 +149,15 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint3
         "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// D = A * B (accumulator starts at zero)
+__device__ __forceinline__ void mma_bf16_16816_zero(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                    uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
 }
 
 // same for fp16 operands
