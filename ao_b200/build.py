@@ -20,10 +20,6 @@ NVCC_FLAGS = [
     "-Xcompiler", "-fPIC", "-Xcompiler", "-O2", "-Xcompiler", "-fvisibility=default",
     "--expt-relaxed-constexpr",
 ]
-# experiment knobs (compile-time defaults live in the sources)
-for _k in ("AO_GEMV_MULHI", "AO_GEMV_CTAS", "AO_GEMV_SKIP", "AO_GEMV_TRACE"):
-    if os.environ.get(_k):
-        NVCC_FLAGS.append(f"-D{_k}={os.environ[_k]}")
 
 
 def _nvcc():

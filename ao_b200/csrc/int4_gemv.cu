@@ -29,35 +29,30 @@ int make_plan(int64_t M, int64_t N, int64_t K, int g, int ikt, Plan* P) {
     }
     P->nslabs = nslabs;
     P->KS = (int)(K / nslabs);
-    // one unit (= one pipeline stage) is CH sub-units, about 1 KiB per 8-row tile; a slab with a sub-unit
-    // count that CH does not divide gets a last unit whose tail reads as zero (tile loads fill out-of-range
-    // elements with zero, and the x fragments past the slab end are zero too)
-    const int subs = P->KS / P->UK;
-    const int ch = stage_units(P->UB);
-    if (nslabs > 1 && subs % ch != 0) return AO_ERR_UNSUPPORTED;                // zero tail only at the end of K
-    P->CH = ch;
-    P->ups = (subs + ch - 1) / ch;
-    P->KSP = P->ups * ch * P->UK;
-    if ((long long)P->NP * P->ups > (1LL << 30)) return AO_ERR_SHAPE;
-    // shared memory: per-warp stage rings, x fragments, zero block, group sums, partial runs, barriers.
-    // One CTA per SM; as many warps (24, 16 or 8) and as deep a ring (4 .. 2 stages) as fit.
-    const int stage_tx = 2 * ch * P->UB + ch * P->GPU * 64;
-    P->stage_bytes = ((stage_tx + 127) / 128) * 128;
-    const int xs_bytes = 2 * P->KSP * P->MR * P->NB, zero_bytes = (P->UK / 32) * P->NB * P->MR * 64;
-    const int sx_bytes = (P->KSP / g) * P->NB * 32, p32_bytes = (P->KSP / 32) * P->NB * 32;
-    const int pcnt_bytes = ((P->NP / (kNumSMs / nslabs > 0 ? kNumSMs / nslabs : 1) + 2) * 4 + 15) / 16 * 16;
-    int nwarps = kMaxWarps, stages = 3;
+    // a stage holds one row pair x up to kMaxSubs sub-units of K
+    P->subs = P->KS / P->UK;
+    P->SUBS = P->subs < kMaxSubs ? P->subs : kMaxSubs;
+    P->cpp = (P->subs + P->SUBS - 1) / P->SUBS;
+    if ((long long)P->NP * P->cpp > (1LL << 30)) return AO_ERR_SHAPE;
+    const int stage_raw = 2 * P->SUBS * P->UB + P->SUBS * P->GPU * 64;
+    P->stage_bytes = ((stage_raw + 127) / 128) * 128;
+    // shared memory: stage ring, x fragments, zero block, group sums, partial sums (two pair parities),
+    // control block, barriers.  As many consumer warps (24, 16, 8) and as deep a ring (4 .. 2) as fit.
+    const int xs_bytes = 2 * P->KS * P->MR * P->NB, zero_bytes = (P->UK / 32) * P->NB * P->MR * 64;
+    const int sx_bytes = (P->KS / g) * P->NB * 32, p32_bytes = (P->KS / 32) * P->NB * 32;
+    int nwarps = kMaxConsumerWarps, stages = kMaxStages;
     for (;;) {
-        const int total = xs_bytes + zero_bytes + sx_bytes + p32_bytes + nwarps * (2 * P->NB * 512 + kMaxStages * 8) +
-                          (nwarps + 1) * 4 + 128 + pcnt_bytes + nwarps * stages * P->stage_bytes;
+        const int total = xs_bytes + zero_bytes + sx_bytes + p32_bytes + 2 * nwarps * P->NB * 512 + 512 +
+                          stages * P->stage_bytes;
         if (total <= 220 * 1024) break;
-        if (stages > 2) --stages;
-        else if (nwarps > 8) { nwarps -= 8; stages = 3; }
+        if (stages > 3) --stages;
+        else if (nwarps > 8) nwarps -= 8;
+        else if (stages > 2) --stages;
         else return AO_ERR_UNSUPPORTED;
     }
     P->nwarps = nwarps;
     P->stages = stages;
-    int off = nwarps * stages * P->stage_bytes;
+    int off = stages * P->stage_bytes;
     P->xs_off = off;
     off += xs_bytes;
     P->zero_off = off;
@@ -66,22 +61,28 @@ int make_plan(int64_t M, int64_t N, int64_t K, int g, int ikt, Plan* P) {
     off += sx_bytes;
     P->p32_off = off;
     off += p32_bytes;
-    P->part_off = off;
-    off += 2 * nwarps * P->NB * 512;
-    P->wtab_off = off;
-    off += ((nwarps + 1) * 4 + 15) / 16 * 16;
-    P->pcnt_off = off;
-    off += pcnt_bytes;
-    P->bar_off = off;
-    off += nwarps * kMaxStages * 8;
-    P->smem_bytes = off;
     int G = kNumSMs / nslabs;
     if (G < 1) G = 1;
     if (G > P->NP) G = P->NP;
     P->G = G;
+    // groups of 8 warps (four sub-units per warp and stage, unrolled) when the CTA has enough stages to keep
+    // every group busy; otherwise all warps share each stage
+    const int stages_per_cta = ((P->NP + G - 1) / G) * P->cpp;
+    P->GW = (stages_per_cta >= 2 * (nwarps / 8) && P->SUBS >= 32) ? 8 : nwarps;
+    // ring of pair buffers: within the budget of two buffers of all warps, at most kMaxPairBufs
+    const int NG = nwarps / P->GW;
+    const int nslots = (NG < P->cpp ? NG : P->cpp) * P->GW;
+    int nbuf = (2 * nwarps) / nslots;
+    if (nbuf > 8) nbuf = 8;
+    if (nbuf < 2) nbuf = 2;
+    P->nbuf = nbuf;
+    P->part_off = off;
+    off += nbuf * nslots * P->NB * 512;
+    P->bar_off = off;
+    off += 2 * kMaxStages * 8 + 2 * kMaxPairBufs * 8;
+    P->smem_bytes = off;
     P->nib_mask = 0x000F000Fu;
     P->magic = 0x43004300u;
-    P->mul28 = 1u << 28;
     P->ws_counters_off = kHeaderBytes;
     P->ws_slots_off = kHeaderBytes + (size_t)kMaxPairs * 4;
     P->ws_bytes = P->ws_slots_off + (nslabs > 1 ? (size_t)nslabs * P->NP * P->NB * 512 : 0);

@@ -4,60 +4,36 @@
 //
 // The kernel is HBM-bound: every packed weight byte is read exactly once.
 //  * One CTA per SM.  Row pairs (16 rows = two 8-row tiles) are dealt out whole and contiguously to the
-//    CTAs, so no CTA ever needs another CTA's partial sums; inside a CTA the (pair, k) work is cut
-//    into one contiguous range per warp and the main loop needs no CTA-wide synchronisation.
-//  * The weight of one 8-row tile is one contiguous byte stream along K: a warp streams its range
-//    with 1-D bulk async copies (cp.async.bulk, 2 KiB each, completion on an mbarrier) into its own
-//    ring of shared-memory stages; the group scales/zeros of the stage follow with one 16-byte
-//    cp.async per lane that signals the same mbarrier.
-//  * A packed word already is an m16n8k16 MMA fragment (8 codes of one row): codes become bf16
-//    (128 + q) with one logic op per pair and feed mma.sync with W as the 16-row operand (two 8-row
-//    tiles) and x^T as the 8-column operand, fp32 accumulate.  Scale and zero are applied per group
-//    on the accumulator:  y += s * (acc - 136 * Sx) + z * Sx,  Sx = sum of x over the group.
-//  * A row pair whose K range is shared by several warps is combined through shared memory at the
-//    end of the CTA, in a fixed order (deterministic results).  Only when the activations of the
-//    whole K range do not fit in shared memory (large M * K) is K cut into slabs handled by
-//    different CTAs; their partial sums meet in fixed slots of the workspace and the CTA that
-//    completes the pair (atomic counter) adds the slots in a fixed order and leaves the counter at
+//    CTAs, so no CTA ever needs another CTA's partial sums.
+//  * Warp specialisation: one producer warp streams the CTA's weights through a ring of shared-memory
+//    stages; a stage is one row pair x one K chunk (up to 32 sub-units of 128 k): the bytes of each
+//    8-row tile are one contiguous run in memory, so a stage is two large 1-D bulk async copies
+//    (cp.async.bulk, up to 16 KiB each, completion counted on an mbarrier) plus the chunk's group
+//    scales/zeros (16-byte cp.async pieces that signal the same mbarrier).  Full/empty mbarriers
+//    hand the stages to the consumer warps and back.
+//  * The consumer warps take the sub-units of the CTA's stream round-robin.  A packed word already is
+//    an m16n8k16 MMA fragment (8 codes of one row): codes become bf16 (128 + q) with one logic op
+//    per pair and feed mma.sync with W as the 16-row operand (two 8-row tiles) and x^T as the
+//    8-column operand, fp32 accumulate.  Scale and zero are applied per group on the accumulator:
+//    y += s * (acc - 136 * Sx) + z * Sx,  Sx = sum of x over the group.
+//  * At the end of a row pair every consumer warp leaves its partial sums in shared memory; the last
+//    one to arrive adds them in warp order (deterministic) and stores bf16.  Only when the
+//    activations of the whole K range do not fit in shared memory (large M * K) is K cut into slabs
+//    handled by different CTAs; their partial sums meet in fixed slots of the workspace and the CTA
+//    that completes the pair (atomic counter) adds the slots in slab order and leaves the counter at
 //    zero for the next call.
 #pragma once
 #include "common.cuh"
 #include "ptx.cuh"
 
-// build-time experiment knobs
-#ifndef AO_GEMV_SKIP
-#define AO_GEMV_SKIP 0
-#endif
-#ifndef AO_GEMV_TRACE
-#define AO_GEMV_TRACE 0
-#endif
-#ifndef AO_GEMV_MULHI
-#define AO_GEMV_MULHI false
-#endif
 
 namespace ao {
 namespace gemv {
 
-#if AO_GEMV_TRACE
-static __device__ unsigned long long g_trace[1024 * 8];
-__device__ __forceinline__ unsigned long long gtime() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-#define AO_TRACE(slot) do { if (threadIdx.x == 0) g_trace[(blockIdx.y * gridDim.x + blockIdx.x) * 8 + (slot)] = gtime(); } while (0)
-#else
-#define AO_TRACE(slot) do { } while (0)
-#endif
-
-constexpr int kMaxWarps = 16;
-constexpr int kMaxThreads = kMaxWarps * 32;
+constexpr int kMaxConsumerWarps = 16;
+constexpr int kMaxThreads = (kMaxConsumerWarps + 2) * 32;  // + the producer warp and the reducer warp
 constexpr int kMaxStages = 4;
-constexpr bool kShiftOnFmaPipe = AO_GEMV_MULHI;  // right shifts as mul.hi (FMA pipe) instead of shf (ALU pipe)
-
-// sub-units per unit (= per pipeline stage) for a sub-unit of UB bytes per 8-row tile: 2 KiB per tile, so
-// that one bulk copy moves enough bytes to keep the copy engine's request rate off the critical path
-__host__ __device__ constexpr int stage_units(int ub) { return 2048 / ub > 1 ? 2048 / ub : 1; }
+constexpr int kMaxSubs = 32;             // sub-units per stage
 constexpr int kWaitPolls = 2000;          // suspending polls (<= 0.1 ms each) of one mbarrier phase
 constexpr int kXsmemBudget = 64 * 1024;   // bytes of shared memory for the activation fragments
 constexpr int kHeaderBytes = 256;
@@ -68,16 +44,17 @@ struct Plan {
     int M, N, K, g, ikt, NB, MR;
     int NT, NP;        // 8-row tiles, 16-row pairs
     int UK, UB;        // k values per sub-unit, bytes per sub-unit per 8-row tile
-    int CH;            // sub-units per unit; one unit = one pipeline stage = one weight tile load
     int GPU;           // groups per sub-unit
     int nslabs, KS;    // K slabs (split-K across CTAs so that the x slab fits shared memory)
-    int ups;           // units per pair per slab
+    int subs;          // sub-units per pair per slab
+    int SUBS, cpp;     // sub-units per full stage, stages (K chunks) per pair
     int G;             // CTAs per slab
-    int nwarps;        // warps per CTA
+    int nwarps;        // consumer warps per CTA (the CTA has one more warp, the producer)
+    int GW;            // consumer warps that share one stage (nwarps / GW groups take the stages in turn)
+    int nbuf;          // ring of per-pair partial-sum buffers
     int stages, stage_bytes;  // ring depth, bytes per stage
-    int KSP;           // slab length rounded up to whole units (x fragments beyond KS are zero)
-    int xs_off, zero_off, sx_off, p32_off, part_off, wtab_off, pcnt_off, bar_off, smem_bytes;
-    uint32_t nib_mask, magic, mul28;  // 0x000F000F, bf16x2 (128, 128), 2^28: runtime values so they stay in registers
+    int xs_off, zero_off, sx_off, p32_off, part_off, bar_off, smem_bytes;
+    uint32_t nib_mask, magic;  // 0x000F000F, bf16x2 (128, 128): runtime values so they stay in registers
     size_t ws_counters_off, ws_slots_off, ws_bytes;
 };
 
@@ -179,21 +156,17 @@ struct Shape {
     static constexpr int SPU = UK / 32;                                       // k32 steps per sub-unit
     static constexpr int GPU = SPU / G32;                                     // groups per sub-unit
     static constexpr int UB = UK * 4;                                         // bytes per sub-unit per 8-row tile
-    static constexpr int CH = stage_units(UB);                                // sub-units per unit (stage)
     static constexpr int MRL = MR * 4;                                        // lanes that carry a batch column
     static constexpr int XSTEP = NB * MRL * 16;                               // bytes of x fragments per k32 step
 };
 
 // Dequantise-and-multiply CNT consecutive sub-units that start at sub-unit i0 of the stage at `st`.
-//   su: index (inside the K slab) of the first of these sub-units.
-//   m28, m24, m20: 2^28, 2^24, 2^20 as runtime values (right shifts by 4, 8, 12 as a multiply-high).
+//   su: index (inside the K slab) of the first of these sub-units; tile_b: byte offset of tile B's bytes.
 template <int IKT, int NB, int MR, int G32, int CNT>
-__device__ __forceinline__ void process_units(float (&acc)[NB][4], uint32_t st, int i0, int su, uint32_t w_lane,
-                                              uint32_t sc_lane, uint32_t x_base, uint32_t x_unit_stride,
-                                              uint32_t sx_base, uint32_t nib, uint32_t magic, uint32_t m28,
-                                              uint32_t m24, uint32_t m20) {
+__device__ __forceinline__ void process_units(float (&acc)[NB][4], uint32_t st, int i0, int su, uint32_t tile_b,
+                                              uint32_t w_lane, uint32_t sc_lane, uint32_t x_base,
+                                              uint32_t x_unit_stride, uint32_t sx_base, uint32_t nib, uint32_t magic) {
     using S = Shape<IKT, NB, MR, G32>;
-    constexpr uint32_t tile_b = S::CH * S::UB;
 #pragma unroll
     for (int i = 0; i < CNT; ++i) {
         const uint32_t xa = x_base + (su + i) * x_unit_stride;
@@ -212,18 +185,10 @@ __device__ __forceinline__ void process_units(float (&acc)[NB][4], uint32_t st, 
                 const int ks_rel = o * kHalf + jj;
                 const uint32_t wa_ = wa[jj], wb_ = wb[jj];
                 // (128 + q) as bf16 pairs: rows of tile A in a0/a2, rows of tile B in a1/a3
-                uint32_t sa4, sa8, sa12, sb4, sb8, sb12;
-                if constexpr (kShiftOnFmaPipe) {
-                    sa4 = ptx::mulhi(wa_, m28); sa8 = ptx::mulhi(wa_, m24); sa12 = ptx::mulhi(wa_, m20);
-                    sb4 = ptx::mulhi(wb_, m28); sb8 = ptx::mulhi(wb_, m24); sb12 = ptx::mulhi(wb_, m20);
-                } else {
-                    sa4 = wa_ >> 4; sa8 = wa_ >> 8; sa12 = wa_ >> 12;
-                    sb4 = wb_ >> 4; sb8 = wb_ >> 8; sb12 = wb_ >> 12;
-                }
-                const uint32_t a0 = ptx::and_or(wa_, nib, magic), a2 = ptx::and_or(sa4, nib, magic);
-                const uint32_t a1 = ptx::and_or(wb_, nib, magic), a3 = ptx::and_or(sb4, nib, magic);
-                const uint32_t e0 = ptx::and_or(sa8, nib, magic), e2 = ptx::and_or(sa12, nib, magic);
-                const uint32_t e1 = ptx::and_or(sb8, nib, magic), e3 = ptx::and_or(sb12, nib, magic);
+                const uint32_t a0 = ptx::and_or(wa_, nib, magic), a2 = ptx::and_or(wa_ >> 4, nib, magic);
+                const uint32_t a1 = ptx::and_or(wb_, nib, magic), a3 = ptx::and_or(wb_ >> 4, nib, magic);
+                const uint32_t e0 = ptx::and_or(wa_ >> 8, nib, magic), e2 = ptx::and_or(wa_ >> 12, nib, magic);
+                const uint32_t e1 = ptx::and_or(wb_ >> 8, nib, magic), e3 = ptx::and_or(wb_ >> 12, nib, magic);
 #pragma unroll
                 for (int nb = 0; nb < NB; ++nb) {
                     const uint4 xb = ptx::lds128(xa + ks_rel * S::XSTEP + nb * (S::MRL * 16));
@@ -263,117 +228,150 @@ __device__ __forceinline__ void process_units(float (&acc)[NB][4], uint32_t st, 
     }
 }
 
+// shared-memory control block of one CTA
+constexpr int kMaxPairBufs = 8;
+
 template <int IKT, int NB, int MR, int G32>
 __global__ void __launch_bounds__(kMaxThreads, 1)
 int4_gemv_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int Kx, const uint8_t* __restrict__ wq,
                  const uint8_t* __restrict__ sz, __nv_bfloat16* __restrict__ y, uint8_t* __restrict__ ws,
                  const __grid_constant__ Plan P) {
     using S = Shape<IKT, NB, MR, G32>;
-    constexpr int UB = S::UB, UK = S::UK, MRL = S::MRL, CH = S::CH;
-    constexpr int kScaleCopies = CH * S::GPU * 4;  // 16-byte pieces of one stage's scales/zeros
+    constexpr int UB = S::UB, UK = S::UK, MRL = S::MRL;
     extern __shared__ __align__(128) uint8_t smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int nthreads = blockDim.x, nwarps = nthreads >> 5;
+    const int nwarps = P.nwarps, nconsumers = nwarps * 32;
     const int slab = blockIdx.y, cta = blockIdx.x;
-    AO_TRACE(0);
     const uint32_t smem_base = ptx::smem_addr(smem);
     const int nstages = P.stages, stage_bytes = P.stage_bytes;
-    const uint32_t stage0 = smem_base + warp * nstages * stage_bytes;
-    const uint32_t bars = smem_base + P.bar_off + warp * kMaxStages * 8;
-    const int ups = P.ups, subs = P.KS / UK;
+    const uint32_t full_bar = smem_base + P.bar_off, empty_bar = full_bar + kMaxStages * 8;
+    const uint32_t pair_full_bar = empty_bar + kMaxStages * 8, pair_free_bar = pair_full_bar + kMaxPairBufs * 8;
+    const int subs = P.subs, SUBS = P.SUBS, cpp = P.cpp;
+    const uint32_t tile_b = SUBS * UB, sc_off = 2 * SUBS * UB;
     int* status = reinterpret_cast<int*>(ws);
 
-    // whole row pairs per CTA; the CTA's units (pair-major, k-minor) are cut into one range per warp
+    // whole row pairs per CTA; its stream of stages is (pair, K chunk), pair-major
     const int pbeg = static_cast<int>((static_cast<unsigned>(cta) * static_cast<unsigned>(P.NP)) / static_cast<unsigned>(P.G));
     const int pend = static_cast<int>((static_cast<unsigned>(cta + 1) * static_cast<unsigned>(P.NP)) / static_cast<unsigned>(P.G));
-    const int ubeg = pbeg * ups, Lc = (pend - pbeg) * ups;
-    const int wbeg = ubeg + (warp * Lc) / nwarps, wend = ubeg + ((warp + 1) * Lc) / nwarps;
+    const int nstage_total = (pend - pbeg) * cpp;
 
-    // bring this slab of x towards L2 before the weight stream fills the memory queues
-    {
-        const int kx0 = slab * P.KS;
-        const int xbytes = 2 * max(0, min(P.KS, Kx - kx0));
-        const int lines = (xbytes + 127) >> 7;
-        for (int i = tid; i < P.M * lines; i += nthreads) {
-            const int m = i / lines, l = i - m * lines;
-            ptx::prefetch_l2(reinterpret_cast<const uint8_t*>(x + (long long)m * ldx + kx0) + (l << 7));
+    if (tid == nconsumers) {
+        for (int s = 0; s < nstages; ++s) {
+            ptx::mbar_init(full_bar + 8 * s, 33);       // expect_tx arrival + one cp.async arrival per producer lane
+            ptx::mbar_init(empty_bar + 8 * s, P.GW);    // one arrival per consumer warp of the stage's group
         }
-        int* pc = reinterpret_cast<int*>(smem + P.pcnt_off);
-        for (int i = tid; i < pend - pbeg; i += nthreads) pc[i] = 0;
-    }
-    if (lane == 0) {
-        int* wt = reinterpret_cast<int*>(smem + P.wtab_off);
-        wt[warp] = wbeg;
-        if (warp == nwarps - 1) wt[nwarps] = ubeg + Lc;
-        // one arrival for the expect_tx of the weight copies, one per lane for its scale copies
-        for (int s = 0; s < nstages; ++s) ptx::mbar_init(bars + 8 * s, 33);
+        const int nslots_init = min(nwarps / P.GW, cpp) * P.GW;
+        for (int i = 0; i < P.nbuf; ++i) {
+            ptx::mbar_init(pair_full_bar + 8 * i, nslots_init);  // one arrival per warp that worked on the pair
+            ptx::mbar_init(pair_free_bar + 8 * i, 1);            // the reducer hands the buffer back
+        }
         ptx::fence_mbar_init();
     }
-    __syncwarp();
-    AO_TRACE(6);
+    __syncthreads();
 
-    // ---- producer side: one unit = one stage: [tile A bytes][tile B bytes][scales/zeros] ----------------
-    //   weights: CH sub-units (fewer in the last unit of K when CH does not divide) of rows 2p and 2p+1 of the
-    //            packed tensor, two 1-D bulk copies issued by lane 0;
-    //   scales/zeros: CH*GPU group rows x 64 bytes ((scale, zero) of the pair's 16 rows), 16 bytes per lane;
-    //            pieces past the end of K or N are zero-filled.
-    int pu = wbeg, pp = wbeg / ups, pul = wbeg - pp * ups, pstage = 0, issued = 0;
-    auto issue_weights = [&](int p_, int ul_, int stage) {
-        const int k0 = slab * P.KS + ul_ * (CH * UK);
-        const int nsub = min(CH, subs - ul_ * CH);
-        const bool has_b = (2 * p_ + 1) < P.NT;
-        const uint32_t wbytes = static_cast<uint32_t>(nsub * UB);
-        const uint32_t dst = stage0 + stage * stage_bytes;
-        const uint32_t bar = bars + 8 * stage;
-        const uint8_t* src = wq + ((size_t)(2 * p_) * P.K + k0) * 4;
-        ptx::mbar_arrive_expect_tx(bar, has_b ? 2u * wbytes : wbytes);
-        ptx::bulk_copy_g2s(dst, src, wbytes, bar);
-        if (has_b) ptx::bulk_copy_g2s(dst + CH * UB, src + (size_t)P.K * 4, wbytes, bar);
-    };
-    auto issue_scales = [&](int p_, int ul_, int stage) {
-        const int kg0 = (slab * P.KS + ul_ * (CH * UK)) / (32 * G32);
-        const uint32_t dst = stage0 + stage * stage_bytes + 2 * CH * UB;
-        const int pieces_ok = (2 * p_ + 1) < P.NT ? 4 : 2;  // a lone last tile has only 32 bytes per group
-#pragma unroll
-        for (int c0 = 0; c0 < kScaleCopies; c0 += 32) {
-            const int c = c0 + lane;
-            if (kScaleCopies % 32 == 0 || c < kScaleCopies) {
-                const int gi = c >> 2, piece = c & 3;
-                const bool live = (kg0 + gi) * (32 * G32) < P.K && piece < pieces_ok;
-                const uint8_t* src = sz + ((size_t)(live ? kg0 + gi : 0) * P.N + 16 * p_) * 4 + (live ? piece * 16 : 0);
-                ptx::cp_async_16(dst + c * 16, src, live ? 16u : 0u);
+    if (warp == nwarps) {
+        // =============================== producer warp =================================================
+        // stage = [tile A bytes][tile B bytes][scales/zeros: one 64-byte row per group]
+        int pi = 0, c = 0, s = 0;
+        uint32_t phase = 1;  // a fresh barrier counts as "previous phase complete"
+        bool ok = true;
+        for (int t = 0; t < nstage_total; ++t) {
+            if (!ptx::mbar_wait_bounded(empty_bar + 8 * s, phase, kWaitPolls)) {
+                ok = false;
+                break;
+            }
+            const int p = pbeg + pi;
+            const int sub0 = c * SUBS;
+            const int nsub = min(SUBS, subs - sub0);
+            const int k0 = slab * P.KS + sub0 * UK;
+            const bool has_b = (2 * p + 1) < P.NT;
+            const uint32_t dst = smem_base + s * stage_bytes;
+            const uint32_t bar = full_bar + 8 * s;
+            if (lane == 0) {
+                const uint32_t wbytes = static_cast<uint32_t>(nsub * UB);
+                const uint8_t* src = wq + ((size_t)(2 * p) * P.K + k0) * 4;
+                ptx::mbar_arrive_expect_tx(bar, has_b ? 2u * wbytes : wbytes);
+                ptx::bulk_copy_g2s(dst, src, wbytes, bar);
+                if (has_b) ptx::bulk_copy_g2s(dst + tile_b, src + (size_t)P.K * 4, wbytes, bar);
+            }
+            {
+                // 64 bytes ((scale, zero) of the pair's 16 rows) per group; a lone last tile has only 32
+                const int kg0 = k0 / (32 * G32);
+                const int pieces = nsub * S::GPU * 4;
+                const int piece_ok = has_b ? 4 : 2;
+                for (int q = lane; q < pieces; q += 32) {
+                    const int gi = q >> 2, piece = q & 3;
+                    const bool live = piece < piece_ok;
+                    const uint8_t* src = sz + ((size_t)(kg0 + gi) * P.N + 16 * p) * 4 + (live ? piece * 16 : 0);
+                    ptx::cp_async_16(dst + sc_off + q * 16, src, live ? 16u : 0u);
+                }
+                ptx::cp_async_mbar_arrive_noinc(bar);
+            }
+            if (++c == cpp) {
+                c = 0;
+                ++pi;
+            }
+            if (++s == nstages) {
+                s = 0;
+                phase ^= 1u;
             }
         }
-        ptx::cp_async_mbar_arrive_noinc(bars + 8 * stage);
-    };
-    auto advance = [&]() {
-        ++pu;
-        if (++pul == ups) {
-            pul = 0;
-            ++pp;
-        }
-        if (++pstage == nstages) pstage = 0;
-        ++issued;
-    };
-    {
-        const int first = min(nstages, wend - wbeg);
-        for (int s = 0; s < first; ++s) {
-            if (lane == 0) issue_weights(pp, pul, pstage);
-            issue_scales(pp, pul, pstage);
-            advance();
-        }
+        if (!ok && lane == 0) atomicExch(status, AO_ERR_TIMEOUT);
+        return;
     }
-    AO_TRACE(1);
 
-    // ---- activation prologue: x slab -> MMA fragment order, plus per-group sums of x ----------------
+    if (warp == nwarps + 1) {
+        // =============================== reducer warp ==================================================
+        // adds the consumer warps' partial sums of each finished pair in slot order and stores the rows
+        const int NGr = nwarps / P.GW;
+        const int nslots = min(NGr, cpp) * P.GW, nbuf = P.nbuf;
+        const float4* parts = reinterpret_cast<const float4*>(smem + P.part_off);
+        bool ok = true;
+        for (int pi = 0; pi < pend - pbeg; ++pi) {
+            const int buf = pi % nbuf;
+            if (!ptx::mbar_wait_bounded(pair_full_bar + 8 * buf, static_cast<uint32_t>(pi / nbuf) & 1u, kWaitPolls)) {
+                ok = false;
+                break;
+            }
+            float sum[NB][4];
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) sum[nb][i] = 0.f;
+            // nslots is a multiple of 8: eight slots' loads are issued before any is used
+            const float4* src = parts + (buf * nslots) * (NB * 32) + lane;
+            for (int w0 = 0; w0 < nslots; w0 += 8) {
+                float4 v[8][NB];
+#pragma unroll
+                for (int q = 0; q < 8; ++q)
+#pragma unroll
+                    for (int nb = 0; nb < NB; ++nb) v[q][nb] = src[((w0 + q) * NB + nb) * 32];
+#pragma unroll
+                for (int q = 0; q < 8; ++q)
+#pragma unroll
+                    for (int nb = 0; nb < NB; ++nb) {
+                        sum[nb][0] += v[q][nb].x; sum[nb][1] += v[q][nb].y;
+                        sum[nb][2] += v[q][nb].z; sum[nb][3] += v[q][nb].w;
+                    }
+            }
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(pair_free_bar + 8 * buf);
+            finish_pair<NB>(P, sum, pbeg + pi, slab, lane, y, ws);
+        }
+        if (!ok && lane == 0) atomicExch(status, AO_ERR_TIMEOUT);
+        return;
+    }
+
+    // ================================= consumer warps ==================================================
+    // ---- activation prologue: x slab -> MMA fragment order, plus per-group sums of x -------------------
     {
-        const int steps = P.KSP / 32;         // fragments past the slab end (odd sub-unit count) are zero
+        const int steps = P.KS / 32;
         const int items = steps * NB * MRL;  // one item = 4 words (two k16 tiles) of one lane
         const int items_round = (items + 31) / 32 * 32;
         float* p32 = reinterpret_cast<float*>(smem + P.p32_off);
         // lanes without a batch column read zeros: one sub-unit's worth of fragment bytes
-        for (int i = tid; i < S::SPU * S::XSTEP / 4; i += nthreads) reinterpret_cast<uint32_t*>(smem + P.zero_off)[i] = 0u;
-        for (int it = tid; it < items_round; it += nthreads) {
+        for (int i = tid; i < S::SPU * S::XSTEP / 4; i += nconsumers) reinterpret_cast<uint32_t*>(smem + P.zero_off)[i] = 0u;
+        for (int it = tid; it < items_round; it += nconsumers) {
             uint4 wv = make_uint4(0u, 0u, 0u, 0u);
             float psum = 0.f;
             int l = 0, blk = 0;
@@ -389,7 +387,7 @@ int4_gemv_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int Kx, con
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
                         const int kk = k + 8 * q;
-                        w[q] = (kk < Kx && step * 32 + 2 * c + 8 * q < P.KS) ? __ldg(row + (kk >> 1)) : 0u;
+                        w[q] = (kk < Kx) ? __ldg(row + (kk >> 1)) : 0u;
                     }
                     wv = make_uint4(w[0], w[1], w[2], w[3]);
 #pragma unroll
@@ -403,10 +401,10 @@ int4_gemv_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int Kx, con
             psum += __shfl_xor_sync(0xffffffffu, psum, 2);
             if (it < items && (l & 3) == 0) p32[blk * 8 + (l >> 2)] = psum;
         }
-        __syncthreads();
+        ptx::named_barrier_sync(1, nconsumers);
         float* sx = reinterpret_cast<float*>(smem + P.sx_off);
-        const int groups = P.KSP / (32 * G32);
-        for (int it = tid; it < groups * NB * 8; it += nthreads) {
+        const int groups = P.KS / (32 * G32);
+        for (int it = tid; it < groups * NB * 8; it += nconsumers) {
             const int mm = it & 7, nb = (it >> 3) % NB, kg = it / (8 * NB);
             float s = 0.f;
             if (mm < MR) {
@@ -415,122 +413,78 @@ int4_gemv_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int Kx, con
             }
             sx[it] = s;
         }
-        __syncthreads();
+        ptx::named_barrier_sync(1, nconsumers);
     }
 
-    AO_TRACE(2);
-    // ---- main loop: no CTA-wide synchronisation -----------------------------------------------------
+    // ---- main loop: sub-units of the CTA's stream are dealt round-robin to the consumer warps ---------
     const bool x_lane = lane < MRL;
     const uint32_t x_base = x_lane ? smem_base + P.xs_off + lane * 16 : smem_base + P.zero_off;
     const uint32_t x_unit_stride = x_lane ? static_cast<uint32_t>(S::SPU * S::XSTEP) : 0u;
     const uint32_t sx_base = smem_base + P.sx_off + (lane & 3) * 8;
     const uint32_t w_lane = lane * (S::HALF * 4);
-    const uint32_t sc_lane = 2 * CH * UB + (lane >> 2) * 4;
-    const uint32_t nib = P.nib_mask, magic = P.magic, m28 = P.mul28, m24 = P.mul28 >> 4, m20 = P.mul28 >> 8;
-    float4* part = reinterpret_cast<float4*>(smem + P.part_off) + warp * (2 * NB * 32);
-    const float4* parts = reinterpret_cast<const float4*>(smem + P.part_off);
-    const int* wtab = reinterpret_cast<const int*>(smem + P.wtab_off);  // first unit of every warp, then the end
-    int* pcnt = reinterpret_cast<int*>(smem + P.pcnt_off);               // units finished, per pair of this CTA
-    const float inv_units_per_warp = Lc > 0 ? static_cast<float>(nwarps) / static_cast<float>(Lc) : 0.f;
-    int cstage = 0, consumed = 0;
-    uint32_t phase = 0;
-    bool ok = true;
+    const uint32_t sc_lane = sc_off + (lane >> 2) * 4;
+    const uint32_t nib = P.nib_mask, magic = P.magic;
+    float4* parts = reinterpret_cast<float4*>(smem + P.part_off);  // [pair parity][warp][NB][32]
     float acc[NB][4];
 #pragma unroll
     for (int nb = 0; nb < NB; ++nb)
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[nb][i] = 0.f;
-    int p = wbeg / ups, ul = wbeg - p * ups, ul0 = ul;
-    for (int u = wbeg; u < wend; ++u) {
-        if (!ptx::mbar_wait_bounded(bars + 8 * cstage, phase, kWaitPolls)) {
+    // Consumer warps form NG groups of GW warps; the stages of the CTA's stream go to the groups in turn, and
+    // inside a group every warp takes a contiguous run of the stage's sub-units (unrolled four at a time).
+    const int GW = P.GW, NG = nwarps / GW;
+    const int grp = warp / GW, wi = warp - grp * GW;
+    const int npairs = pend - pbeg;
+    bool ok = true;
+    const int ncontrib = min(NG, cpp);           // groups that work on one pair
+    const int nslots = ncontrib * GW;            // warps whose partial sums make up one pair
+    const int nbuf = P.nbuf;                     // pair buffers in the ring
+    for (int pi = 0; pi < npairs && ok; ++pi) {
+        const int first_grp = (pi * cpp) % NG;   // the pair's stages go to groups first_grp, first_grp + 1, ...
+        int ordinal = grp - first_grp;
+        if (ordinal < 0) ordinal += NG;
+        if (ordinal >= ncontrib) continue;       // this warp's group has no stage of this pair
+        for (int c = ordinal; c < cpp; c += NG) {
+            const int t = pi * cpp + c;
+            const int s = t % nstages;
+            const uint32_t phase = static_cast<uint32_t>(t / nstages) & 1u;
+            const int sub0 = c * SUBS;
+            const int nsub = min(SUBS, subs - sub0);
+            if (!ptx::mbar_wait_bounded(full_bar + 8 * s, phase, kWaitPolls)) {
+                ok = false;
+                break;
+            }
+            const uint32_t st = smem_base + s * stage_bytes;
+            int j = (wi * nsub) / GW;
+            const int jend = ((wi + 1) * nsub) / GW;
+            for (; j + 4 <= jend; j += 4)
+                process_units<IKT, NB, MR, G32, 4>(acc, st, j, sub0 + j, tile_b, w_lane, sc_lane, x_base, x_unit_stride,
+                                                   sx_base, nib, magic);
+            for (; j < jend; ++j)
+                process_units<IKT, NB, MR, G32, 1>(acc, st, j, sub0 + j, tile_b, w_lane, sc_lane, x_base, x_unit_stride,
+                                                   sx_base, nib, magic);
+            __syncwarp();  // every lane is done reading this stage
+            if (lane == 0) ptx::mbar_arrive(empty_bar + 8 * s);
+        }
+        if (!ok) break;
+        // the pair is complete for this warp: leave the partial sums for the reducer warp
+        const int buf = pi % nbuf;
+        // the buffer must have been handed back after the pair that used it before
+        if (!ptx::mbar_wait_bounded(pair_free_bar + 8 * buf, (static_cast<uint32_t>(pi / nbuf) & 1u) ^ 1u, kWaitPolls)) {
             ok = false;
             break;
         }
-#if AO_GEMV_SKIP != 1
-        process_units<IKT, NB, MR, G32, CH>(acc, stage0 + cstage * stage_bytes, 0, ul * CH, w_lane, sc_lane, x_base,
-                                            x_unit_stride, sx_base, nib, magic, m28, m24, m20);
-#else
-        acc[0][0] += __uint_as_float(ptx::lds32(stage0 + cstage * stage_bytes + w_lane));
-#endif
-        ++consumed;
-        __syncwarp();  // every lane is done reading this stage
-        if (pu < wend) {
-            if (lane == 0) issue_weights(pp, pul, pstage);
-            issue_scales(pp, pul, pstage);
-            advance();
+        float4* slot = parts + (buf * nslots + ordinal * GW + wi) * (NB * 32);
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) {
+            slot[nb * 32 + lane] = make_float4(acc[nb][0], acc[nb][1], acc[nb][2], acc[nb][3]);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[nb][i] = 0.f;
         }
-        if (++cstage == nstages) {
-            cstage = 0;
-            phase ^= 1u;
-        }
-        ++ul;
-        if (ul == ups || u + 1 == wend) {
-            // this warp's run over row pair p ends
-            if (ul0 == 0 && ul == ups) {
-                // the whole K range (of this slab) of the pair was ours
-                finish_pair<NB>(P, acc, p, slab, lane, y, ws);
-            } else {
-                // partial run: a head (started inside the pair) goes to slot 0, a tail to slot 1; the warp that
-                // brings the pair's unit count to ups adds all of its runs in warp order and stores the rows
-                float4* slot = part + (ul0 > 0 ? 0 : NB * 32);
-#pragma unroll
-                for (int nb = 0; nb < NB; ++nb)
-                    slot[nb * 32 + lane] = make_float4(acc[nb][0], acc[nb][1], acc[nb][2], acc[nb][3]);
-                __threadfence_block();
-                __syncwarp();
-                int old = 0;
-                if (lane == 0) old = atomicAdd(pcnt + (p - pbeg), ul - ul0);
-                old = __shfl_sync(0xffffffffu, old, 0);
-                if (old + (ul - ul0) == ups) {
-                    __threadfence_block();
-                    const int g0 = p * ups, g1 = g0 + ups;
-                    int w = min(nwarps - 1, static_cast<int>(static_cast<float>(g0 - ubeg) * inv_units_per_warp));
-                    while (w > 0 && wtab[w] > g0) --w;
-                    while (w + 1 < nwarps && wtab[w + 1] <= g0) ++w;
-                    float sum[NB][4];
-#pragma unroll
-                    for (int nb = 0; nb < NB; ++nb)
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) sum[nb][i] = 0.f;
-                    for (; w < nwarps && wtab[w] < g1; ++w) {
-                        if (wtab[w + 1] <= g0) continue;  // a warp without units
-                        const float4* sl = parts + w * (2 * NB * 32) + (wtab[w] > g0 ? 0 : NB * 32);
-#pragma unroll
-                        for (int nb = 0; nb < NB; ++nb) {
-                            const float4 v = sl[nb * 32 + lane];
-                            sum[nb][0] += v.x; sum[nb][1] += v.y; sum[nb][2] += v.z; sum[nb][3] += v.w;
-                        }
-                    }
-                    finish_pair<NB>(P, sum, p, slab, lane, y, ws);
-                }
-            }
-#pragma unroll
-            for (int nb = 0; nb < NB; ++nb)
-#pragma unroll
-                for (int i = 0; i < 4; ++i) acc[nb][i] = 0.f;
-            if (ul == ups) {
-                ul = 0;
-                ++p;
-            }
-            ul0 = ul;
-        }
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(pair_full_bar + 8 * buf);
     }
-    AO_TRACE(3);
-    if (!ok) {
-        // A copy never signalled.  Record it, then wait (bounded) for whatever else is in flight so that the
-        // CTA's shared memory is not released under a pending copy.
-        if (lane == 0) atomicExch(status, AO_ERR_TIMEOUT);
-        int ss = cstage;
-        uint32_t ph = phase;
-        for (int q = consumed; q < issued; ++q) {
-            ptx::mbar_wait_bounded(bars + 8 * ss, ph, kWaitPolls);
-            if (++ss == nstages) {
-                ss = 0;
-                ph ^= 1u;
-            }
-        }
-    }
-    AO_TRACE(5);
+    if (!ok && lane == 0) atomicExch(status, AO_ERR_TIMEOUT);
 }
 
 template <int IKT, int NB, int MR, int G32>
@@ -540,7 +494,7 @@ int launch_one(const Plan& P, const void* x, long long ldx, int Kx, const void* 
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P.smem_bytes) != cudaSuccess)
         return AO_ERR_LAUNCH;
     dim3 grid(P.G, P.nslabs);
-    kern<<<grid, P.nwarps * 32, P.smem_bytes, st>>>(static_cast<const __nv_bfloat16*>(x), ldx, Kx,
+    kern<<<grid, (P.nwarps + 2) * 32, P.smem_bytes, st>>>(static_cast<const __nv_bfloat16*>(x), ldx, Kx,
                                                     static_cast<const uint8_t*>(wq), static_cast<const uint8_t*>(sz),
                                                     static_cast<__nv_bfloat16*>(y), static_cast<uint8_t*>(ws), P);
     return launch_status();

@@ -8,8 +8,3 @@ template int launch_ikt<8>(const Plan&, const void*, long long, int, const void*
 }
 }  // namespace ao
 
-#if AO_GEMV_TRACE
-extern "C" int ao_debug_read_trace(unsigned long long* host_out, int n) {
-    return (int)cudaMemcpyFromSymbol(host_out, ao::gemv::g_trace, sizeof(unsigned long long) * n);
-}
-#endif
