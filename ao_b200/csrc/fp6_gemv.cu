@@ -1,0 +1,514 @@
+// Decode-shaped FP6 (e3m2) weight-only linear, M <= 16:
+//   y[M][N] = x[M][K] (fp16) @ (decode(W)[N][K] * scale[N])^T      -> fp16
+// on the tensor-core pre-packed weight of torchao/prototype/quant_llm/quant_llm.py:90-106, replacing
+// torchao::quant_llm_linear (torchao/ops.py:15-37, torchao/csrc/cuda/fp6_llm/fp6_linear.cu:139-196) for
+// decode shapes.
+//
+// Layout facts used here (derived from the packer): for a block of 64 output rows `a` and a 16-wide k tile
+// `f` the 2-bit plane holds 256 contiguous bytes and the 4-bit plane 512; all k tiles of one row block are
+// contiguous, so a row block is two byte streams (16*K and 32*K bytes).  Inside (a, f), word t of each
+// 128-byte piece belongs to warp lane t and already is the m16n8k16 A fragment of that lane: the four
+// bytes of the 4-bit word are (row e+8 | row e) x (col 2c | col 2c+1), high nibble column j, low nibble
+// column j+8 (e = t/4, c = t%4); the 2-bit word has the same byte meaning with the two 16-row halves of a
+// 32-row piece in bits 7..4 and 3..0.
+//
+// Structure: one CTA per SM; a producer warp streams (row block, K chunk) stages with two 1-D bulk async
+// copies each through a full/empty mbarrier ring; groups of eight consumer warps take the stages in turn,
+// every warp a contiguous run of k tiles; codes become fp16 bit patterns (sign, exponent and mantissa bits
+// land in fp16's fields, a factor 2^12 short) with logic ops and one integer multiply per register, and
+// feed mma.sync (fp16 operands, fp32 accumulate) with W as the 16-row operand.  A reducer warp adds the
+// consumer warps' partial sums in slot order, applies 2^12 * scale[row] and stores fp16.  K is cut into
+// slabs over CTAs when there are too few row blocks to fill the machine or the activations do not fit
+// in shared memory; slab partial sums meet in workspace slots and the CTA that completes a row block
+// (atomic counter) adds them in slab order.
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace ao {
+namespace fp6 {
+
+constexpr int kConsumerWarps = 16;
+constexpr int kGroupWarps = 8;
+constexpr int kThreads = (kConsumerWarps + 2) * 32;
+constexpr int kMaxStages = 4;
+constexpr int kMaxTiles = 32;   // k16 tiles per stage (512 k)
+constexpr int kMaxBlockBufs = 4;
+constexpr int kWaitPolls = 2000;
+constexpr int kHeaderBytes = 256;
+constexpr int kMaxBlocks = 16384;
+
+struct Plan {
+    int M, N, K, NB, MR;
+    int NA;            // 64-row blocks
+    int nslabs, KS;    // K slabs
+    int tiles;         // k16 tiles per slab
+    int TILES, cpb;    // k16 tiles per full stage, stages (K chunks) per row block
+    int G;             // CTAs per slab
+    int stages, stage_bytes;
+    int nbuf;          // ring of per-row-block partial-sum buffers
+    int xs_off, zero_off, part_off, bar_off, smem_bytes;
+    uint32_t m4, mh, f_hi, f_lo, k_hi, k_lo;  // masks / multipliers as runtime values (kept in registers)
+    size_t ws_counters_off, ws_slots_off, ws_bytes;
+};
+
+static int make_plan(int64_t M, int64_t N, int64_t K, Plan* P) {
+    if (M < 1 || M > 16) return AO_ERR_SHAPE;
+    if (N < 64 || N % 64 != 0 || K < 64 || K % 64 != 0) return AO_ERR_SHAPE;
+    if (N > 64 * kMaxBlocks || K > (1 << 22)) return AO_ERR_SHAPE;
+    P->M = (int)M; P->N = (int)N; P->K = (int)K;
+    P->NB = M > 8 ? 2 : 1;
+    P->MR = M > 4 ? 8 : (M > 2 ? 4 : (M > 1 ? 2 : 1));
+    P->NA = (int)(N / 64);
+    // K slabs: the x fragments of a slab (KS * MR * NB * 2 bytes) must fit next to a ring of two stages, and
+    // row blocks x slabs should fill the SMs evenly
+    const int ngroups = kConsumerWarps / kGroupWarps;
+    int best = 0;
+    double best_eff = -1.0;
+    for (int ns = 1; ns <= 32; ++ns) {
+        if (K % (64 * ns) != 0) continue;
+        const int ks = (int)(K / ns);
+        const int tl = ks / 16, TL = tl < kMaxTiles ? tl : kMaxTiles, cb = (tl + TL - 1) / TL;
+        const int slots = (ngroups < cb ? ngroups : cb) * kGroupWarps;
+        const long long need = 2LL * TL * 768 + (long long)ks * P->MR * P->NB * 2 + 4 * P->NB * P->MR * 32 +
+                               2LL * slots * 4 * P->NB * 512 + 512;
+        if (need > 220 * 1024) continue;
+        int g = kNumSMs / ns;
+        if (g < 1) continue;
+        if (g > P->NA) g = P->NA;
+        const int per = (P->NA + g - 1) / g;
+        double eff = (double)P->NA / ((double)per * g) * ((double)g * ns / kNumSMs);
+        eff -= 0.02 * (ns - 1);  // every extra slab costs a trip through the workspace
+        if (eff > best_eff) {
+            best_eff = eff;
+            best = ns;
+        }
+    }
+    if (best == 0) return AO_ERR_UNSUPPORTED;
+    P->nslabs = best;
+    P->KS = (int)(K / best);
+    P->tiles = P->KS / 16;
+    P->TILES = P->tiles < kMaxTiles ? P->tiles : kMaxTiles;
+    P->cpb = (P->tiles + P->TILES - 1) / P->TILES;
+    P->stage_bytes = P->TILES * 768;
+    int G = kNumSMs / best;
+    if (G > P->NA) G = P->NA;
+    P->G = G;
+    const int xs_bytes = P->KS * P->MR * P->NB * 2;  // per k16 tile: NB * MR*4 lanes * 8 bytes
+    const int zero_bytes = 4 * P->NB * P->MR * 32;
+    const int nslots = (ngroups < P->cpb ? ngroups : P->cpb) * kGroupWarps;
+    int nbuf = (64 * 1024) / (nslots * 4 * P->NB * 512);
+    if (nbuf > kMaxBlockBufs) nbuf = kMaxBlockBufs;
+    if (nbuf < 2) nbuf = 2;
+    int stages = kMaxStages;
+    auto total = [&](int st, int nb_) {
+        return (long long)st * P->stage_bytes + xs_bytes + zero_bytes + (long long)nb_ * nslots * 4 * P->NB * 512 + 512;
+    };
+    while (total(stages, nbuf) > 220 * 1024) {
+        if (stages > 3) --stages;
+        else if (nbuf > 2) --nbuf;
+        else if (stages > 2) --stages;
+        else return AO_ERR_UNSUPPORTED;
+    }
+    P->nbuf = nbuf;
+    const int part_bytes = nbuf * nslots * 4 * P->NB * 512;
+    P->stages = stages;
+    int off = stages * P->stage_bytes;
+    P->xs_off = off;
+    off += xs_bytes;
+    P->zero_off = off;
+    off += zero_bytes;
+    P->part_off = off;
+    off += part_bytes;
+    P->bar_off = off;
+    off += 2 * kMaxStages * 8 + 2 * kMaxBlockBufs * 8;
+    P->smem_bytes = off;
+    P->m4 = 0x0F000F00u;
+    P->mh = 0x90009000u;
+    P->f_hi = 0x00C000C0u;
+    P->f_lo = 0x00300030u;
+    P->k_hi = 0x140u;   // 2^8 + 2^6
+    P->k_lo = 0x500u;   // 2^10 + 2^8
+    P->ws_counters_off = kHeaderBytes;
+    P->ws_slots_off = kHeaderBytes + (size_t)kMaxBlocks * 4;
+    P->ws_bytes = P->ws_slots_off + (best > 1 ? (size_t)best * P->NA * 4 * P->NB * 512 : 0);
+    return AO_OK;
+}
+
+// rows of fragment fr (16 rows) of row block a: store y = acc * 2^12 * scale[row]
+template <int NB>
+__device__ __forceinline__ void store_block(const Plan& P, const float (&v)[4][NB][4], int a, int lane,
+                                            const __half* __restrict__ scale, __half* __restrict__ y) {
+    const int row = lane >> 2, c = lane & 3;
+#pragma unroll
+    for (int fr = 0; fr < 4; ++fr) {
+        const int n0 = a * 64 + fr * 16 + row, n1 = n0 + 8;
+        const float s0 = 4096.f * __half2float(scale[n0]), s1 = 4096.f * __half2float(scale[n1]);
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) {
+            const int m0 = nb * 8 + 2 * c;
+            if (m0 < P.M) {
+                y[(size_t)m0 * P.N + n0] = __float2half_rn(v[fr][nb][0] * s0);
+                y[(size_t)m0 * P.N + n1] = __float2half_rn(v[fr][nb][2] * s1);
+            }
+            if (m0 + 1 < P.M) {
+                y[(size_t)(m0 + 1) * P.N + n0] = __float2half_rn(v[fr][nb][1] * s0);
+                y[(size_t)(m0 + 1) * P.N + n1] = __float2half_rn(v[fr][nb][3] * s1);
+            }
+        }
+    }
+}
+
+template <int NB>
+__device__ __noinline__ void finish_block(const Plan& P, const float (&v)[4][NB][4], int a, int slab, int lane,
+                                          const __half* __restrict__ scale, __half* __restrict__ y,
+                                          uint8_t* __restrict__ ws) {
+    if (P.nslabs == 1) {
+        store_block<NB>(P, v, a, lane, scale, y);
+        return;
+    }
+    float4* slots = reinterpret_cast<float4*>(ws + P.ws_slots_off);
+    const size_t slot_stride = (size_t)4 * NB * 32;  // float4 per slot
+    float4* mine = slots + ((size_t)slab * P.NA + a) * slot_stride;
+#pragma unroll
+    for (int fr = 0; fr < 4; ++fr)
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb)
+            mine[(fr * NB + nb) * 32 + lane] = make_float4(v[fr][nb][0], v[fr][nb][1], v[fr][nb][2], v[fr][nb][3]);
+    __threadfence();
+    __syncwarp();
+    int* counter = reinterpret_cast<int*>(ws + P.ws_counters_off) + a;
+    int old = 0;
+    if (lane == 0) old = atomicAdd(counter, 1);
+    old = __shfl_sync(0xffffffffu, old, 0);
+    if (old + 1 != P.nslabs) return;
+    __threadfence();
+    float sum[4][NB][4];
+#pragma unroll
+    for (int fr = 0; fr < 4; ++fr)
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) sum[fr][nb][i] = 0.f;
+    for (int sl = 0; sl < P.nslabs; ++sl) {
+        const float4* src = slots + ((size_t)sl * P.NA + a) * slot_stride + lane;
+#pragma unroll
+        for (int fr = 0; fr < 4; ++fr)
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb) {
+                const float4 q = ptx::ldcg_f32x4(src + (fr * NB + nb) * 32);
+                sum[fr][nb][0] += q.x; sum[fr][nb][1] += q.y; sum[fr][nb][2] += q.z; sum[fr][nb][3] += q.w;
+            }
+    }
+    store_block<NB>(P, sum, a, lane, scale, y);
+    if (lane == 0) *counter = 0;
+}
+
+// fp16 bit patterns (value / 2^12) of the four A-fragment registers of one 16-row fragment.
+//   w4: the lane's 4-bit word; t: the lane's 2-bit word with this fragment's fields in bits 7..4 of every byte
+__device__ __forceinline__ void decode_fragment(uint32_t w4, uint32_t t, const Plan& P, uint32_t m4, uint32_t mh,
+                                                uint32_t f_hi, uint32_t f_lo, uint32_t k_hi, uint32_t k_lo,
+                                                uint32_t (&a)[4]) {
+    (void)P;
+    const uint32_t v = t >> 8;  // bytes 1, 3 (row e) moved to the place of bytes 0, 2 (row e + 8)
+    // sign -> bit 15, top exponent bit -> bit 12 (both halves), low four bits -> bits 11..8
+    a[0] = ptx::and_or((v & f_hi) * k_hi, mh, (w4 >> 4) & m4);   // row e,     cols 2c, 2c+1
+    a[1] = ptx::and_or((t & f_hi) * k_hi, mh, (w4 << 4) & m4);   // row e + 8, cols 2c, 2c+1
+    a[2] = ptx::and_or((v & f_lo) * k_lo, mh, w4 & m4);          // row e,     cols 2c+8, 2c+9
+    a[3] = ptx::and_or((t & f_lo) * k_lo, mh, (w4 << 8) & m4);   // row e + 8, cols 2c+8, 2c+9
+}
+
+template <int NB, int MR>
+__global__ void __launch_bounds__(kThreads, 1)
+fp6_gemv_kernel(const __half* __restrict__ x, long long ldx, const uint8_t* __restrict__ wq,
+                const __half* __restrict__ scale, __half* __restrict__ y, uint8_t* __restrict__ ws,
+                const __grid_constant__ Plan P) {
+    constexpr int MRL = MR * 4;
+    constexpr int XT = NB * MRL * 8;  // bytes of x fragments per k16 tile
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    constexpr int nwarps = kConsumerWarps, nconsumers = nwarps * 32;
+    const int slab = blockIdx.y, cta = blockIdx.x;
+    const uint32_t smem_base = ptx::smem_addr(smem);
+    const int nstages = P.stages, stage_bytes = P.stage_bytes;
+    const uint32_t full_bar = smem_base + P.bar_off, empty_bar = full_bar + kMaxStages * 8;
+    const uint32_t blk_full_bar = empty_bar + kMaxStages * 8, blk_free_bar = blk_full_bar + kMaxBlockBufs * 8;
+    const int tiles = P.tiles, TILES = P.TILES, cpb = P.cpb;
+    const uint32_t plane4_off = TILES * 256;
+    int* status = reinterpret_cast<int*>(ws);
+
+    const int abeg = static_cast<int>((static_cast<unsigned>(cta) * static_cast<unsigned>(P.NA)) / static_cast<unsigned>(P.G));
+    const int aend = static_cast<int>((static_cast<unsigned>(cta + 1) * static_cast<unsigned>(P.NA)) / static_cast<unsigned>(P.G));
+    const int nstage_total = (aend - abeg) * cpb;
+    constexpr int NG = kConsumerWarps / kGroupWarps;
+    const int ncontrib = min(NG, cpb), nslots = ncontrib * kGroupWarps;
+
+    if (tid == nconsumers) {
+        for (int s = 0; s < nstages; ++s) {
+            ptx::mbar_init(full_bar + 8 * s, 1);
+            ptx::mbar_init(empty_bar + 8 * s, kGroupWarps);
+        }
+        for (int i = 0; i < P.nbuf; ++i) {
+            ptx::mbar_init(blk_full_bar + 8 * i, nslots);
+            ptx::mbar_init(blk_free_bar + 8 * i, 1);
+        }
+        ptx::fence_mbar_init();
+    }
+    __syncthreads();
+
+    if (warp == nwarps) {
+        // =============================== producer warp =================================================
+        // stage = [2-bit plane bytes of the chunk: 256 per k tile][4-bit plane bytes: 512 per k tile]
+        if (lane == 0) {
+            const uint8_t* plane2 = wq;
+            const uint8_t* plane4 = wq + (size_t)P.N * P.K / 4;
+            int ai = 0, c = 0, s = 0;
+            uint32_t phase = 1;
+            bool ok = true;
+            for (int t = 0; t < nstage_total; ++t) {
+                if (!ptx::mbar_wait_bounded(empty_bar + 8 * s, phase, kWaitPolls)) {
+                    ok = false;
+                    break;
+                }
+                const int a = abeg + ai;
+                const int f0 = slab * tiles + c * TILES;             // first k tile, counted over the whole K
+                const int nf = min(TILES, tiles - c * TILES);
+                const size_t tile_index = (size_t)a * (P.K / 16) + f0;
+                const uint32_t dst = smem_base + s * stage_bytes;
+                const uint32_t bar = full_bar + 8 * s;
+                ptx::mbar_arrive_expect_tx(bar, nf * 768u);
+                ptx::bulk_copy_g2s(dst, plane2 + tile_index * 256, nf * 256u, bar);
+                ptx::bulk_copy_g2s(dst + plane4_off, plane4 + tile_index * 512, nf * 512u, bar);
+                if (++c == cpb) {
+                    c = 0;
+                    ++ai;
+                }
+                if (++s == nstages) {
+                    s = 0;
+                    phase ^= 1u;
+                }
+            }
+            if (!ok) atomicExch(status, AO_ERR_TIMEOUT);
+        }
+        return;
+    }
+
+    const float4* parts_ro = reinterpret_cast<const float4*>(smem + P.part_off);
+    if (warp == nwarps + 1) {
+        // =============================== reducer warp ==================================================
+        bool ok = true;
+        for (int ai = 0; ai < aend - abeg; ++ai) {
+            const int buf = ai % P.nbuf;
+            if (!ptx::mbar_wait_bounded(blk_full_bar + 8 * buf, static_cast<uint32_t>(ai / P.nbuf) & 1u, kWaitPolls)) {
+                ok = false;
+                break;
+            }
+            float sum[4][NB][4];
+#pragma unroll
+            for (int fr = 0; fr < 4; ++fr)
+#pragma unroll
+                for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) sum[fr][nb][i] = 0.f;
+            const float4* src = parts_ro + (size_t)(buf * nslots) * (4 * NB * 32) + lane;
+            for (int w = 0; w < nslots; ++w) {
+#pragma unroll
+                for (int fr = 0; fr < 4; ++fr)
+#pragma unroll
+                    for (int nb = 0; nb < NB; ++nb) {
+                        const float4 q = src[(size_t)(w * 4 * NB + fr * NB + nb) * 32];
+                        sum[fr][nb][0] += q.x; sum[fr][nb][1] += q.y; sum[fr][nb][2] += q.z; sum[fr][nb][3] += q.w;
+                    }
+            }
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(blk_free_bar + 8 * buf);
+            finish_block<NB>(P, sum, abeg + ai, slab, lane, scale, y, ws);
+        }
+        if (!ok && lane == 0) atomicExch(status, AO_ERR_TIMEOUT);
+        return;
+    }
+
+    // ================================= consumer warps ==================================================
+    // x slab -> MMA B-fragment order: per k16 tile and lane (batch column m = lane/4, c = lane%4) the words
+    // x[m][k0+2c .. +1] and x[m][k0+2c+8 .. +9]
+    {
+        const int items = tiles * NB * MRL;
+        for (int i = tid; i < 4 * XT / 4; i += nconsumers) reinterpret_cast<uint32_t*>(smem + P.zero_off)[i] = 0u;
+        for (int it = tid; it < items; it += nconsumers) {
+            const int l = it % MRL, blk = it / MRL;
+            const int nb = blk % NB, tile = blk / NB;
+            const int m = nb * 8 + (l >> 2), c = l & 3;
+            uint2 wv = make_uint2(0u, 0u);
+            if (m < P.M) {
+                const int k = slab * P.KS + tile * 16 + 2 * c;
+                const uint32_t* row = reinterpret_cast<const uint32_t*>(x + (long long)m * ldx);
+                wv.x = __ldg(row + (k >> 1));
+                wv.y = __ldg(row + ((k + 8) >> 1));
+            }
+            *reinterpret_cast<uint2*>(smem + P.xs_off + (size_t)it * 8) = wv;
+        }
+        ptx::named_barrier_sync(1, nconsumers);
+    }
+
+    const bool x_lane = lane < MRL;
+    const uint32_t x_base = x_lane ? smem_base + P.xs_off + lane * 8 : smem_base + P.zero_off;
+    const uint32_t x_tile_stride = x_lane ? static_cast<uint32_t>(XT) : 0u;
+    const uint32_t m4 = P.m4, mh = P.mh, f_hi = P.f_hi, f_lo = P.f_lo, k_hi = P.k_hi, k_lo = P.k_lo;
+    float4* parts = reinterpret_cast<float4*>(smem + P.part_off);
+    const int grp = warp / kGroupWarps, wi = warp - grp * kGroupWarps;
+    float acc[4][NB][4];
+#pragma unroll
+    for (int fr = 0; fr < 4; ++fr)
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[fr][nb][i] = 0.f;
+    bool ok = true;
+    for (int ai = 0; ai < aend - abeg && ok; ++ai) {
+        const int first_grp = (ai * cpb) % NG;
+        int ordinal = grp - first_grp;
+        if (ordinal < 0) ordinal += NG;
+        if (ordinal >= ncontrib) continue;
+        for (int c = ordinal; c < cpb; c += NG) {
+            const int t = ai * cpb + c;
+            const int s = t % nstages;
+            const uint32_t phase = static_cast<uint32_t>(t / nstages) & 1u;
+            const int nf = min(TILES, tiles - c * TILES);
+            if (!ptx::mbar_wait_bounded(full_bar + 8 * s, phase, kWaitPolls)) {
+                ok = false;
+                break;
+            }
+            const uint32_t st = smem_base + s * stage_bytes;
+            const int j0 = (wi * nf) / kGroupWarps, j1 = ((wi + 1) * nf) / kGroupWarps;
+#pragma unroll 2
+            for (int j = j0; j < j1; ++j) {
+                const uint32_t p2 = st + j * 256 + lane * 4;
+                const uint32_t p4 = st + plane4_off + j * 512 + lane * 4;
+                const uint32_t xa = x_base + (c * TILES + j) * x_tile_stride;
+                uint2 xb[NB];
+#pragma unroll
+                for (int nb = 0; nb < NB; ++nb) xb[nb] = ptx::lds64(xa + nb * (MRL * 8));
+#pragma unroll
+                for (int b = 0; b < 2; ++b) {
+                    const uint32_t w2 = ptx::lds32(p2 + b * 128);
+#pragma unroll
+                    for (int cc = 0; cc < 2; ++cc) {
+                        const uint32_t w4 = ptx::lds32(p4 + (b * 2 + cc) * 128);
+                        uint32_t a[4];
+                        decode_fragment(w4, cc == 0 ? w2 : (w2 << 4), P, m4, mh, f_hi, f_lo, k_hi, k_lo, a);
+#pragma unroll
+                        for (int nb = 0; nb < NB; ++nb)
+                            ptx::mma_f16_16816(acc[b * 2 + cc][nb], a[0], a[1], a[2], a[3], xb[nb].x, xb[nb].y);
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(empty_bar + 8 * s);
+        }
+        if (!ok) break;
+        const int buf = ai % P.nbuf;
+        if (!ptx::mbar_wait_bounded(blk_free_bar + 8 * buf, (static_cast<uint32_t>(ai / P.nbuf) & 1u) ^ 1u, kWaitPolls)) {
+            ok = false;
+            break;
+        }
+        float4* slot = parts + (size_t)(buf * nslots + ordinal * kGroupWarps + wi) * (4 * NB * 32);
+#pragma unroll
+        for (int fr = 0; fr < 4; ++fr)
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb) {
+                slot[(fr * NB + nb) * 32 + lane] = make_float4(acc[fr][nb][0], acc[fr][nb][1], acc[fr][nb][2], acc[fr][nb][3]);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) acc[fr][nb][i] = 0.f;
+            }
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(blk_full_bar + 8 * buf);
+    }
+    if (!ok && lane == 0) atomicExch(status, AO_ERR_TIMEOUT);
+}
+
+template <int NB, int MR>
+static int launch(const Plan& P, const void* x, long long ldx, const void* wq, const void* scale, void* y, void* ws,
+                  cudaStream_t st) {
+    auto kern = fp6_gemv_kernel<NB, MR>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P.smem_bytes) != cudaSuccess)
+        return AO_ERR_LAUNCH;
+    dim3 grid(P.G, P.nslabs);
+    kern<<<grid, kThreads, P.smem_bytes, st>>>(static_cast<const __half*>(x), ldx, static_cast<const uint8_t*>(wq),
+                                               static_cast<const __half*>(scale), static_cast<__half*>(y),
+                                               static_cast<uint8_t*>(ws), P);
+    return launch_status();
+}
+
+}  // namespace fp6
+}  // namespace ao
+
+using namespace ao;
+
+// A 9..16-row call whose activations and partial sums cannot share one SM's shared memory with the stage ring
+// runs as two calls of at most 8 rows.
+extern "C" size_t ao_fp6_gemv_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+    fp6::Plan P;
+    int rc = fp6::make_plan(M, N, K, &P);
+    if (rc == AO_ERR_UNSUPPORTED && M > 8) {
+        const size_t a = ao_fp6_gemv_workspace_bytes(8, N, K), b = ao_fp6_gemv_workspace_bytes(M - 8, N, K);
+        return a == 0 || b == 0 ? 0 : (a > b ? a : b);
+    }
+    return rc == AO_OK ? P.ws_bytes : 0;
+}
+
+extern "C" int ao_fp6_gemv(const void* x_f16, int64_t x_row_stride, const uint8_t* packed, const void* scale_f16,
+                           int64_t M, int64_t N, int64_t K, void* y_f16, void* workspace, size_t workspace_bytes,
+                           ao_stream_t stream) {
+    if (M == 0 || N == 0) return AO_OK;
+    fp6::Plan P;
+    int rc = fp6::make_plan(M, N, K, &P);
+    if (rc == AO_ERR_UNSUPPORTED && M > 8) {
+        rc = ao_fp6_gemv(x_f16, x_row_stride, packed, scale_f16, 8, N, K, y_f16, workspace, workspace_bytes, stream);
+        if (rc) return rc;
+        return ao_fp6_gemv(static_cast<const __half*>(x_f16) + 8 * x_row_stride, x_row_stride, packed, scale_f16, M - 8, N,
+                           K, static_cast<__half*>(y_f16) + 8 * N, workspace, workspace_bytes, stream);
+    }
+    if (rc) return rc;
+    if (x_row_stride < K || x_row_stride % 2 != 0) return AO_ERR_SHAPE;
+    if (!aligned(x_f16, 4) || !aligned(packed, 16) || !aligned(scale_f16, 2) || !aligned(y_f16, 2) ||
+        !aligned(workspace, 256))
+        return AO_ERR_ALIGN;
+    if (workspace == nullptr || workspace_bytes < P.ws_bytes) return AO_ERR_WORKSPACE;
+    cudaStream_t st = as_stream(stream);
+    if (P.NB == 2) return fp6::launch<2, 8>(P, x_f16, x_row_stride, packed, scale_f16, y_f16, workspace, st);
+    switch (P.MR) {
+        case 1: return fp6::launch<1, 1>(P, x_f16, x_row_stride, packed, scale_f16, y_f16, workspace, st);
+        case 2: return fp6::launch<1, 2>(P, x_f16, x_row_stride, packed, scale_f16, y_f16, workspace, st);
+        case 4: return fp6::launch<1, 4>(P, x_f16, x_row_stride, packed, scale_f16, y_f16, workspace, st);
+        case 8: return fp6::launch<1, 8>(P, x_f16, x_row_stride, packed, scale_f16, y_f16, workspace, st);
+    }
+    return AO_ERR_UNSUPPORTED;
+}
+
+// torchao::quant_llm_linear for e3m2: decode shapes go to the GEMV kernel, larger batches in row blocks of 16.
+extern "C" size_t ao_fp6_linear_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+    if (M <= 16) return ao_fp6_gemv_workspace_bytes(M, N, K);
+    size_t need = 0;  // full 16-row blocks and one ragged block of any height
+    for (int m = 1; m <= 16; m *= 2) {
+        const size_t b = ao_fp6_gemv_workspace_bytes(m, N, K);
+        if (b == 0) return 0;
+        need = b > need ? b : need;
+    }
+    return need;
+}
+
+extern "C" int ao_fp6_linear(const void* x_f16, int64_t x_row_stride, const uint8_t* packed, const void* scale_f16,
+                             int64_t M, int64_t N, int64_t K, void* y_f16, void* workspace, size_t workspace_bytes,
+                             ao_stream_t stream) {
+    if (M < 0 || N < 0) return AO_ERR_SHAPE;
+    if (M <= 16)
+        return ao_fp6_gemv(x_f16, x_row_stride, packed, scale_f16, M, N, K, y_f16, workspace, workspace_bytes, stream);
+    const auto* x = static_cast<const __half*>(x_f16);
+    auto* y = static_cast<__half*>(y_f16);
+    for (int64_t m0 = 0; m0 < M; m0 += 16) {
+        const int64_t mb = M - m0 < 16 ? M - m0 : 16;
+        int rc = ao_fp6_gemv(x + m0 * x_row_stride, x_row_stride, packed, scale_f16, mb, N, K, y + m0 * N, workspace,
+                             workspace_bytes, stream);
+        if (rc) return rc;
+    }
+    return AO_OK;
+}

@@ -20,12 +20,18 @@ int make_plan(int64_t M, int64_t N, int64_t K, int g, int ikt, Plan* P) {
     P->UK = ikt * 16 > g ? ikt * 16 : g;
     P->UB = P->UK * 4;
     P->GPU = P->UK / g;
-    // K slabs: the x fragments of one slab take 2 * KS * MR * NB bytes
-    const int ks_max = kXsmemBudget / (2 * P->MR * P->NB);
+    // K slabs: as few as possible such that the x fragments of one slab (2 * KS * MR * NB bytes), a ring of two
+    // stages and the smallest set of partial-sum buffers still fit in shared memory
     int nslabs = 1;
-    while (!(K % nslabs == 0 && (K / nslabs) % P->UK == 0 && K / nslabs <= ks_max)) {
-        ++nslabs;
+    for (;; ++nslabs) {
         if (nslabs > K / P->UK) return AO_ERR_UNSUPPORTED;
+        if (K % nslabs != 0 || (K / nslabs) % P->UK != 0) continue;
+        const int ks = (int)(K / nslabs);
+        const int subs_ = ks / P->UK, SUBS_ = subs_ < kMaxSubs ? subs_ : kMaxSubs;
+        const int stage_ = ((2 * SUBS_ * P->UB + SUBS_ * P->GPU * 64 + 127) / 128) * 128;
+        const long long need = 2LL * ks * P->MR * P->NB + (P->UK / 32) * P->NB * P->MR * 64 + (ks / g) * P->NB * 32 +
+                               (ks / 32) * P->NB * 32 + 2 * 8 * P->NB * 512 + 512 + 2 * stage_;
+        if (need <= 220 * 1024) break;
     }
     P->nslabs = nslabs;
     P->KS = (int)(K / nslabs);

@@ -35,7 +35,6 @@ constexpr int kMaxThreads = (kMaxConsumerWarps + 2) * 32;  // + the producer war
 constexpr int kMaxStages = 4;
 constexpr int kMaxSubs = 32;             // sub-units per stage
 constexpr int kWaitPolls = 2000;          // suspending polls (<= 0.1 ms each) of one mbarrier phase
-constexpr int kXsmemBudget = 64 * 1024;   // bytes of shared memory for the activation fragments
 constexpr int kHeaderBytes = 256;
 constexpr int kMaxPairs = 16384;          // completion counters live in a fixed region so that calls of
                                           // different shapes can share one workspace

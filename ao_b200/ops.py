@@ -136,3 +136,47 @@ def prepack_fp6_weight(codes: Tensor) -> Tensor:
         rc = _cabi.lib().ao_pack_tc_fp6(_cabi.ptr(codes), M, N, _cabi.ptr(out), _stream(codes))
     _cabi.check(rc, "prepack_fp6_weight")
     return out
+
+
+def quant_llm_linear(EXPONENT: int, MANTISSA: int, _in_feats: Tensor, _weights: Tensor, _scales: Tensor,
+                     splitK: int = 1) -> Tensor:
+    """Quant-LLM linear layer A @ W.T (torchao/ops.py:15-55).  _in_feats fp16 [BS][IC], _weights packed FPx uint8
+    [OC][IC/8*nbits], _scales fp16 [OC] -> fp16 [BS][OC].  Built for e3m2; `splitK` is accepted and ignored (the
+    kernel chooses its own K split)."""
+    torch._check(_in_feats.dim() == 2, lambda: f"input should be a 2d tensor, got {_in_feats.dim()}D")
+    torch._check(_in_feats.dtype is torch.float16, lambda: f"weight must be FP16, got {_in_feats.dtype}")
+    torch._check(_weights.dim() == 2, lambda: f"weight should be a 2d tensor, got {_weights.dim()}D")
+    torch._check(_weights.dtype is torch.uint8, lambda: f"weight must be UINT8, got {_weights.dtype}")
+    torch._check(_scales.dim() == 1, lambda: f"scale should be a 2d tensor, got {_scales.dim()}D")
+    torch._check(_scales.dtype is torch.float16, lambda: f"scale must be FP16, got {_scales.dtype}")
+    BS, IC = _in_feats.shape
+    OC, _ = _weights.shape
+    N_BITS = 1 + EXPONENT + MANTISSA
+    torch._check(IC // 8 * N_BITS == _weights.shape[1], lambda: "Dimensions mismatched")
+    torch._check(OC == _scales.shape[0], lambda: "Dimensions mismatched")
+    if (EXPONENT, MANTISSA) != (3, 2):
+        raise NotImplementedError("quant_llm_linear is built for fp6 e3m2 only")
+    torch._check(IC % 64 == 0, lambda: f"Expect IC to be a multiple of 64, got {IC}")
+    torch._check(OC % 64 == 0, lambda: f"Expect OC to be a multiple of 64, got {OC}")
+    _cabi.require_cuda(_in_feats, _weights, _scales)
+    x = _in_feats if (_in_feats.stride(1) == 1 and _in_feats.stride(0) % 2 == 0 and _in_feats.data_ptr() % 4 == 0) \
+        else _in_feats.contiguous()
+    w = _weights.contiguous()
+    s = _scales.contiguous()
+    y = torch.empty((BS, OC), dtype=torch.float16, device=x.device)
+    if BS == 0:
+        return y
+    lib = _cabi.lib()
+    nbytes = lib.ao_fp6_linear_workspace_bytes(BS, OC, IC)
+    torch._check(nbytes > 0, lambda: f"unsupported fp6 linear shape BS={BS} OC={OC} IC={IC}")
+    with torch.cuda.device(x.device):
+        ws = _cabi.workspace(nbytes, x.device)
+        rc = lib.ao_fp6_linear(_cabi.ptr(x), x.stride(0), _cabi.ptr(w), _cabi.ptr(s), BS, OC, IC, _cabi.ptr(y),
+                               _cabi.ptr(ws), ws.numel(), _stream(x))
+    _cabi.check(rc, "quant_llm_linear")
+    return y
+
+
+def fp6_llm_linear(_in_feats: Tensor, _weights: Tensor, _scales: Tensor, splitK: int = 1) -> Tensor:
+    """The e3m2 case under the name of the earlier torchao release."""
+    return quant_llm_linear(3, 2, _in_feats, _weights, _scales, splitK)

@@ -183,6 +183,23 @@ int ao_int4_gemv(const void* x_bf16, int64_t x_row_stride, int64_t x_cols, const
                  int inner_k_tiles, void* y_bf16, void* workspace, size_t workspace_bytes,
                  ao_stream_t stream);
 
+/* torchao::quant_llm_linear(3, 2, x, w, s, splitK) — torchao/ops.py:15-37, schema
+ * torchao/csrc/fp6_llm.cpp:5-8, CUDA entry torchao/csrc/cuda/fp6_llm/fp6_linear.cu:139-196.
+ * x fp16 [M][K] (row stride x_row_stride), packed uint8 [N][K*6/8] as produced by
+ * ao_pack_tc_fp6 / ao_to_scaled_tc_fp6, scale fp16 [N] -> y fp16 [M][N].  N % 64 == 0,
+ * K % 64 == 0.  The K split is chosen by the kernel (the reference's splitK argument has no
+ * counterpart).  Workspace rules as for ao_int4_tinygemm_linear. */
+size_t ao_fp6_linear_workspace_bytes(int64_t M, int64_t N, int64_t K);
+int ao_fp6_linear(const void* x_f16, int64_t x_row_stride, const uint8_t* packed, const void* scale_f16,
+                  int64_t M, int64_t N, int64_t K, void* y_f16, void* workspace,
+                  size_t workspace_bytes, ao_stream_t stream);
+
+/* The decode kernel alone (1 <= M <= 16). */
+size_t ao_fp6_gemv_workspace_bytes(int64_t M, int64_t N, int64_t K);
+int ao_fp6_gemv(const void* x_f16, int64_t x_row_stride, const uint8_t* packed, const void* scale_f16,
+                int64_t M, int64_t N, int64_t K, void* y_f16, void* workspace, size_t workspace_bytes,
+                ao_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

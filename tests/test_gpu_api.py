@@ -1,0 +1,140 @@
+"""GPU tests of the user-facing API: quantize(m, int4_weight_only(..)), AffineQuantizedTensor and its layouts,
+modelled on test/quantization/test_quant_api.py and test/integration/test_integration.py of the reference."""
+import copy
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as orc
+from tests import gpu_util as tu
+
+pytestmark = pytest.mark.gpu
+
+
+def _sqnr(x, y):
+    x, y = x.detach().float(), y.detach().float()
+    return float(20 * torch.log10(torch.linalg.norm(x) / torch.linalg.norm(x - y)))
+
+
+@pytest.mark.parametrize("group_size", [32, 64, 128, 256])
+@pytest.mark.parametrize("inner_k_tiles", [8, 4, 2])
+def test_quantize_int4_weight_only_linear(group_size, inner_k_tiles):
+    from ao_b200.dtypes import AffineQuantizedTensor, TensorCoreTiledAQTLayout
+    from ao_b200.quantization import int4_weight_only, quantize
+    torch.manual_seed(0)
+    m = torch.nn.Sequential(torch.nn.Linear(1024, 1024, bias=False), torch.nn.Linear(1024, 512, bias=True))
+    m = m.to(device="cuda", dtype=torch.bfloat16)
+    ref = copy.deepcopy(m)
+    out = quantize(m, int4_weight_only(group_size=group_size, inner_k_tiles=inner_k_tiles))
+    assert out is m
+    for lin in m:
+        assert isinstance(lin.weight, AffineQuantizedTensor)
+        assert isinstance(lin.weight.layout_tensor, TensorCoreTiledAQTLayout)
+        assert lin.weight.shape == lin.weight.dequantize().shape
+    x = torch.randn(2, 1024, device="cuda", dtype=torch.bfloat16)
+    y, y_ref = m(x), ref(x)
+    assert y.dtype == torch.bfloat16 and y.shape == y_ref.shape
+    assert _sqnr(y_ref, y) >= 10  # test_integration.py:735-763
+    # quantizing twice does not touch already quantized weights
+    w0 = m[0].weight
+    quantize(m, int4_weight_only(group_size=group_size))
+    assert m[0].weight is w0
+
+
+def test_int4_aqt_matches_oracle_bit_for_bit():
+    from ao_b200.dtypes import to_affine_quantized
+    from ao_b200.quantization import MappingType, ZeroPointDomain
+    w = tu.make_weight((256, 2048), seed=4)
+    aqt = to_affine_quantized(w.cuda(), MappingType.ASYMMETRIC, (1, 64), torch.int32, 0, 15, 1e-6,
+                              zero_point_dtype=torch.bfloat16, preserve_zero=False,
+                              zero_point_domain=ZeroPointDomain.FLOAT, extended_layout="tensor_core_tiled",
+                              inner_k_tiles=8)
+    wf = w.float().numpy()
+    s, z = orc.choose_qparams_affine(wf, orc.BF16, orc.ASYMMETRIC, [1, 64], 0, 15, 1e-6, orc.BF16, orc.BF16, False,
+                                     orc.ZP_FLOAT)
+    q = orc.quantize_affine(wf, orc.BF16, [1, 64], s, orc.BF16, z, orc.BF16, 0, 15, orc.ZP_FLOAT)
+    int_data, scale, zero = aqt.layout_tensor.get_plain()
+    assert np.array_equal(tu.bits(int_data), q)
+    assert np.array_equal(tu.bits(scale), orc.f32_to_bf16_bits(s))
+    assert np.array_equal(tu.bits(zero), orc.f32_to_bf16_bits(z))
+    assert np.array_equal(tu.bits(aqt.layout_tensor.packed_weight), orc.pack_tinygemm(q, 8))
+    dq = orc.dequantize_affine(q, [1, 64], s, orc.BF16, z, orc.BF16, 0, 15, orc.ZP_FLOAT, orc.BF16)
+    assert np.array_equal(tu.bits(aqt.dequantize()), orc.f32_to_bf16_bits(dq))
+    # the fused constructor and the step-by-step route (plain -> from_plain) agree
+    plain = to_affine_quantized(w.cuda(), MappingType.ASYMMETRIC, (1, 64), torch.int32, 0, 15, 1e-6,
+                                zero_point_dtype=torch.bfloat16, preserve_zero=False,
+                                zero_point_domain=ZeroPointDomain.FLOAT)
+    assert torch.equal(plain.layout_tensor.int_data, int_data)
+    assert _sqnr(w.cuda(), aqt.dequantize()) >= 15  # test_integration.py:631-658
+
+
+def test_plain_layout_linear_takes_dequantize_route():
+    """Config "runs on CPU today" of the reference: x @ dequantize_affine(W_q).T, here on the GPU."""
+    from ao_b200.dtypes import to_affine_quantized
+    from ao_b200.quantization import MappingType, ZeroPointDomain
+    w = tu.make_weight((4096, 4096), seed=1234, outliers=False)
+    x = torch.randn(1, 4096, generator=torch.Generator().manual_seed(1234)).bfloat16()
+    aqt = to_affine_quantized(w.cuda(), MappingType.ASYMMETRIC, (1, 64), torch.int32, 0, 15, 1e-6,
+                              zero_point_dtype=torch.bfloat16, preserve_zero=False,
+                              zero_point_domain=ZeroPointDomain.FLOAT)
+    y = torch.nn.functional.linear(x.cuda(), aqt)
+    y_ref = x.cuda().float() @ aqt.dequantize(torch.float32).T
+    assert float((y.float() - y_ref).abs().max() / y_ref.abs().max()) <= 2e-2
+
+
+def test_odd_shapes_are_padded_like_the_reference():
+    from ao_b200.quantization import int4_weight_only, quantize
+    torch.manual_seed(1)
+    lin = torch.nn.Linear(1000, 260, bias=True, device="cuda", dtype=torch.bfloat16)
+    ref = copy.deepcopy(lin)
+    quantize(lin, int4_weight_only(group_size=32))
+    assert tuple(lin.weight.shape) == (260, 1000)
+    assert tuple(lin.weight.layout_tensor.packed_weight.shape) == (264 // 8, 1024 // 128, 32, 4)
+    x = torch.randn(3, 5, 1000, device="cuda", dtype=torch.bfloat16)
+    y = lin(x)
+    assert y.shape == (3, 5, 260)
+    assert _sqnr(ref(x), y) >= 10
+
+
+def test_state_dict_roundtrip_and_flatten():
+    from ao_b200.dtypes import AffineQuantizedTensor
+    from ao_b200.quantization import int4_weight_only, quantize
+    torch.manual_seed(2)
+    m = torch.nn.Sequential(torch.nn.Linear(1024, 256, bias=False)).to(device="cuda", dtype=torch.bfloat16)
+    quantize(m, int4_weight_only(group_size=128))
+    x = torch.randn(4, 1024, device="cuda", dtype=torch.bfloat16)
+    y = m(x)
+    w = m[0].weight
+    names, attrs = w.__tensor_flatten__()
+    assert names == ["layout_tensor"]
+    inner_names, inner_attrs = w.layout_tensor.__tensor_flatten__()
+    assert inner_names == ["packed_weight", "scale_and_zero"]
+    layout2 = type(w.layout_tensor).__tensor_unflatten__(
+        {n: getattr(w.layout_tensor, n).clone() for n in inner_names}, inner_attrs, None, None)
+    w2 = AffineQuantizedTensor.__tensor_unflatten__({"layout_tensor": layout2}, attrs, None, None)
+    m2 = torch.nn.Sequential(torch.nn.Linear(1024, 256, bias=False)).to(device="cuda", dtype=torch.bfloat16)
+    m2[0].weight = torch.nn.Parameter(w2, requires_grad=False)
+    assert torch.equal(m2(x), y)
+    sd = m.state_dict()
+    assert isinstance(sd["0.weight"], AffineQuantizedTensor)
+
+
+def test_int8_weight_only_route():
+    from ao_b200.quantization import int8_weight_only, quantize
+    torch.manual_seed(3)
+    lin = torch.nn.Linear(256, 128, device="cuda", dtype=torch.bfloat16)
+    ref = copy.deepcopy(lin)
+    quantize(lin, int8_weight_only())
+    x = torch.randn(8, 256, device="cuda", dtype=torch.bfloat16)
+    assert _sqnr(ref(x), lin(x)) >= 30
+
+
+def test_filter_fn_and_transpose():
+    from ao_b200.dtypes import AffineQuantizedTensor
+    from ao_b200.quantization import int4_weight_only, quantize
+    m = torch.nn.Sequential(torch.nn.Linear(1024, 64), torch.nn.Linear(64, 1024)).to(device="cuda", dtype=torch.bfloat16)
+    quantize(m, int4_weight_only(group_size=32), filter_fn=lambda mod, fqn: isinstance(mod, torch.nn.Linear) and fqn == "0")
+    assert isinstance(m[0].weight, AffineQuantizedTensor) and not isinstance(m[1].weight, AffineQuantizedTensor)
+    wt = m[0].weight.t()
+    assert wt.shape == (1024, 64)  # test/dtypes/test_affine_quantized.py:12-26

@@ -1,0 +1,102 @@
+"""GPU parity of the FP6 (e3m2) linear: outputs within max|y - y_ref| <= 1e-2 * max|y_ref| of the fp32
+dequant-matmul oracle x.float() @ from_scaled_tc_fpx(w).T, and under the reference's own mean-relative-error bar."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as orc
+from tests import golden_util as gu
+from tests import gpu_util as tu
+
+pytestmark = pytest.mark.gpu
+MAN = gu.manifest()
+TOL = 1e-2
+
+
+def rel_err(y, ref):
+    return float(np.max(np.abs(y - ref)) / max(np.max(np.abs(ref)), 1e-30))
+
+
+@pytest.mark.parametrize("case", MAN["fp6_linear"], ids=lambda c: c["name"])
+def test_fp6_linear_vs_reference_fixture(case):
+    from ao_b200 import _cabi, ops
+    A = gu.load("linear.npz")
+    n = case["name"]
+    packed = tu.to_torch(A[f"{n}/packed"], "u8")
+    scale = tu.to_torch(A[f"{n}/scale"], "f16")
+    for M in case["Ms"]:
+        x = tu.to_torch(A[f"{n}/x_m{M}"], "f16")
+        y = ops.quant_llm_linear(3, 2, x, packed, scale, 1)
+        assert y.shape == (M, case["N"]) and y.dtype == torch.float16
+        assert rel_err(tu.f32(y), A[f"{n}/y_m{M}"]) <= TOL, f"M={M}"
+    assert _cabi.workspace_status("cuda") == 0
+
+
+@pytest.mark.parametrize("shape", [(256, 512), (1088, 1024), (4096, 4096), (4096, 11008)], ids=str)
+def test_fp6_gemv_vs_oracle(shape):
+    from ao_b200 import _cabi, ops
+    from ao_b200.prototype.quant_llm.quant_llm import to_scaled_tc_fpx
+    N, K = shape
+    w = tu.make_weight((N, K), seed=N + K, dtype=torch.float16, outliers=False)
+    packed_ref, scale_ref = orc.to_scaled_tc_fp6(w.float().numpy())
+    wd = orc.from_scaled_tc_fp6(packed_ref, scale_ref)
+    packed, scale = to_scaled_tc_fpx(w.cuda(), 3, 2)
+    assert np.array_equal(tu.bits(packed), packed_ref) and np.array_equal(tu.bits(scale), scale_ref)
+    g = torch.Generator().manual_seed(N)
+    for M in (1, 2, 3, 5, 8, 9, 16):
+        x = torch.randn(M, K, generator=g).half()
+        y_ref = orc.linear_f32(x.float().numpy(), wd)
+        y = ops.fp6_llm_linear(x.cuda(), packed, scale)
+        assert rel_err(tu.f32(y), y_ref) <= TOL, f"M={M}"
+        assert torch.equal(y, ops.fp6_llm_linear(x.cuda(), packed, scale)), "two runs must give identical bits"
+    assert _cabi.workspace_status("cuda") == 0
+
+
+@pytest.mark.parametrize("BS,OC,IC", [(1, 2048, 4096), (2, 8192, 8192), (64, 256, 512)])
+def test_random_bytes_like_the_reference_op_test(BS, OC, IC):
+    """Every byte random, scale and activation in [0.5, 1.5): the reference's test/test_ops.py:24-62 checks
+    mean |err| / mean |y| < 1e-3 against fp16_act @ from_scaled_tc_fpx(w).half().T."""
+    from ao_b200 import ops
+    from ao_b200.prototype.quant_llm.quant_llm import from_scaled_tc_fpx
+    g = torch.Generator().manual_seed(BS + OC)
+    w = torch.randint(256, (OC, IC // 8 * 6), dtype=torch.uint8, generator=g).cuda()
+    scale = (torch.rand(OC, generator=g).half() + 0.5).cuda()
+    act = (torch.rand(BS, IC, generator=g).half() + 0.5).cuda()
+    out = ops.quant_llm_linear(3, 2, act, w, scale, 5)
+    ref = act.float() @ from_scaled_tc_fpx(w, 3, 2, scale).T
+    err = (out.float() - ref).abs().mean() / ref.abs().mean()
+    assert float(err) < 1e-3
+
+
+def test_quant_llm_weight_subclass_linear():
+    from ao_b200.prototype.quant_llm import QuantLlmLinearWeight, fp6_llm_weight_only
+    from ao_b200.quantization import quantize
+    torch.manual_seed(0)
+    lin = torch.nn.Linear(512, 256, bias=True, device="cuda", dtype=torch.float16)
+    ref_w = lin.weight.detach().clone()
+    skip = torch.nn.Linear(100, 256, device="cuda", dtype=torch.float16)  # in_features % 64 != 0: left as is
+    m = torch.nn.Sequential(lin)
+    quantize(m, fp6_llm_weight_only())
+    assert isinstance(m[0].weight, QuantLlmLinearWeight)
+    assert fp6_llm_weight_only()(skip.weight) is skip.weight
+    x = torch.randn(2, 3, 512, device="cuda", dtype=torch.float16)
+    y = m(x)
+    assert y.shape == (2, 3, 256) and y.dtype == torch.float16
+    ref = torch.nn.functional.linear(x.float(), m[0].weight.dequantize(torch.float32), lin.bias.float())
+    assert float((y.float() - ref).abs().max() / ref.abs().max()) <= TOL
+    # fp6 keeps ~2 mantissa bits: the quantized layer stays close to the original one
+    y0 = torch.nn.functional.linear(x, ref_w, lin.bias)
+    assert float(20 * torch.log10(y0.float().norm() / (y0.float() - y.float()).norm())) > 15
+
+
+def test_bad_arguments_raise():
+    from ao_b200 import ops
+    w = torch.zeros(256, 384, dtype=torch.uint8, device="cuda")
+    s = torch.ones(256, dtype=torch.float16, device="cuda")
+    x = torch.zeros(1, 512, dtype=torch.float16, device="cuda")
+    with pytest.raises(RuntimeError, match="weight must be FP16"):
+        ops.quant_llm_linear(3, 2, x.float(), w, s, 1)
+    with pytest.raises(RuntimeError, match="Dimensions mismatched"):
+        ops.quant_llm_linear(3, 2, x, w[:, :100], s, 1)
+    with pytest.raises(NotImplementedError):
+        ops.quant_llm_linear(2, 2, x, torch.zeros(256, 320, dtype=torch.uint8, device="cuda"), s, 1)
