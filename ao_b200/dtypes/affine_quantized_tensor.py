@@ -245,6 +245,8 @@ class PlainAQTLayout(AQTLayout):
             tensor = args[0]
             new = tensor.__class__(tensor.int_data.view(tensor.shape[::-1]), tensor.scale, tensor.zero_point)
             return return_and_correct_aliasing(func, args, kwargs, new)
+        if func is aten.clone.default:
+            return return_and_correct_aliasing(func, args, kwargs, args[0]._apply_fn_to_data(torch.clone))
         raise NotImplementedError(f"PlainAQTLayout dispatch: attempting to run {func}, this is not supported")
 
     __torch_function__ = torch._C._disabled_torch_function_impl
@@ -312,6 +314,10 @@ class TensorCoreTiledAQTLayout(AQTLayout):
         if func is aten.t.default:
             args[0].transposed = not args[0].transposed
             return return_and_correct_aliasing(func, args, kwargs, args[0])
+        if func is aten.clone.default:
+            t = args[0]
+            new = t.__class__(t.packed_weight.clone(), t.scale_and_zero.clone(), t.transposed)
+            return return_and_correct_aliasing(func, args, kwargs, new)
         raise NotImplementedError(
             f"TensorCoreTiledAQTLayout dispatch: attempting to run {func}, this is not supported")
 

@@ -52,10 +52,13 @@ def unpack_int4pack(packed: Tensor) -> Tensor:
     return out
 
 
-def weight_int4pack_mm(x: Tensor, packed: Tensor, group_size: int, scale_and_zero: Tensor, x_cols=None) -> Tensor:
+def weight_int4pack_mm(x: Tensor, packed: Tensor, group_size: int, scale_and_zero: Tensor, x_cols=None, *,
+                       out: Tensor = None, workspace: Tensor = None) -> Tensor:
     """y[M][N] = x[M][K] @ dequant(W)^T for a tensor_core_tiled weight; bf16 in, bf16 out.
 
-    x may have fewer columns than the (padded) weight: the missing ones count as zero."""
+    x may have fewer columns than the (padded) weight: the missing ones count as zero.
+    `out` (bf16 [M][N], contiguous) and `workspace` (uint8, zero-filled once, see int4_workspace_bytes) let a
+    caller that replays the call in a CUDA graph keep every buffer it touches fixed."""
     _cabi.require_cuda(x, packed, scale_and_zero)
     torch._check(x.dim() == 2 and x.dtype == torch.bfloat16, lambda: "x must be a 2-D bfloat16 tensor")
     torch._check(packed.dim() == 4 and packed.dtype == torch.int32 and packed.shape[2] == 32,
@@ -72,19 +75,34 @@ def weight_int4pack_mm(x: Tensor, packed: Tensor, group_size: int, scale_and_zer
         x = torch.nn.functional.pad(x, (0, x.shape[1] % 2)).contiguous()
     packed = packed.contiguous()
     scale_and_zero = scale_and_zero.contiguous()
-    y = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    if out is None:
+        y = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    else:
+        torch._check(out.shape == (M, N) and out.dtype == torch.bfloat16 and out.is_contiguous() and out.device == x.device,
+                     lambda: "out must be a contiguous bfloat16 [M][N] tensor on x's device")
+        y = out
     if M == 0:
         return y
     lib = _cabi.lib()
     nbytes = lib.ao_int4_tinygemm_linear_workspace_bytes(M, N, K, group_size, ikt)
     torch._check(nbytes > 0, lambda: f"unsupported int4 linear shape M={M} N={N} K={K} group={group_size}")
     with torch.cuda.device(x.device):
-        ws = _cabi.workspace(nbytes, x.device)
+        if workspace is None:
+            ws = _cabi.workspace(nbytes, x.device)
+        else:
+            torch._check(workspace.dtype == torch.uint8 and workspace.numel() >= nbytes and workspace.device == x.device,
+                         lambda: f"workspace must be a uint8 tensor of at least {nbytes} bytes on x's device")
+            ws = workspace
         rc = lib.ao_int4_tinygemm_linear(_cabi.ptr(x), x.stride(0), x.shape[1], _cabi.ptr(packed),
                                          _cabi.ptr(scale_and_zero), M, N, K, group_size, ikt, _cabi.ptr(y),
                                          _cabi.ptr(ws), ws.numel(), _stream(x))
     _cabi.check(rc, "weight_int4pack_mm")
     return y
+
+
+def int4_workspace_bytes(M: int, N: int, K: int, group_size: int, inner_k_tiles: int = 8) -> int:
+    """Bytes of zero-initialised scratch weight_int4pack_mm needs for this shape (0: unsupported shape)."""
+    return int(_cabi.lib().ao_int4_tinygemm_linear_workspace_bytes(M, N, K, group_size, inner_k_tiles))
 
 
 def int4_quantize_pack(weight: Tensor, group_size: int, inner_k_tiles: int = 8):

@@ -138,3 +138,15 @@ def test_filter_fn_and_transpose():
     assert isinstance(m[0].weight, AffineQuantizedTensor) and not isinstance(m[1].weight, AffineQuantizedTensor)
     wt = m[0].weight.t()
     assert wt.shape == (1024, 64)  # test/dtypes/test_affine_quantized.py:12-26
+
+
+def test_clone_makes_independent_storage():
+    from ao_b200.quantization import int4_weight_only, quantize
+    lin = torch.nn.Linear(1024, 64, bias=False, device="cuda", dtype=torch.bfloat16)
+    quantize(lin, int4_weight_only(group_size=64))
+    w = lin.weight
+    c = w.clone()
+    assert c.layout_tensor.packed_weight.data_ptr() != w.layout_tensor.packed_weight.data_ptr()
+    assert torch.equal(c.layout_tensor.packed_weight, w.layout_tensor.packed_weight)
+    x = torch.randn(2, 1024, device="cuda", dtype=torch.bfloat16)
+    assert torch.equal(torch.nn.functional.linear(x, c), lin(x))
