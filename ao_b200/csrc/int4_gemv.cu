@@ -51,9 +51,8 @@ int make_plan(int64_t M, int64_t N, int64_t K, int g, int ikt, Plan* P) {
         const int total = xs_bytes + zero_bytes + sx_bytes + p32_bytes + 2 * nwarps * P->NB * 512 + 512 +
                           stages * P->stage_bytes;
         if (total <= 220 * 1024) break;
-        if (stages > 3) --stages;
+        if (stages > 2) stages = 2;   // the ring depth stays a power of two
         else if (nwarps > 8) nwarps -= 8;
-        else if (stages > 2) --stages;
         else return AO_ERR_UNSUPPORTED;
     }
     P->nwarps = nwarps;
@@ -78,10 +77,12 @@ int make_plan(int64_t M, int64_t N, int64_t K, int g, int ikt, Plan* P) {
     // ring of pair buffers: within the budget of two buffers of all warps, at most kMaxPairBufs
     const int NG = nwarps / P->GW;
     const int nslots = (NG < P->cpp ? NG : P->cpp) * P->GW;
-    int nbuf = (2 * nwarps) / nslots;
-    if (nbuf > 8) nbuf = 8;
-    if (nbuf < 2) nbuf = 2;
+    int nbuf = (2 * nwarps) / nslots;  // 2, 4 or more; kept a power of two
+    nbuf = nbuf >= 8 ? 8 : (nbuf >= 4 ? 4 : 2);
     P->nbuf = nbuf;
+    P->nbuf_shift = nbuf == 8 ? 3 : (nbuf == 4 ? 2 : 1);
+    P->gw_shift = P->GW == 16 ? 4 : 3;
+    P->stage_shift = stages == 4 ? 2 : 1;
     P->part_off = off;
     off += nbuf * nslots * P->NB * 512;
     P->bar_off = off;

@@ -50,8 +50,9 @@ struct Plan {
     int G;             // CTAs per slab
     int nwarps;        // consumer warps per CTA (the CTA has one more warp, the producer)
     int GW;            // consumer warps that share one stage (nwarps / GW groups take the stages in turn)
-    int nbuf;          // ring of per-pair partial-sum buffers
-    int stages, stage_bytes;  // ring depth, bytes per stage
+    int nbuf;          // ring of per-pair partial-sum buffers (a power of two)
+    int stages, stage_bytes;  // ring depth (a power of two), bytes per stage
+    int gw_shift, stage_shift, nbuf_shift;  // log2 of GW, stages, nbuf: the per-stage bookkeeping has no divisions
     int xs_off, zero_off, sx_off, p32_off, part_off, bar_off, smem_bytes;
     uint32_t nib_mask, magic;  // 0x000F000F, bf16x2 (128, 128): runtime values so they stay in registers
     size_t ws_counters_off, ws_slots_off, ws_bytes;
@@ -259,7 +260,7 @@ int4_gemv_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int Kx, con
             ptx::mbar_init(full_bar + 8 * s, 33);       // expect_tx arrival + one cp.async arrival per producer lane
             ptx::mbar_init(empty_bar + 8 * s, P.GW);    // one arrival per consumer warp of the stage's group
         }
-        const int nslots_init = min(nwarps / P.GW, cpp) * P.GW;
+        const int nslots_init = min(nwarps >> P.gw_shift, cpp) << P.gw_shift;
         for (int i = 0; i < P.nbuf; ++i) {
             ptx::mbar_init(pair_full_bar + 8 * i, nslots_init);  // one arrival per warp that worked on the pair
             ptx::mbar_init(pair_free_bar + 8 * i, 1);            // the reducer hands the buffer back
@@ -322,13 +323,14 @@ int4_gemv_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int Kx, con
     if (warp == nwarps + 1) {
         // =============================== reducer warp ==================================================
         // adds the consumer warps' partial sums of each finished pair in slot order and stores the rows
-        const int NGr = nwarps / P.GW;
-        const int nslots = min(NGr, cpp) * P.GW, nbuf = P.nbuf;
+        const int NGr = nwarps >> P.gw_shift;
+        const int nslots = min(NGr, cpp) << P.gw_shift;
+        const int nbuf_mask = P.nbuf - 1, nbuf_shift = P.nbuf_shift;
         const float4* parts = reinterpret_cast<const float4*>(smem + P.part_off);
         bool ok = true;
         for (int pi = 0; pi < pend - pbeg; ++pi) {
-            const int buf = pi % nbuf;
-            if (!ptx::mbar_wait_bounded(pair_full_bar + 8 * buf, static_cast<uint32_t>(pi / nbuf) & 1u, kWaitPolls)) {
+            const int buf = pi & nbuf_mask;
+            if (!ptx::mbar_wait_bounded(pair_full_bar + 8 * buf, static_cast<uint32_t>(pi >> nbuf_shift) & 1u, kWaitPolls)) {
                 ok = false;
                 break;
             }
@@ -431,22 +433,23 @@ int4_gemv_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int Kx, con
         for (int i = 0; i < 4; ++i) acc[nb][i] = 0.f;
     // Consumer warps form NG groups of GW warps; the stages of the CTA's stream go to the groups in turn, and
     // inside a group every warp takes a contiguous run of the stage's sub-units (unrolled four at a time).
-    const int GW = P.GW, NG = nwarps / GW;
-    const int grp = warp / GW, wi = warp - grp * GW;
+    // GW, the number of groups NG, the ring depth and the number of pair buffers are powers of two
+    const int gw_shift = P.gw_shift, GW = 1 << gw_shift, NG = nwarps >> gw_shift, ng_mask = NG - 1;
+    const int grp = warp >> gw_shift, wi = warp & (GW - 1);
     const int npairs = pend - pbeg;
     bool ok = true;
     const int ncontrib = min(NG, cpp);           // groups that work on one pair
-    const int nslots = ncontrib * GW;            // warps whose partial sums make up one pair
-    const int nbuf = P.nbuf;                     // pair buffers in the ring
-    for (int pi = 0; pi < npairs && ok; ++pi) {
-        const int first_grp = (pi * cpp) % NG;   // the pair's stages go to groups first_grp, first_grp + 1, ...
-        int ordinal = grp - first_grp;
-        if (ordinal < 0) ordinal += NG;
+    const int nslots = ncontrib << gw_shift;     // warps whose partial sums make up one pair
+    const int stage_mask = nstages - 1, stage_shift = P.stage_shift;
+    const int nbuf_mask = P.nbuf - 1, nbuf_shift = P.nbuf_shift;
+    for (int pi = 0, t0 = 0; pi < npairs && ok; ++pi, t0 += cpp) {
+        // the pair's stages t0 .. t0 + cpp - 1 go to groups t0 % NG, t0 % NG + 1, ...
+        const int ordinal = (grp - t0) & ng_mask;
         if (ordinal >= ncontrib) continue;       // this warp's group has no stage of this pair
         for (int c = ordinal; c < cpp; c += NG) {
-            const int t = pi * cpp + c;
-            const int s = t % nstages;
-            const uint32_t phase = static_cast<uint32_t>(t / nstages) & 1u;
+            const int t = t0 + c;
+            const int s = t & stage_mask;
+            const uint32_t phase = static_cast<uint32_t>(t >> stage_shift) & 1u;
             const int sub0 = c * SUBS;
             const int nsub = min(SUBS, subs - sub0);
             if (!ptx::mbar_wait_bounded(full_bar + 8 * s, phase, kWaitPolls)) {
@@ -454,8 +457,8 @@ int4_gemv_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int Kx, con
                 break;
             }
             const uint32_t st = smem_base + s * stage_bytes;
-            int j = (wi * nsub) / GW;
-            const int jend = ((wi + 1) * nsub) / GW;
+            int j = (wi * nsub) >> gw_shift;
+            const int jend = ((wi + 1) * nsub) >> gw_shift;
             for (; j + 4 <= jend; j += 4)
                 process_units<IKT, NB, MR, G32, 4>(acc, st, j, sub0 + j, tile_b, w_lane, sc_lane, x_base, x_unit_stride,
                                                    sx_base, nib, magic);
@@ -467,13 +470,13 @@ int4_gemv_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int Kx, con
         }
         if (!ok) break;
         // the pair is complete for this warp: leave the partial sums for the reducer warp
-        const int buf = pi % nbuf;
+        const int buf = pi & nbuf_mask;
         // the buffer must have been handed back after the pair that used it before
-        if (!ptx::mbar_wait_bounded(pair_free_bar + 8 * buf, (static_cast<uint32_t>(pi / nbuf) & 1u) ^ 1u, kWaitPolls)) {
+        if (!ptx::mbar_wait_bounded(pair_free_bar + 8 * buf, (static_cast<uint32_t>(pi >> nbuf_shift) & 1u) ^ 1u, kWaitPolls)) {
             ok = false;
             break;
         }
-        float4* slot = parts + (buf * nslots + ordinal * GW + wi) * (NB * 32);
+        float4* slot = parts + (buf * nslots + (ordinal << gw_shift) + wi) * (NB * 32);
 #pragma unroll
         for (int nb = 0; nb < NB; ++nb) {
             slot[nb * 32 + lane] = make_float4(acc[nb][0], acc[nb][1], acc[nb][2], acc[nb][3]);
