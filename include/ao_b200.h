@@ -183,6 +183,20 @@ int ao_int4_gemv(const void* x_bf16, int64_t x_row_stride, int64_t x_cols, const
                  int inner_k_tiles, void* y_bf16, void* workspace, size_t workspace_bytes,
                  ao_stream_t stream);
 
+/* The same GEMV without a workspace argument.  This entry point has no counterpart in the reference.
+ * It is for callers that cannot pass scratch memory and must not allocate (a fixed operator signature,
+ * a C serving loop without a device allocator): the scratch is a device array inside the library, one per
+ * GPU, of ao_int4_gemv_static_scratch_max_bytes() bytes (2 MiB).  Nothing is allocated by the call.
+ *  - The first call on a device performs a one-time set-up (address look-up of the array); make it
+ *    during start-up, before any stream capture.
+ *  - A shape whose ao_int4_gemv_workspace_bytes() exceeds the maximum returns AO_ERR_WORKSPACE.
+ *  - All calls on a device share the array; the call clears the part that has to start at zero on
+ *    `stream` itself, but calls that overlap on the GPU race on it: serialise them, or use ao_int4_gemv. */
+size_t ao_int4_gemv_static_scratch_max_bytes(void);
+int ao_int4_gemv_static_scratch(const void* x_bf16, int64_t x_row_stride, int64_t x_cols,
+                                const int32_t* packed, const void* scale_and_zero, int64_t M, int64_t N,
+                                int64_t K, int group, int inner_k_tiles, void* y_bf16, ao_stream_t stream);
+
 /* torchao::quant_llm_linear(3, 2, x, w, s, splitK) — torchao/ops.py:15-37, schema
  * torchao/csrc/fp6_llm.cpp:5-8, CUDA entry torchao/csrc/cuda/fp6_llm/fp6_linear.cu:139-196.
  * x fp16 [M][K] (row stride x_row_stride), packed uint8 [N][K*6/8] as produced by

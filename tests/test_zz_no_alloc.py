@@ -1,0 +1,56 @@
+"""The workspace-free int4 GEMV entry point (scratch in a device array inside the library), called through the C ABI
+and compared with the regular entry point on the same inputs, two calls in a row."""
+import ctypes
+
+import pytest
+import torch
+
+from tests import gpu_util as tu
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-2
+
+
+def _setup(N, K, g, M, seed):
+    from ao_b200 import ops
+    w = tu.make_weight((N, K), seed=seed).cuda()
+    packed, sz = ops.int4_quantize_pack(w, g, 8)
+    x = torch.randn(M, K, generator=torch.Generator().manual_seed(seed + 1)).bfloat16().cuda()
+    return packed, sz, x
+
+
+def _static(lib, x, packed, sz, M, N, K, g):
+    from ao_b200 import _cabi
+    y = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    rc = lib.ao_int4_gemv_static_scratch(_cabi.ptr(x), x.stride(0), K, _cabi.ptr(packed), _cabi.ptr(sz), M, N, K, g, 8,
+                                         _cabi.ptr(y), _cabi.stream_ptr())
+    return rc, y
+
+
+@pytest.mark.parametrize("N,K,g,M", [(4096, 4096, 64, 1), (1024, 14336, 128, 4), (2048, 4096, 64, 16)])
+def test_static_scratch_matches_regular_entry_point(N, K, g, M):
+    from ao_b200 import _cabi, ops
+    lib = _cabi.lib()
+    packed, sz, x = _setup(N, K, g, M, seed=N + K + M)
+    need = lib.ao_int4_gemv_workspace_bytes(M, N, K, g, 8)
+    assert 0 < need <= lib.ao_int4_gemv_static_scratch_max_bytes()
+    y_ref = ops.weight_int4pack_mm(x, packed, g, sz)
+    for _ in range(2):  # the second call finds the first call's contents in the shared array
+        rc, y = _static(lib, x, packed, sz, M, N, K, g)
+        assert rc == 0, lib.ao_status_string(rc)
+        torch.cuda.synchronize()
+        err = float((y.float() - y_ref.float()).abs().max() / y_ref.float().abs().max())
+        assert err <= TOL
+        assert torch.equal(y, y_ref)  # same kernel, same order of additions
+
+
+def test_static_scratch_rejects_oversized_requests():
+    from ao_b200 import _cabi
+    lib = _cabi.lib()
+    M, N, K, g = 16, 28672, 4096, 64
+    assert lib.ao_int4_gemv_workspace_bytes(M, N, K, g, 8) > lib.ao_int4_gemv_static_scratch_max_bytes()
+    dummy = torch.zeros(16, dtype=torch.int32, device="cuda")
+    rc = lib.ao_int4_gemv_static_scratch(_cabi.ptr(dummy), K, K, _cabi.ptr(dummy), _cabi.ptr(dummy), M, N, K, g, 8,
+                                         _cabi.ptr(dummy), _cabi.stream_ptr())
+    assert rc == 7  # AO_ERR_WORKSPACE
+    assert b"workspace" in lib.ao_status_string(rc).lower()
