@@ -1,5 +1,13 @@
-// Dispatcher of the int4 tensor_core_tiled linear: decode shapes go to the GEMV kernel.
+// Dispatcher of the int4 tensor_core_tiled linear: decode shapes (M <= 16) go to the GEMV kernel, larger
+// batches to the tcgen05 kernel; shapes that kernel does not take run as row blocks of 16 through the GEMV.
 #include "common.cuh"
+
+namespace ao {
+namespace umma {
+int int4_umma_linear(const void* x, int64_t ldx, int64_t x_cols, const int32_t* packed, const void* sz, int64_t M,
+                     int64_t N, int64_t K, int g, int ikt, void* y, void* ws, cudaStream_t st);
+}
+}  // namespace ao
 
 extern "C" size_t ao_int4_tinygemm_linear_workspace_bytes(int64_t M, int64_t N, int64_t K, int group,
                                                           int inner_k_tiles) {
@@ -14,6 +22,12 @@ extern "C" int ao_int4_tinygemm_linear(const void* x_bf16, int64_t x_row_stride,
     if (M <= 16)
         return ao_int4_gemv(x_bf16, x_row_stride, x_cols, packed, scale_and_zero, M, N, K, group, inner_k_tiles, y_bf16,
                             workspace, workspace_bytes, stream);
+    if (workspace == nullptr || workspace_bytes < 256 || !ao::aligned(workspace, 256)) return AO_ERR_WORKSPACE;
+    {
+        const int rc = ao::umma::int4_umma_linear(x_bf16, x_row_stride, x_cols, packed, scale_and_zero, M, N, K, group,
+                                                  inner_k_tiles, y_bf16, workspace, ao::as_stream(stream));
+        if (rc != AO_ERR_UNSUPPORTED) return rc;
+    }
     // row blocks of 16 through the same kernel, back to back on the stream
     const auto* x = static_cast<const __nv_bfloat16*>(x_bf16);
     auto* y = static_cast<__nv_bfloat16*>(y_bf16);
