@@ -4,14 +4,23 @@
 
 namespace ao {
 namespace umma {
+size_t int4_umma_workspace_bytes(int64_t M, int64_t N, int64_t K, int g, int ikt);
 int int4_umma_linear(const void* x, int64_t ldx, int64_t x_cols, const int32_t* packed, const void* sz, int64_t M,
-                     int64_t N, int64_t K, int g, int ikt, void* y, void* ws, cudaStream_t st);
+                     int64_t N, int64_t K, int g, int ikt, void* y, void* ws, size_t ws_bytes, cudaStream_t st);
 }
 }  // namespace ao
 
 extern "C" size_t ao_int4_tinygemm_linear_workspace_bytes(int64_t M, int64_t N, int64_t K, int group,
                                                           int inner_k_tiles) {
-    return ao_int4_gemv_workspace_bytes(M > 16 ? 16 : M, N, K, group, inner_k_tiles);
+    if (M <= 16) return ao_int4_gemv_workspace_bytes(M, N, K, group, inner_k_tiles);
+    // large batches: the tcgen05 kernel's need, and the decode kernel's for shapes that fall back to row blocks
+    size_t need = ao::umma::int4_umma_workspace_bytes(M, N, K, group, inner_k_tiles);
+    for (int m = 1; m <= 16; m *= 2) {
+        const size_t b = ao_int4_gemv_workspace_bytes(m, N, K, group, inner_k_tiles);
+        if (b == 0) return 0;
+        need = b > need ? b : need;
+    }
+    return need;
 }
 
 extern "C" int ao_int4_tinygemm_linear(const void* x_bf16, int64_t x_row_stride, int64_t x_cols,
@@ -25,7 +34,7 @@ extern "C" int ao_int4_tinygemm_linear(const void* x_bf16, int64_t x_row_stride,
     if (workspace == nullptr || workspace_bytes < 256 || !ao::aligned(workspace, 256)) return AO_ERR_WORKSPACE;
     {
         const int rc = ao::umma::int4_umma_linear(x_bf16, x_row_stride, x_cols, packed, scale_and_zero, M, N, K, group,
-                                                  inner_k_tiles, y_bf16, workspace, ao::as_stream(stream));
+                                                  inner_k_tiles, y_bf16, workspace, workspace_bytes, ao::as_stream(stream));
         if (rc != AO_ERR_UNSUPPORTED) return rc;
     }
     // row blocks of 16 through the same kernel, back to back on the stream
