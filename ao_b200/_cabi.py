@@ -61,6 +61,8 @@ PROTOTYPES = {
     "ao_int4_gemv_workspace_bytes": (_size, [_i64, _i64, _i64, _int, _int]),
     "ao_int4_gemv_static_scratch_max_bytes": (_size, []),
     "ao_int4_gemv_static_scratch": (_int, [_ptr, _i64, _i64, _ptr, _ptr, _i64, _i64, _i64, _int, _int, _ptr, _ptr]),
+    "ao_hqq_int4_linear_workspace_bytes": (_size, [_i64, _i64, _i64, _int]),
+    "ao_hqq_int4_linear": (_int, [_ptr, _int, _i64, _ptr, _ptr, _ptr, _i64, _i64, _i64, _int, _ptr, _ptr, _size, _ptr]),
     "ao_fp6_linear_workspace_bytes": (_size, [_i64, _i64, _i64]),
     "ao_fp6_linear": (_int, [_ptr, _i64, _ptr, _ptr, _i64, _i64, _i64, _ptr, _ptr, _size, _ptr]),
     "ao_fp6_gemv_workspace_bytes": (_size, [_i64, _i64, _i64]),

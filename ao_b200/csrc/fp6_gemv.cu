@@ -23,6 +23,7 @@
 // (atomic counter) adds them in slab order.
 #include "common.cuh"
 #include "ptx.cuh"
+#include "fp6_decode.cuh"
 
 namespace ao {
 namespace fp6 {
@@ -203,20 +204,6 @@ __device__ __noinline__ void finish_block(const Plan& P, const float (&v)[4][NB]
     if (lane == 0) *counter = 0;
 }
 
-// fp16 bit patterns (value / 2^12) of the four A-fragment registers of one 16-row fragment.
-//   w4: the lane's 4-bit word; t: the lane's 2-bit word with this fragment's fields in bits 7..4 of every byte
-__device__ __forceinline__ void decode_fragment(uint32_t w4, uint32_t t, const Plan& P, uint32_t m4, uint32_t mh,
-                                                uint32_t f_hi, uint32_t f_lo, uint32_t k_hi, uint32_t k_lo,
-                                                uint32_t (&a)[4]) {
-    (void)P;
-    const uint32_t v = t >> 8;  // bytes 1, 3 (row e) moved to the place of bytes 0, 2 (row e + 8)
-    // sign -> bit 15, top exponent bit -> bit 12 (both halves), low four bits -> bits 11..8
-    a[0] = ptx::and_or((v & f_hi) * k_hi, mh, (w4 >> 4) & m4);   // row e,     cols 2c, 2c+1
-    a[1] = ptx::and_or((t & f_hi) * k_hi, mh, (w4 << 4) & m4);   // row e + 8, cols 2c, 2c+1
-    a[2] = ptx::and_or((v & f_lo) * k_lo, mh, w4 & m4);          // row e,     cols 2c+8, 2c+9
-    a[3] = ptx::and_or((t & f_lo) * k_lo, mh, (w4 << 8) & m4);   // row e + 8, cols 2c+8, 2c+9
-}
-
 template <int NB, int MR>
 __global__ void __launch_bounds__(kThreads, 1)
 fp6_gemv_kernel(const __half* __restrict__ x, long long ldx, const uint8_t* __restrict__ wq,
@@ -394,7 +381,7 @@ fp6_gemv_kernel(const __half* __restrict__ x, long long ldx, const uint8_t* __re
                     for (int cc = 0; cc < 2; ++cc) {
                         const uint32_t w4 = ptx::lds32(p4 + (b * 2 + cc) * 128);
                         uint32_t a[4];
-                        decode_fragment(w4, cc == 0 ? w2 : (w2 << 4), P, m4, mh, f_hi, f_lo, k_hi, k_lo, a);
+                        decode_fragment(w4, cc == 0 ? w2 : (w2 << 4), m4, mh, f_hi, f_lo, k_hi, k_lo, a);
 #pragma unroll
                         for (int nb = 0; nb < NB; ++nb)
                             ptx::mma_f16_16816(acc[b * 2 + cc][nb], a[0], a[1], a[2], a[3], xb[nb].x, xb[nb].y);
@@ -439,6 +426,14 @@ static int launch(const Plan& P, const void* x, long long ldx, const void* wq, c
 }
 
 }  // namespace fp6
+}  // namespace ao
+
+namespace ao {
+namespace umma {
+size_t fp6_umma_workspace_bytes(int64_t M, int64_t N, int64_t K);
+int fp6_umma_linear(const void* x, int64_t ldx, const uint8_t* packed, const void* scale, int64_t M, int64_t N, int64_t K,
+                    void* y, void* ws, size_t ws_bytes, cudaStream_t st);
+}  // namespace umma
 }  // namespace ao
 
 using namespace ao;
@@ -487,7 +482,8 @@ extern "C" int ao_fp6_gemv(const void* x_f16, int64_t x_row_stride, const uint8_
 // torchao::quant_llm_linear for e3m2: decode shapes go to the GEMV kernel, larger batches in row blocks of 16.
 extern "C" size_t ao_fp6_linear_workspace_bytes(int64_t M, int64_t N, int64_t K) {
     if (M <= 16) return ao_fp6_gemv_workspace_bytes(M, N, K);
-    size_t need = 0;  // full 16-row blocks and one ragged block of any height
+    // large batches: the tcgen05 kernel's need, and the decode kernel's for shapes that fall back to row blocks
+    size_t need = umma::fp6_umma_workspace_bytes(M, N, K);
     for (int m = 1; m <= 16; m *= 2) {
         const size_t b = ao_fp6_gemv_workspace_bytes(m, N, K);
         if (b == 0) return 0;
@@ -502,6 +498,12 @@ extern "C" int ao_fp6_linear(const void* x_f16, int64_t x_row_stride, const uint
     if (M < 0 || N < 0) return AO_ERR_SHAPE;
     if (M <= 16)
         return ao_fp6_gemv(x_f16, x_row_stride, packed, scale_f16, M, N, K, y_f16, workspace, workspace_bytes, stream);
+    if (workspace == nullptr || workspace_bytes < 256 || !aligned(workspace, 256)) return AO_ERR_WORKSPACE;
+    {
+        const int rc = umma::fp6_umma_linear(x_f16, x_row_stride, packed, scale_f16, M, N, K, y_f16, workspace,
+                                             workspace_bytes, as_stream(stream));
+        if (rc != AO_ERR_UNSUPPORTED) return rc;
+    }
     const auto* x = static_cast<const __half*>(x_f16);
     auto* y = static_cast<__half*>(y_f16);
     for (int64_t m0 = 0; m0 < M; m0 += 16) {

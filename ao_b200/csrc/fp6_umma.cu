@@ -1,0 +1,106 @@
+// Prefill-shaped FP6 (e3m2) weight-only linear (M > 16) on the tensor-core pre-packed weight of
+// torchao/prototype/quant_llm/quant_llm.py:90-106, replacing torchao::quant_llm_linear
+// (torchao/csrc/cuda/fp6_llm/fp6_linear.cu:139-196) for large batches.  The pipeline is umma_linear.cuh.
+//
+// Raw stage: for each of the CTA's two 64-row blocks, 8 k16 tiles of the 2-bit plane (256 B per tile) and of the
+// 4-bit plane (512 B per tile), four 1-D bulk copies.  Dequant: word t of every 128-byte piece is lane t's
+// m16n8k16 fragment; decode_fragment gives four fp16 registers (value / 2^12) = four 8x8 matrices that one
+// stmatrix writes into the swizzled K-major operand tile.  2^12 * scale[row] is applied to the fp32 accumulator.
+#include "fp6_decode.cuh"
+#include "umma_linear.cuh"
+
+namespace ao {
+namespace umma {
+
+struct Fp6Policy {
+    static constexpr int kTiles = kRawK / 16;              // k16 tiles per raw stage
+    static constexpr int kP2 = kTiles * 256, kP4 = kTiles * 512, kBlk = kP2 + kP4;   // per 64-row block
+    static constexpr int kRawBytes = 2 * kBlk;             // 12 KiB
+    static constexpr bool kBF16 = false;
+    static constexpr bool kAMajorMN = false;
+
+    static __device__ __forceinline__ void issue_raw(const Params& p, uint32_t dst, uint32_t bar, int k0, int n0) {
+        const int nblk = (p.N - n0) >= kRows ? 2 : 1;       // N is a multiple of 64
+        // the 2-bit plane of every 64-row block comes first (N * K / 4 bytes), then the 4-bit plane; inside a plane
+        // the k16 tiles of one block are contiguous
+        const uint8_t* plane2 = static_cast<const uint8_t*>(p.w);
+        const uint8_t* plane4 = plane2 + (size_t)p.N * p.K / 4;
+        ptx::mbar_arrive_expect_tx(bar, nblk * kBlk);
+        for (int b = 0; b < nblk; ++b) {
+            const size_t tile_index = (size_t)(n0 / 64 + b) * (p.K / 16) + k0 / 16;
+            ptx::bulk_copy_g2s(dst + b * kBlk, plane2 + tile_index * 256, kP2, bar);
+            ptx::bulk_copy_g2s(dst + b * kBlk + kP2, plane4 + tile_index * 512, kP4, bar);
+        }
+    }
+
+    // warp dw takes k16 tile dw of the stage, all 128 rows (2 blocks x 4 fragments of 16 rows)
+    static __device__ __forceinline__ void dequant(uint32_t raw, uint32_t a_tiles, int dw, int lane) {
+        const uint32_t m4 = 0x0F000F00u, mh = 0x90009000u, f_hi = 0x00C000C0u, f_lo = 0x00300030u;
+        const uint32_t k_hi = 0x140u, k_lo = 0x500u;
+        const int j = dw;
+        // stmatrix: lane 8i + rr gives row rr of matrix i; matrix i = rows (i & 1) * 8.., k chunk (i >> 1)
+        const int i = lane >> 3, rr = lane & 7;
+        const int chunk = (j & 3) * 2 + (i >> 1);
+        const uint32_t st_lane = ((i & 1) * 8 + rr) * 128 + ((chunk ^ rr) << 4);
+        const uint32_t tile = a_tiles + (j >> 2) * kABytes;
+#pragma unroll
+        for (int blk = 0; blk < 2; ++blk) {
+            const uint32_t p2 = raw + blk * kBlk + j * 256 + lane * 4;
+            const uint32_t p4 = raw + blk * kBlk + kP2 + j * 512 + lane * 4;
+#pragma unroll
+            for (int b = 0; b < 2; ++b) {
+                const uint32_t w2 = ptx::lds32(p2 + b * 128);
+#pragma unroll
+                for (int cc = 0; cc < 2; ++cc) {
+                    const uint32_t w4 = ptx::lds32(p4 + (b * 2 + cc) * 128);
+                    uint32_t a[4];
+                    fp6::decode_fragment(w4, cc == 0 ? w2 : (w2 << 4), m4, mh, f_hi, f_lo, k_hi, k_lo, a);
+                    // fragment registers: a0 (rows e, k 0..7), a1 (rows e + 8, k 0..7), a2 (rows e, k 8..15), a3
+                    ptx::stmatrix_x4(tile + (blk * 64 + (b * 2 + cc) * 16) * 128 + st_lane, a[0], a[1], a[2], a[3]);
+                }
+            }
+        }
+    }
+
+    static __device__ __forceinline__ int out_row(int row) { return row; }
+    static __device__ __forceinline__ float row_scale(const Params& p, int n) {
+        return 4096.f * __half2float(static_cast<const __half*>(p.scale)[n]);
+    }
+};
+
+static bool fp6_shape_ok(int64_t M, int64_t N, int64_t K) {
+    if (M <= 16 || N < kRows || N % 64 != 0 || K % 128 != 0 || K < 128) return false;
+    if (M > (1 << 30) || N > (1 << 30) || K > (1 << 22)) return false;
+    return true;
+}
+
+size_t fp6_umma_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+    Plan P;
+    if (!fp6_shape_ok(M, N, K) || !make_plan(M, N, K, &P)) return 0;
+    return P.ws_bytes;
+}
+
+// AO_ERR_UNSUPPORTED: the caller falls back to row blocks through the decode kernel.
+int fp6_umma_linear(const void* x, int64_t ldx, const uint8_t* packed, const void* scale, int64_t M, int64_t N, int64_t K,
+                    void* y, void* ws, size_t ws_bytes, cudaStream_t st) {
+    Plan P;
+    if (!fp6_shape_ok(M, N, K) || !make_plan(M, N, K, &P)) return AO_ERR_UNSUPPORTED;
+    if (!aligned(x, 16) || (ldx * 2) % 16 != 0 || ldx < K || !aligned(packed, 16)) return AO_ERR_UNSUPPORTED;
+    if (ws == nullptr || ws_bytes < P.ws_bytes || !aligned(ws, 256)) return AO_ERR_WORKSPACE;
+    Params prm{};
+    if (!make_x_map(&prm.map_x, false, x, K, M, ldx, P.MT)) return AO_ERR_LAUNCH;
+    prm.map_w = prm.map_x;   // unused by this format
+    prm.map_s = prm.map_x;
+    prm.map_z = prm.map_x;
+    prm.w = packed;
+    prm.scale = scale;
+    prm.y = y;
+    prm.ws = static_cast<uint8_t*>(ws);
+    prm.M = (int)M;
+    prm.N = (int)N;
+    prm.K = (int)K;
+    return launch_mt<Fp6Policy>(P, prm, st);
+}
+
+}  // namespace umma
+}  // namespace ao

@@ -1,0 +1,153 @@
+// Fused int4 dequant GEMM on the HQQ weight layout (torchao/prototype/hqq/mixed_mm.py:36-173, kernel
+// torchao/prototype/hqq/kernels.py:162-387):  c[M][N] = a[M][K] @ ((q - zeros) * scales)[K][N]
+//   b       uint8 [K/2][N]: row r holds k = 2r in the low nibble and k = 2r + 1 in the high nibble (pack_2xint4)
+//   scales, zeros  [K/g][N] in the activation dtype (bf16 or fp16), one per group of g along K
+// The pipeline is umma_linear.cuh.  The packed bytes run along N, so the dequantised operand tile is MN-major:
+// a thread takes 8 bytes (8 consecutive n of one k pair), reorders the bytes with one prmt so that a masked
+// shift yields (n, n+1) pairs, turns codes into 16-bit floats with one logic op per pair, applies
+// (q - z) * s as q * s - z * s with two fp16x2/bf16x2 FMAs and stores one 16-byte chunk per k.
+#include "umma_linear.cuh"
+
+namespace ao {
+namespace umma {
+
+template <bool BF16>
+__device__ __forceinline__ uint32_t fma2(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    if constexpr (BF16)
+        asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    else
+        asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+template <int GSHIFT, bool BF16>
+struct HqqPolicy {
+    static constexpr int kWBytes = (kRawK / 2) * kRows;   // 64 byte rows x 128 n = 8 KiB
+    static constexpr int kScaleRows = (kRawK >> GSHIFT) > 0 ? (kRawK >> GSHIFT) : 1;
+    static constexpr int kRawBytes = kWBytes + 2048;       // + scales (<= 4 x 256 B) + zeros (<= 4 x 256 B)
+    static constexpr bool kBF16 = BF16;
+    static constexpr bool kAMajorMN = true;
+
+    static __device__ __forceinline__ void issue_raw(const Params& p, uint32_t dst, uint32_t bar, int k0, int n0) {
+        ptx::mbar_arrive_expect_tx(bar, kWBytes + 2 * kScaleRows * 256);
+        ptx::tma_load_2d(dst, &p.map_w, n0, k0 / 2, bar);
+        ptx::tma_load_2d(dst + kWBytes, &p.map_s, n0, k0 >> GSHIFT, bar);
+        ptx::tma_load_2d(dst + kWBytes + 1024, &p.map_z, n0, k0 >> GSHIFT, bar);
+    }
+
+    static __device__ __forceinline__ void dequant(uint32_t raw, uint32_t a_tiles, int dw, int lane) {
+        // 128 + q (bf16) or 1024 + q (fp16), exact; minus the offset gives q
+        const uint32_t nib = 0x000F000Fu;
+        const uint32_t magic = BF16 ? 0x43004300u : 0x64006400u;
+        const uint32_t one2 = BF16 ? 0x3F803F80u : 0x3C003C00u;
+        const uint32_t moff = BF16 ? 0xC300C300u : 0xE400E400u;
+        const int td = dw * 32 + lane;
+        const int c = td & 15;            // 8-byte chunk of the 128 n: n = 8c .. 8c + 7
+        const int r_lo = td >> 4;         // byte row inside a group of 16
+        const uint32_t sc_addr = raw + kWBytes + c * 16;
+        const uint32_t blk_off = (c >> 3) * 8192 + 0;   // 64-wide n block
+        const int cc = c & 7;
+        uint32_t s[4] = {0, 0, 0, 0}, nzs[4] = {0, 0, 0, 0};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int r = q * 16 + r_lo;   // byte row 0..63: k = 2r, 2r + 1 of the 128-k stage
+            if (q == 0 || GSHIFT == 5 || (GSHIFT == 6 && q == 2)) {
+                const int gi = GSHIFT >= 7 ? 0 : (q * 32) >> GSHIFT;
+                const uint4 sv = ptx::lds128(sc_addr + gi * 256);
+                const uint4 zv = ptx::lds128(sc_addr + 1024 + gi * 256);
+                s[0] = sv.x; s[1] = sv.y; s[2] = sv.z; s[3] = sv.w;
+                // -(z * s), rounded once
+                nzs[0] = fma2<BF16>(zv.x, sv.x, 0u) ^ 0x80008000u;
+                nzs[1] = fma2<BF16>(zv.y, sv.y, 0u) ^ 0x80008000u;
+                nzs[2] = fma2<BF16>(zv.z, sv.z, 0u) ^ 0x80008000u;
+                nzs[3] = fma2<BF16>(zv.w, sv.w, 0u) ^ 0x80008000u;
+            }
+            const uint2 wv = ptx::lds64(raw + r * 128 + c * 8);
+            const uint32_t va = __byte_perm(wv.x, wv.x, 0x3120), vb = __byte_perm(wv.y, wv.y, 0x3120);
+            uint32_t lo[4], hi[4];
+            lo[0] = ptx::and_or(va, nib, magic);       hi[0] = ptx::and_or(va >> 4, nib, magic);
+            lo[1] = ptx::and_or(va >> 8, nib, magic);  hi[1] = ptx::and_or(va >> 12, nib, magic);
+            lo[2] = ptx::and_or(vb, nib, magic);       hi[2] = ptx::and_or(vb >> 4, nib, magic);
+            lo[3] = ptx::and_or(vb >> 8, nib, magic);  hi[3] = ptx::and_or(vb >> 12, nib, magic);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                lo[i] = fma2<BF16>(fma2<BF16>(lo[i], one2, moff), s[i], nzs[i]);
+                hi[i] = fma2<BF16>(fma2<BF16>(hi[i], one2, moff), s[i], nzs[i]);
+            }
+            // operand tile of this 64-k block, MN-major: [n block of 64][k group of 8][k % 8][chunk ^ (k % 8)]
+            const int kl = (2 * r) & 63, kg = kl >> 3, kr = kl & 7;
+            const uint32_t t = a_tiles + (r >> 5) * kABytes + blk_off + kg * 1024;
+            ptx::sts128(t + kr * 128 + ((cc ^ kr) << 4), lo[0], lo[1], lo[2], lo[3]);
+            ptx::sts128(t + (kr + 1) * 128 + ((cc ^ (kr + 1)) << 4), hi[0], hi[1], hi[2], hi[3]);
+        }
+    }
+
+    static __device__ __forceinline__ int out_row(int row) { return row; }
+    static __device__ __forceinline__ float row_scale(const Params&, int) { return 1.f; }
+};
+
+template <bool BF16>
+static int launch_g(const Plan& P, int g, const Params& prm, cudaStream_t st) {
+    switch (g) {
+        case 32: return launch_mt<HqqPolicy<5, BF16>>(P, prm, st);
+        case 64: return launch_mt<HqqPolicy<6, BF16>>(P, prm, st);
+        case 128: return launch_mt<HqqPolicy<7, BF16>>(P, prm, st);
+        default: return launch_mt<HqqPolicy<8, BF16>>(P, prm, st);
+    }
+}
+
+static bool hqq_shape_ok(int64_t M, int64_t N, int64_t K, int g) {
+    if (M < 1 || N < kRows || N % 16 != 0 || K % 128 != 0 || K < 128) return false;
+    if (!(g == 32 || g == 64 || g == 128 || g == 256) || K % g != 0) return false;
+    if (M > (1 << 30) || N > (1 << 30) || K > (1 << 24)) return false;
+    return true;
+}
+
+}  // namespace umma
+}  // namespace ao
+
+using namespace ao;
+
+extern "C" size_t ao_hqq_int4_linear_workspace_bytes(int64_t M, int64_t N, int64_t K, int group) {
+    umma::Plan P;
+    if (!umma::hqq_shape_ok(M, N, K, group) || !umma::make_plan(M, N, K, &P)) return 0;
+    return P.ws_bytes;
+}
+
+extern "C" int ao_hqq_int4_linear(const void* a, int a_dtype, int64_t a_row_stride, const uint8_t* b_packed,
+                                  const void* scales, const void* zeros, int64_t M, int64_t N, int64_t K, int group,
+                                  void* c, void* workspace, size_t workspace_bytes, ao_stream_t stream) {
+    if (M == 0 || N == 0) return AO_OK;
+    if (a_dtype != AO_BF16 && a_dtype != AO_F16) return AO_ERR_DTYPE;
+    umma::Plan P;
+    if (!umma::hqq_shape_ok(M, N, K, group)) return AO_ERR_SHAPE;
+    if (!umma::make_plan(M, N, K, &P)) return AO_ERR_UNSUPPORTED;
+    if (!aligned(a, 16) || (a_row_stride * 2) % 16 != 0 || a_row_stride < K || !aligned(b_packed, 16) ||
+        !aligned(scales, 16) || !aligned(zeros, 16) || !aligned(c, 2))
+        return AO_ERR_ALIGN;
+    if (workspace == nullptr || workspace_bytes < P.ws_bytes || !aligned(workspace, 256)) return AO_ERR_WORKSPACE;
+    const bool bf16 = a_dtype == AO_BF16;
+    umma::Params prm{};
+    const uint32_t scale_rows = umma::kRawK / group > 0 ? umma::kRawK / group : 1;
+    const CUtensorMapDataType dt16 = bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    if (!umma::make_x_map(&prm.map_x, bf16, a, K, M, a_row_stride, P.MT)) return AO_ERR_LAUNCH;
+    if (!make_tensor_map_2d(&prm.map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, b_packed, (uint64_t)N, (uint64_t)(K / 2), (uint64_t)N,
+                            umma::kRows, umma::kRawK / 2))
+        return AO_ERR_LAUNCH;
+    if (!make_tensor_map_2d(&prm.map_s, dt16, scales, (uint64_t)N, (uint64_t)(K / group), (uint64_t)N * 2, umma::kRows,
+                            scale_rows))
+        return AO_ERR_LAUNCH;
+    if (!make_tensor_map_2d(&prm.map_z, dt16, zeros, (uint64_t)N, (uint64_t)(K / group), (uint64_t)N * 2, umma::kRows,
+                            scale_rows))
+        return AO_ERR_LAUNCH;
+    prm.w = b_packed;
+    prm.scale = scales;
+    prm.y = c;
+    prm.ws = static_cast<uint8_t*>(workspace);
+    prm.M = (int)M;
+    prm.N = (int)N;
+    prm.K = (int)K;
+    cudaStream_t st = as_stream(stream);
+    return bf16 ? umma::launch_g<true>(P, group, prm, st) : umma::launch_g<false>(P, group, prm, st);
+}

@@ -140,6 +140,9 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
     return v;
 }
+__device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
 __device__ __forceinline__ uint2 lds64(uint32_t addr) {
     uint2 v;
     asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
@@ -247,9 +250,23 @@ __device__ __forceinline__ uint64_t umma_desc_k_sw128(uint32_t smem_addr_bytes) 
     return d;
 }
 
-// Instruction descriptor, kind::f16: fp32 accumulate, bf16 A and B, both K-major, M x N tile
-__host__ __device__ constexpr uint32_t umma_idesc_bf16(int M, int N) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+// The same for an MN-major 16-bit tile (elements of one k contiguous along the M/N dimension): atoms of 64 elements
+// (128 bytes) x 8 k, 1024 bytes each, chunk index XORed with (k % 8); atoms of one 64-element block are 1024 bytes
+// apart along k (stride offset), the next 64-element block starts 8192 bytes later (leading offset: a 64-k tile).
+// Moving 16 elements along K = adding 2048 bytes to the start address.
+__device__ __forceinline__ uint64_t umma_desc_mn_sw128(uint32_t smem_addr_bytes) {
+    uint64_t d = (uint64_t)((smem_addr_bytes & 0x3FFFFu) >> 4);
+    d |= (uint64_t)(8192 >> 4) << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+// Instruction descriptor, kind::f16: fp32 accumulate, A and B both bf16 or both fp16, B K-major, A K- or MN-major
+__host__ __device__ constexpr uint32_t umma_idesc(int M, int N, bool bf16, bool a_mn_major) {
+    return (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | ((a_mn_major ? 1u : 0u) << 15) |
+           ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 
 __device__ __forceinline__ float ldcg_f32(const float* p) {

@@ -1,0 +1,346 @@
+// Skeleton of the prefill-shaped weight-only linears (M > 16) on the 5th-generation tensor cores:
+//   y[M][N] = x[M][K] @ dequant(W)[N][K]^T,   tcgen05.mma with the accumulator in tensor memory.
+//
+// The product is computed transposed: a CTA owns 128 weight rows (the MMA's M dimension, one tensor-memory lane
+// per row) and MT activation rows (the MMA's N dimension, one fp32 column each), and walks K in iterations of
+// 128 = two operand stages of 64.
+//   warp 0     streams the packed weight bytes of its 128 rows x 128 k (and their scales) into a raw ring;
+//   warp 1     streams x tiles [MT][64] with TMA in the 128-byte-swizzle K-major layout the MMA reads;
+//   warp 2     owns the tensor memory and issues the MMAs: four K=16 instructions per operand stage, then a
+//              commit that frees the stage;
+//   warps 3-10 dequantise raw bytes in registers and write the 16-bit operand tile (layout chosen by the weight
+//              format's policy); after the K loop the same warps read the accumulator from tensor memory and
+//              store y.
+// When the tiles alone would leave SMs idle, K is cut into slabs over gridDim.z; fp32 partial tiles meet in the
+// workspace and the CTA that completes a tile (atomic counter) adds them in slab order (deterministic).
+// Every wait is bounded; a wait that runs out sets the status word and the CTA still frees its tensor memory.
+//
+// A weight format plugs in as a Policy:
+//   kRawBytes                      bytes of one raw stage (packed weights + scales of 128 rows x 128 k)
+//   kBF16                          operands are bf16 (else fp16); y has the same type
+//   kAMajorMN                      the dequantised operand tile is MN-major (else K-major), both 128-byte swizzle
+//   issue_raw(p, dst, bar, k0, n0) one thread: expect_tx + the async copies of a raw stage
+//   dequant(raw, a_tiles, dw, lane) 8 warps: raw stage -> two consecutive 16 KiB operand tiles (k 0..63, 64..127)
+//   out_row(lane_row)              weight row (inside the CTA's 128) that tensor-memory lane `lane_row` holds
+//   row_scale(p, n)                factor applied to the accumulator of weight row n
+#pragma once
+#include "common.cuh"
+#include "ptx.cuh"
+#include "tensormap.cuh"
+
+namespace ao {
+namespace umma {
+
+constexpr int kRows = 128;            // weight rows per CTA
+constexpr int kKB = 64;               // k per operand stage (one 128-byte swizzle atom of 16-bit elements)
+constexpr int kRawK = 128;            // k per raw stage / dequant iteration
+constexpr int kABytes = kRows * kKB * 2;       // 16 KiB
+constexpr int kS = 4;                 // operand stages
+constexpr int kDequantWarps = 8;
+constexpr int kThreads = (3 + kDequantWarps) * 32;
+constexpr int kWaitPolls = 2000;
+constexpr int kHeaderBytes = 256;
+constexpr int kMaxTiles = 16384;      // completion counters (same workspace region as the decode kernels')
+constexpr int kMaxSplit = 8;
+constexpr int kSmemLimit = 227 * 1024;
+
+struct alignas(64) Params {
+    CUtensorMap map_x;   // activations [M][K]
+    CUtensorMap map_w;   // packed weights (policy-specific view)
+    CUtensorMap map_s;   // scales (policy-specific view)
+    CUtensorMap map_z;   // zero points (policy-specific view)
+    const void* w;       // raw pointers for policies that copy without tensor maps
+    const void* scale;
+    void* y;
+    uint8_t* ws;
+    int M, N, K;
+};
+
+template <int MT, class Policy>
+struct Cfg {
+    static constexpr int XBytes = MT * kKB * 2;
+    static constexpr int Fixed = 1024 + kS * (kABytes + XBytes) + 256;
+    static constexpr int Rfit = (kSmemLimit - Fixed) / Policy::kRawBytes;
+    static constexpr int R = Rfit > 4 ? 4 : Rfit;         // raw stages
+    static_assert(R >= 2, "raw ring needs two stages");
+    static constexpr int TmemCols = MT < 32 ? 32 : MT;
+    static constexpr int SmemBytes = Fixed + R * Policy::kRawBytes;
+};
+
+// work split of one call
+struct Plan {
+    int MT, nsplit, row_tiles, m_tiles;
+    size_t ws_bytes;
+};
+
+inline bool make_plan(int64_t M, int64_t N, int64_t K, Plan* P) {
+    P->MT = M > 128 ? 256 : (M > 64 ? 128 : (M > 32 ? 64 : 32));
+    P->row_tiles = (int)((N + kRows - 1) / kRows);
+    P->m_tiles = (int)((M + P->MT - 1) / P->MT);
+    const long long tiles = (long long)P->row_tiles * P->m_tiles;
+    if (tiles > kMaxTiles) return false;
+    // K slabs over gridDim.z when the tiles alone leave SMs idle; every slab keeps at least 8 iterations of 128 k
+    int nsplit = (int)(kNumSMs / tiles);
+    const int nit = (int)(K / kRawK);
+    if (nsplit > kMaxSplit) nsplit = kMaxSplit;
+    if (P->MT == 256 && nsplit > 2) nsplit = 2;
+    while (nsplit > 1 && nit / nsplit < 8) --nsplit;
+    if (nsplit < 1) nsplit = 1;
+    P->nsplit = nsplit;
+    P->ws_bytes = kHeaderBytes + (size_t)kMaxTiles * 4 + (nsplit > 1 ? (size_t)tiles * nsplit * kRows * P->MT * 4 : 0);
+    return true;
+}
+
+template <bool BF16>
+__device__ __forceinline__ void store_out(void* y, size_t idx, float v) {
+    if constexpr (BF16)
+        static_cast<__nv_bfloat16*>(y)[idx] = __float2bfloat16_rn(v);
+    else
+        static_cast<__half*>(y)[idx] = __float2half_rn(v);
+}
+
+template <int MT, class Policy>
+__global__ void __launch_bounds__(kThreads, 1) umma_linear_kernel(const __grid_constant__ Params p) {
+    using C = Cfg<MT, Policy>;
+    constexpr int R = C::R;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = ptx::smem_addr(smem_raw);
+    const uint32_t base = (raw_addr + 1023u) & ~1023u;   // operand tiles need 1024-byte alignment
+    uint8_t* sbase = smem_raw + (base - raw_addr);
+    const uint32_t a_base = base, x_base = a_base + kS * kABytes, raw_base = x_base + kS * C::XBytes;
+    const uint32_t bar_base = raw_base + R * Policy::kRawBytes;
+    const uint32_t full_a = bar_base, full_x = full_a + 8 * kS, empty = full_x + 8 * kS;
+    const uint32_t raw_full = empty + 8 * kS, raw_empty = raw_full + 8 * 4, acc_full = raw_empty + 8 * 4;
+    const uint32_t tmem_slot = acc_full + 8, flag_slot = tmem_slot + 4;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int M = p.M, N = p.N;
+    const int n0 = blockIdx.x * kRows, m0 = blockIdx.y * MT;
+    const int nsplit = gridDim.z, z = blockIdx.z;
+    const int nit_all = p.K / kRawK;
+    const int it_begin = (int)(((long long)z * nit_all) / nsplit), it_end = (int)(((long long)(z + 1) * nit_all) / nsplit);
+    const int nit = it_end - it_begin;     // iterations of 128 k for this CTA
+    int* status = reinterpret_cast<int*>(p.ws);
+
+    if (tid == 0) {
+        for (int s = 0; s < kS; ++s) {
+            ptx::mbar_init(full_a + 8 * s, kDequantWarps);
+            ptx::mbar_init(full_x + 8 * s, 1);
+            ptx::mbar_init(empty + 8 * s, 1);
+        }
+        for (int b = 0; b < R; ++b) {
+            ptx::mbar_init(raw_full + 8 * b, 1);
+            ptx::mbar_init(raw_empty + 8 * b, kDequantWarps);
+        }
+        ptx::mbar_init(acc_full, 1);
+        ptx::fence_mbar_init();
+    }
+    if (warp == 2) {
+        ptx::tmem_alloc(tmem_slot, C::TmemCols);
+        ptx::tmem_relinquish_alloc_permit();
+    }
+    ptx::tcgen05_fence_before_thread_sync();
+    __syncthreads();
+    ptx::tcgen05_fence_after_thread_sync();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(sbase + (tmem_slot - base));
+    bool ok = true;
+
+    if (warp == 0) {
+        // ---------------- packed weights and scales: one raw stage per iteration ----------------
+        if (lane == 0) {
+            int rb = 0;
+            uint32_t ph = 1;   // a fresh barrier counts as "previous phase complete"
+            for (int it = 0; it < nit; ++it) {
+                if (!ptx::mbar_wait_bounded(raw_empty + 8 * rb, ph, kWaitPolls)) {
+                    ok = false;
+                    break;
+                }
+                Policy::issue_raw(p, raw_base + rb * Policy::kRawBytes, raw_full + 8 * rb, (it_begin + it) * kRawK, n0);
+                if (++rb == R) {
+                    rb = 0;
+                    ph ^= 1u;
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- activations: one operand stage per 64 k ----------------
+        if (lane == 0) {
+            for (int kb = 0; kb < 2 * nit; ++kb) {
+                const int s = kb & (kS - 1);
+                if (!ptx::mbar_wait_bounded(empty + 8 * s, (static_cast<uint32_t>(kb >> 2) & 1u) ^ 1u, kWaitPolls)) {
+                    ok = false;
+                    break;
+                }
+                ptx::mbar_arrive_expect_tx(full_x + 8 * s, C::XBytes);
+                ptx::tma_load_2d(x_base + s * C::XBytes, &p.map_x, (2 * it_begin + kb) * kKB, m0, full_x + 8 * s);
+            }
+        }
+    } else if (warp == 2) {
+        // ---------------- MMA issue ----------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = ptx::umma_idesc(kRows, MT, Policy::kBF16, Policy::kAMajorMN);
+            constexpr uint32_t a_step = Policy::kAMajorMN ? (2048 >> 4) : (32 >> 4);   // descriptor units per k16
+            for (int kb = 0; kb < 2 * nit; ++kb) {
+                const int s = kb & (kS - 1);
+                const uint32_t ph = static_cast<uint32_t>(kb >> 2) & 1u;
+                if (!ptx::mbar_wait_bounded(full_a + 8 * s, ph, kWaitPolls) ||
+                    !ptx::mbar_wait_bounded(full_x + 8 * s, ph, kWaitPolls)) {
+                    ok = false;
+                    break;
+                }
+                ptx::tcgen05_fence_after_thread_sync();
+                const uint64_t da = Policy::kAMajorMN ? ptx::umma_desc_mn_sw128(a_base + s * kABytes)
+                                                      : ptx::umma_desc_k_sw128(a_base + s * kABytes);
+                const uint64_t db = ptx::umma_desc_k_sw128(x_base + s * C::XBytes);
+#pragma unroll
+                for (int k4 = 0; k4 < kKB / 16; ++k4)
+                    ptx::umma_f16_ss(tmem_base, da + a_step * k4, db + 2 * k4, idesc, (kb | k4) != 0 ? 1u : 0u);
+                ptx::umma_commit(empty + 8 * s);
+            }
+            if (ok) ptx::umma_commit(acc_full);
+        }
+    } else {
+        // ---------------- dequantise (128 rows x 128 k per iteration), then epilogue ----------------
+        const int dw = warp - 3;
+        int rb = 0;
+        uint32_t rph = 0;
+        for (int it = 0; it < nit && ok; ++it) {
+            const int s0 = (2 * it) & (kS - 1);
+            const uint32_t eph = (static_cast<uint32_t>(it >> 1) & 1u) ^ 1u;
+            if (!ptx::mbar_wait_bounded(raw_full + 8 * rb, rph, kWaitPolls) ||
+                !ptx::mbar_wait_bounded(empty + 8 * s0, eph, kWaitPolls) ||
+                !ptx::mbar_wait_bounded(empty + 8 * (s0 + 1), eph, kWaitPolls)) {
+                ok = false;
+                break;
+            }
+            Policy::dequant(raw_base + rb * Policy::kRawBytes, a_base + s0 * kABytes, dw, lane);
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+                ptx::mbar_arrive(full_a + 8 * s0);
+                ptx::mbar_arrive(full_a + 8 * (s0 + 1));
+                ptx::mbar_arrive(raw_empty + 8 * rb);
+            }
+            if (++rb == R) {
+                rb = 0;
+                rph ^= 1u;
+            }
+        }
+        // ---------------- epilogue: lane quarter (warp % 4) x column half (dw / 4) ----------------
+        if (ok && !ptx::mbar_wait_bounded(acc_full, 0u, kWaitPolls)) ok = false;
+        const int q = warp & 3, half = dw >> 2;
+        const int row = q * 32 + lane;              // tensor-memory lane
+        const int n = n0 + Policy::out_row(row);    // the weight row it holds
+        const float rs = n < N ? Policy::row_scale(p, n) : 0.f;
+        constexpr int kColsPerWarp = MT / 2;
+        const int c_begin = half * kColsPerWarp;
+        const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+        if (nsplit == 1) {
+            if (ok) {
+                ptx::tcgen05_fence_after_thread_sync();
+#pragma unroll 1
+                for (int c0 = c_begin; c0 < c_begin + kColsPerWarp; c0 += 16) {
+                    if (m0 + c0 >= M) break;   // uniform across the warp
+                    uint32_t v[16];
+                    ptx::tmem_ld_32x32b_x16(t_lane + c0, v);
+                    ptx::tmem_ld_wait();
+                    if (n < N) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const int m = m0 + c0 + j;
+                            if (m < M) store_out<Policy::kBF16>(p.y, (size_t)m * N + n, __uint_as_float(v[j]) * rs);
+                        }
+                    }
+                }
+            }
+        } else {
+            // K slabs: fp32 partial tile [column][lane] into this slab's workspace slot; the CTA that completes the
+            // tile (atomic counter) adds the slabs in order and stores; the counter is left at zero.
+            const int tile_id = blockIdx.y * gridDim.x + blockIdx.x;
+            float* slots = reinterpret_cast<float*>(p.ws + kHeaderBytes + (size_t)kMaxTiles * 4);
+            const size_t slot_elems = (size_t)kRows * MT;
+            float* mine = slots + ((size_t)tile_id * nsplit + z) * slot_elems;
+            if (ok) {
+                ptx::tcgen05_fence_after_thread_sync();
+#pragma unroll 1
+                for (int c0 = c_begin; c0 < c_begin + kColsPerWarp; c0 += 16) {
+                    if (m0 + c0 >= M) break;
+                    uint32_t v[16];
+                    ptx::tmem_ld_32x32b_x16(t_lane + c0, v);
+                    ptx::tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) mine[(size_t)(c0 + j) * kRows + row] = __uint_as_float(v[j]);
+                }
+            }
+            __threadfence();
+            ptx::named_barrier_sync(1, kDequantWarps * 32);
+            volatile int* flag = reinterpret_cast<volatile int*>(sbase + (flag_slot - base));
+            if (tid == 3 * 32) {
+                int* counter = reinterpret_cast<int*>(p.ws + kHeaderBytes) + tile_id;
+                const int old = atomicAdd(counter, 1);
+                *flag = (old + 1 == nsplit) ? 1 : 0;
+                if (old + 1 == nsplit) *counter = 0;   // every slab has arrived: ready for the next call
+            }
+            ptx::named_barrier_sync(1, kDequantWarps * 32);
+            if (*flag) {
+                __threadfence();
+                const float* tile_slots = slots + (size_t)tile_id * nsplit * slot_elems;
+#pragma unroll 1
+                for (int c0 = c_begin; c0 < c_begin + kColsPerWarp; c0 += 8) {
+                    if (m0 + c0 >= M) break;
+                    float acc[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+                    for (int zz = 0; zz < nsplit; ++zz) {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            acc[j] += ptx::ldcg_f32(tile_slots + (size_t)zz * slot_elems + (size_t)(c0 + j) * kRows + row);
+                    }
+                    if (n < N) {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const int m = m0 + c0 + j;
+                            if (m < M) store_out<Policy::kBF16>(p.y, (size_t)m * N + n, acc[j] * rs);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    if (!ok && lane == 0) atomicExch(status, AO_ERR_TIMEOUT);
+    ptx::tcgen05_fence_before_thread_sync();
+    __syncthreads();
+    if (warp == 2) {
+        ptx::tcgen05_fence_after_thread_sync();
+        ptx::tmem_dealloc(tmem_base, C::TmemCols);
+    }
+}
+
+template <int MT, class Policy>
+int launch(const Plan& P, const Params& prm, cudaStream_t st) {
+    auto kern = umma_linear_kernel<MT, Policy>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<MT, Policy>::SmemBytes) != cudaSuccess)
+        return AO_ERR_LAUNCH;
+    dim3 grid(P.row_tiles, P.m_tiles, P.nsplit);
+    kern<<<grid, kThreads, Cfg<MT, Policy>::SmemBytes, st>>>(prm);
+    return launch_status();
+}
+
+template <class Policy>
+int launch_mt(const Plan& P, const Params& prm, cudaStream_t st) {
+    switch (P.MT) {
+        case 32: return launch<32, Policy>(P, prm, st);
+        case 64: return launch<64, Policy>(P, prm, st);
+        case 128: return launch<128, Policy>(P, prm, st);
+        default: return launch<256, Policy>(P, prm, st);
+    }
+}
+
+// x [M][x_cols] with row stride ldx elements (16-bit), box [64][MT], 128-byte swizzle; rows beyond M and columns
+// beyond x_cols read as zero
+inline bool make_x_map(CUtensorMap* map, bool bf16, const void* x, int64_t x_cols, int64_t M, int64_t ldx, int MT) {
+    return make_tensor_map_2d(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, x,
+                              (uint64_t)x_cols, (uint64_t)M, (uint64_t)ldx * 2, kKB, MT, CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
+}  // namespace umma
+}  // namespace ao

@@ -33,3 +33,50 @@ def pack_hqq_from_rowmajor(codes):
                                                            _cabi.stream_ptr(c.device))
         _cabi.check(rc, "pack_hqq_from_rowmajor")
     return out
+
+
+def mixed_mm(a, b, scales, zeros, group_size, transposed=False, acc_dtype=None, input_precision="ieee",
+             fp8_fast_accum=False, kernel_type="compute_bound", BLOCK_M=None, BLOCK_N=None, BLOCK_K=None):
+    """Fused int4 dequant GEMM, the reference's triton_mixed_mm (torchao/prototype/hqq/mixed_mm.py:36-173):
+    c[M][N] = a[M][K] @ ((unpack(b) - zeros) * scales), fp32 accumulation, c in a's dtype.
+
+    a: bf16 / fp16 [M][K];  b: uint8 [K/2][N] from pack_2xint4;  scales, zeros: [K/group_size][N] in a's dtype
+    (any strides: a transposed view of an [N][K/group_size] tensor is accepted, as the reference's tests pass it).
+    The tuning arguments of the Triton version (acc_dtype, input_precision, fp8_fast_accum, kernel_type, BLOCK_*)
+    are accepted and ignored: the tcgen05 kernel picks its own tiles.  transposed=True (the backward form) is not
+    implemented."""
+    if transposed:
+        raise NotImplementedError("mixed_mm: transposed=True is not implemented")
+    _cabi.require_cuda(a, b, scales, zeros)
+    assert b.dtype == torch.int8 or b.dtype == torch.uint8, "b must be int8 or uint8"
+    assert a.dim() == 2 and b.dim() == 2 and scales.ndim == 2
+    assert a.shape[1] == b.shape[0] * 2, "incompatible dimensions"
+    assert scales.dtype == a.dtype
+    assert scales.shape == zeros.shape
+    assert zeros.dtype == a.dtype
+    torch._check(a.dtype in (torch.bfloat16, torch.float16), lambda: "mixed_mm: a must be bfloat16 or float16")
+    M, K = a.shape
+    N = b.shape[1]
+    torch._check(scales.shape == (K // group_size, N),
+                 lambda: f"scales must be [K/group_size][N] = {(K // group_size, N)}, got {tuple(scales.shape)}")
+    if a.stride(1) != 1 or a.stride(0) % 8 != 0 or a.data_ptr() % 16 != 0:
+        a = a.contiguous()
+    b = b.contiguous()
+    scales = scales.contiguous()
+    zeros = zeros.contiguous()
+    c = torch.empty((M, N), device=a.device, dtype=a.dtype)
+    if M == 0:
+        return c
+    lib = _cabi.lib()
+    nbytes = lib.ao_hqq_int4_linear_workspace_bytes(M, N, K, group_size)
+    torch._check(nbytes > 0, lambda: f"mixed_mm: unsupported shape M={M} N={N} K={K} group_size={group_size}")
+    with torch.cuda.device(a.device):
+        ws = _cabi.workspace(nbytes, a.device)
+        rc = lib.ao_hqq_int4_linear(_cabi.ptr(a), _cabi.dtype_code(a.dtype), a.stride(0), _cabi.ptr(b), _cabi.ptr(scales),
+                                    _cabi.ptr(zeros), M, N, K, group_size, _cabi.ptr(c), _cabi.ptr(ws), ws.numel(),
+                                    _cabi.stream_ptr(a.device))
+    _cabi.check(rc, "mixed_mm")
+    return c
+
+
+triton_mixed_mm = mixed_mm  # the reference's name for this operator

@@ -162,7 +162,8 @@ int ao_from_scaled_tc_fp6(const uint8_t* packed, int64_t M, int64_t N, const voi
  * stands in for the reference's per-call zero padding of the activation to the padded K,
  * affine_quantized_tensor.py:625-627), packed int32 tensor_core_tiled (inner_k_tiles 8/4/2),
  * scale_and_zero bf16 [K/group][N][2] -> y bf16 [M][N] contiguous.
- * M <= 16 runs the HBM-bound split-K GEMV kernel; larger M is processed in row blocks.
+ * M <= 16 runs the HBM-bound GEMV kernel; larger M the tcgen05 kernel (inner_k_tiles 8, N >= 128, 16-byte
+ * aligned activation rows), anything else is processed in row blocks of 16 by the GEMV kernel.
  *
  * Workspace: ao_int4_tinygemm_linear_workspace_bytes(...) bytes, 256-byte aligned.  It holds a
  * status word (int at offset 0: AO_OK, or the code of a device-side failure such as a copy
@@ -196,6 +197,17 @@ size_t ao_int4_gemv_static_scratch_max_bytes(void);
 int ao_int4_gemv_static_scratch(const void* x_bf16, int64_t x_row_stride, int64_t x_cols,
                                 const int32_t* packed, const void* scale_and_zero, int64_t M, int64_t N,
                                 int64_t K, int group, int inner_k_tiles, void* y_bf16, ao_stream_t stream);
+
+/* triton_mixed_mm(a, b, scales, zeros, group_size) — torchao/prototype/hqq/mixed_mm.py:36-173 with the kernel
+ * torchao/prototype/hqq/kernels.py:162-387 (non-transposed form): c[M][N] = a[M][K] @ ((q - zeros) * scales)[K][N].
+ * a: bf16 or fp16 (a_dtype = AO_BF16 / AO_F16) [M][K], row stride a_row_stride elements; b_packed uint8 [K/2][N]
+ * as produced by ao_pack_2xint4 on the [K][N] codes; scales, zeros [K/group][N] contiguous in a's dtype;
+ * c [M][N] contiguous in a's dtype.  N % 16 == 0, N >= 128, K % 128 == 0, group in {32, 64, 128, 256}, any M >= 1.
+ * Runs on the tcgen05 tensor cores (fp32 accumulate).  Workspace rules as for ao_int4_tinygemm_linear. */
+size_t ao_hqq_int4_linear_workspace_bytes(int64_t M, int64_t N, int64_t K, int group);
+int ao_hqq_int4_linear(const void* a, int a_dtype, int64_t a_row_stride, const uint8_t* b_packed,
+                       const void* scales, const void* zeros, int64_t M, int64_t N, int64_t K, int group,
+                       void* c, void* workspace, size_t workspace_bytes, ao_stream_t stream);
 
 /* torchao::quant_llm_linear(3, 2, x, w, s, splitK) — torchao/ops.py:15-37, schema
  * torchao/csrc/fp6_llm.cpp:5-8, CUDA entry torchao/csrc/cuda/fp6_llm/fp6_linear.cu:139-196.

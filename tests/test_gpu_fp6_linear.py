@@ -80,12 +80,12 @@ def test_quant_llm_weight_subclass_linear():
     assert isinstance(m[0].weight, QuantLlmLinearWeight)
     assert fp6_llm_weight_only()(skip.weight) is skip.weight
     x = torch.randn(2, 3, 512, device="cuda", dtype=torch.float16)
-    y = m(x)
+    y = m(x).detach()
     assert y.shape == (2, 3, 256) and y.dtype == torch.float16
-    ref = torch.nn.functional.linear(x.float(), m[0].weight.dequantize(torch.float32), lin.bias.float())
+    ref = torch.nn.functional.linear(x.float(), m[0].weight.detach().dequantize(torch.float32), lin.bias.detach().float())
     assert float((y.float() - ref).abs().max() / ref.abs().max()) <= TOL
     # fp6 keeps ~2 mantissa bits: the quantized layer stays close to the original one
-    y0 = torch.nn.functional.linear(x, ref_w, lin.bias)
+    y0 = torch.nn.functional.linear(x, ref_w, lin.bias.detach())
     assert float(20 * torch.log10(y0.float().norm() / (y0.float() - y.float()).norm())) > 15
 
 
@@ -100,3 +100,23 @@ def test_bad_arguments_raise():
         ops.quant_llm_linear(3, 2, x, w[:, :100], s, 1)
     with pytest.raises(NotImplementedError):
         ops.quant_llm_linear(2, 2, x, torch.zeros(256, 320, dtype=torch.uint8, device="cuda"), s, 1)
+
+
+@pytest.mark.parametrize("N,K", [(256, 512), (1024, 4096), (4096, 1024)])
+def test_fp6_prefill_vs_oracle(N, K):
+    """M > 16 runs the tcgen05 kernel."""
+    from ao_b200 import _cabi, ops
+    from ao_b200.prototype.quant_llm.quant_llm import to_scaled_tc_fpx
+    w = tu.make_weight((N, K), seed=N + 3 * K, dtype=torch.float16, outliers=False)
+    packed_ref, scale_ref = orc.to_scaled_tc_fp6(w.float().numpy())
+    wd = orc.from_scaled_tc_fp6(packed_ref, scale_ref)
+    packed, scale = to_scaled_tc_fpx(w.cuda(), 3, 2)
+    g = torch.Generator().manual_seed(K)
+    for M in (17, 64, 100, 128, 256, 300):
+        x = torch.randn(M, K, generator=g).half()
+        y_ref = orc.linear_f32(x.float().numpy(), wd)
+        y = ops.fp6_llm_linear(x.cuda(), packed, scale)
+        assert y.shape == (M, N) and y.dtype == torch.float16
+        assert rel_err(tu.f32(y), y_ref) <= TOL, f"M={M}"
+        assert torch.equal(y, ops.fp6_llm_linear(x.cuda(), packed, scale))
+    assert _cabi.workspace_status("cuda") == 0
