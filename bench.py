@@ -245,6 +245,15 @@ class GpuLayerSet:
         return int(self.ws[:4].view(torch.int32).item())
 
 
+def _note(msg):
+    """Progress line on stderr (BENCH_VERBOSE=1): where a multi-rank run is when something stalls."""
+    if os.environ.get("BENCH_VERBOSE"):
+        print(f"[bench rank {os.environ.get('RANK', '0')} +{time.perf_counter() - _T0:.1f}s] {msg}", file=sys.stderr, flush=True)
+
+
+_T0 = time.perf_counter()
+
+
 def run_ours(args):
     import torch.distributed as dist
     from ao_b200 import _cabi
@@ -259,9 +268,12 @@ def run_ours(args):
     device = torch.device("cuda", local_rank)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=device)
+        import datetime
+        dist.init_process_group("nccl", device_id=device, timeout=datetime.timedelta(seconds=90))
     M, g, copies = args.m, args.group, args.copies
+    _note("process group ready; building the layer set")
     ls = GpuLayerSet(M, g, copies, device, rank)
+    _note("layer set ready")
 
     gather = None
     if world > 1:
@@ -279,6 +291,7 @@ def run_ours(args):
     for c in range(copies):
         ls.kernels_only(c, gather)
     torch.cuda.synchronize()
+    _note("eager warm-up done")
     graphs = None
     if not args.no_graph:
         try:
@@ -299,6 +312,7 @@ def run_ours(args):
         else:
             ls.kernels_only(i % copies, gather)
 
+    _note(f"graphs captured: {graphs is not None}")
     for i in range(max(args.warmup, 3)):
         one_step(i)
     sampler = ClockSampler(local_rank)
@@ -313,12 +327,15 @@ def run_ours(args):
     stop.record()
     barrier()
     ms = start.elapsed_time(stop)
-    # keep the GPU under the same load a little longer so that nvidia-smi sees it (not part of the number)
-    t_end = time.perf_counter() + 0.5
-    while time.perf_counter() < t_end:
-        for i in range(200):
-            one_step(i)
-        torch.cuda.synchronize()
+    _note(f"timed region done: {ms:.3f} ms")
+    # keep the GPU under the same load a little longer so that nvidia-smi sees it (not part of the number); a fixed
+    # count, so that every rank issues the same collectives
+    for i in range(6000):
+        one_step(i)
+        if i % 500 == 499:
+            torch.cuda.synchronize()
+    torch.cuda.synchronize()
+    _note("load loop done")
     clocks = sampler.stop() if rank == 0 else None
     if ls.status() != 0:
         raise RuntimeError(f"kernel status word {ls.status()} (a bounded wait ran out)")
@@ -333,6 +350,7 @@ def run_ours(args):
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
     barrier()
+    _note("end-to-end region done")
 
     times = torch.tensor([ms, e2e_s * 1e3], dtype=torch.float64, device=device)
     if world > 1:
@@ -373,7 +391,24 @@ def run_ours(args):
             line["cpu_baseline"] = None
         print(json.dumps(line), flush=True)
     if world > 1:
+        # orderly shutdown: drop the captured graphs (they reference the communicator's kernels), drain the device,
+        # meet at a barrier, then destroy the group; a timer ends the process if the teardown itself stalls (the
+        # result line is already out)
+        import gc
+        import threading
+        sys.stdout.flush()
+        killer = threading.Timer(10.0, lambda: os._exit(0))
+        killer.daemon = True
+        killer.start()
+        graphs = None
+        gc.collect()
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        _note("destroying the process group")
         dist.destroy_process_group()
+        _note("process group destroyed")
+        killer.cancel()
 
 
 # DRAM bytes (read + written) per launch of int4_gemv_kernel averaged over the layer set, from the ncu capture
