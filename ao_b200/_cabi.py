@@ -142,15 +142,24 @@ _workspaces = {}
 
 
 def workspace(nbytes, device):
-    """A zero-initialised scratch buffer of at least nbytes for the current stream of `device`."""
+    """A zero-initialised scratch buffer of at least nbytes for the current stream of `device`.
+
+    While a CUDA graph is being captured the capture stream has no buffer yet; allocating one there would put its
+    zero fill into the graph.  The buffer of a warm-up call on this device (any stream) is used instead when it is
+    large enough: replays of the graph then must not overlap with eager calls that use the same buffer."""
     device = torch.device(device)
-    key = (device.index if device.index is not None else torch.cuda.current_device(),
-           torch.cuda.current_stream(device).cuda_stream)
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    key = (index, torch.cuda.current_stream(device).cuda_stream)
     buf = _workspaces.get(key)
-    if buf is None or buf.numel() < nbytes:
-        size = max(int(nbytes), 1 << 20)
-        buf = torch.zeros(size, dtype=torch.uint8, device=device)
-        _workspaces[key] = buf
+    if buf is not None and buf.numel() >= nbytes:
+        return buf
+    if torch.cuda.is_current_stream_capturing():
+        for (idx, _), other in _workspaces.items():
+            if idx == index and other.numel() >= nbytes:
+                return other
+    size = max(int(nbytes), 1 << 20)
+    buf = torch.zeros(size, dtype=torch.uint8, device=device)
+    _workspaces[key] = buf
     return buf
 
 

@@ -46,7 +46,8 @@ struct Plan {
     int TILES, cpb;    // k16 tiles per full stage, stages (K chunks) per row block
     int G;             // CTAs per slab
     int stages, stage_bytes;
-    int nbuf;          // ring of per-row-block partial-sum buffers
+    int nbuf;          // ring of per-row-block partial-sum buffers (a power of two)
+    int stage_shift, nbuf_shift;  // log2 of stages and nbuf: no divisions in the per-stage bookkeeping
     int xs_off, zero_off, part_off, bar_off, smem_bytes;
     uint32_t m4, mh, f_hi, f_lo, k_hi, k_lo;  // masks / multipliers as runtime values (kept in registers)
     size_t ws_counters_off, ws_slots_off, ws_bytes;
@@ -104,13 +105,15 @@ static int make_plan(int64_t M, int64_t N, int64_t K, Plan* P) {
     auto total = [&](int st, int nb_) {
         return (long long)st * P->stage_bytes + xs_bytes + zero_bytes + (long long)nb_ * nslots * 4 * P->NB * 512 + 512;
     };
+    nbuf = nbuf >= 4 ? 4 : 2;
     while (total(stages, nbuf) > 220 * 1024) {
-        if (stages > 3) --stages;
-        else if (nbuf > 2) --nbuf;
-        else if (stages > 2) --stages;
+        if (nbuf > 2) nbuf = 2;
+        else if (stages > 2) stages = 2;
         else return AO_ERR_UNSUPPORTED;
     }
     P->nbuf = nbuf;
+    P->nbuf_shift = nbuf == 4 ? 2 : 1;
+    P->stage_shift = stages == 4 ? 2 : 1;
     const int part_bytes = nbuf * nslots * 4 * P->NB * 512;
     P->stages = stages;
     int off = stages * P->stage_bytes;
@@ -284,8 +287,8 @@ fp6_gemv_kernel(const __half* __restrict__ x, long long ldx, const uint8_t* __re
         // =============================== reducer warp ==================================================
         bool ok = true;
         for (int ai = 0; ai < aend - abeg; ++ai) {
-            const int buf = ai % P.nbuf;
-            if (!ptx::mbar_wait_bounded(blk_full_bar + 8 * buf, static_cast<uint32_t>(ai / P.nbuf) & 1u, kWaitPolls)) {
+            const int buf = ai & (P.nbuf - 1);
+            if (!ptx::mbar_wait_bounded(blk_full_bar + 8 * buf, static_cast<uint32_t>(ai >> P.nbuf_shift) & 1u, kWaitPolls)) {
                 ok = false;
                 break;
             }
@@ -357,8 +360,8 @@ fp6_gemv_kernel(const __half* __restrict__ x, long long ldx, const uint8_t* __re
         if (ordinal >= ncontrib) continue;
         for (int c = ordinal; c < cpb; c += NG) {
             const int t = ai * cpb + c;
-            const int s = t % nstages;
-            const uint32_t phase = static_cast<uint32_t>(t / nstages) & 1u;
+            const int s = t & (nstages - 1);
+            const uint32_t phase = static_cast<uint32_t>(t >> P.stage_shift) & 1u;
             const int nf = min(TILES, tiles - c * TILES);
             if (!ptx::mbar_wait_bounded(full_bar + 8 * s, phase, kWaitPolls)) {
                 ok = false;
@@ -392,8 +395,8 @@ fp6_gemv_kernel(const __half* __restrict__ x, long long ldx, const uint8_t* __re
             if (lane == 0) ptx::mbar_arrive(empty_bar + 8 * s);
         }
         if (!ok) break;
-        const int buf = ai % P.nbuf;
-        if (!ptx::mbar_wait_bounded(blk_free_bar + 8 * buf, (static_cast<uint32_t>(ai / P.nbuf) & 1u) ^ 1u, kWaitPolls)) {
+        const int buf = ai & (P.nbuf - 1);
+        if (!ptx::mbar_wait_bounded(blk_free_bar + 8 * buf, (static_cast<uint32_t>(ai >> P.nbuf_shift) & 1u) ^ 1u, kWaitPolls)) {
             ok = false;
             break;
         }
@@ -481,8 +484,8 @@ extern "C" int ao_fp6_gemv(const void* x_f16, int64_t x_row_stride, const uint8_
 
 // torchao::quant_llm_linear for e3m2: decode shapes go to the GEMV kernel, larger batches in row blocks of 16.
 extern "C" size_t ao_fp6_linear_workspace_bytes(int64_t M, int64_t N, int64_t K) {
-    if (M <= 16) return ao_fp6_gemv_workspace_bytes(M, N, K);
-    // large batches: the tcgen05 kernel's need, and the decode kernel's for shapes that fall back to row blocks
+    if (M <= 8) return ao_fp6_gemv_workspace_bytes(M, N, K);
+    // larger batches: the tcgen05 kernel's need, and the decode kernel's for shapes that fall back to row blocks
     size_t need = umma::fp6_umma_workspace_bytes(M, N, K);
     for (int m = 1; m <= 16; m *= 2) {
         const size_t b = ao_fp6_gemv_workspace_bytes(m, N, K);
@@ -496,7 +499,7 @@ extern "C" int ao_fp6_linear(const void* x_f16, int64_t x_row_stride, const uint
                              int64_t M, int64_t N, int64_t K, void* y_f16, void* workspace, size_t workspace_bytes,
                              ao_stream_t stream) {
     if (M < 0 || N < 0) return AO_ERR_SHAPE;
-    if (M <= 16)
+    if (M <= 8)
         return ao_fp6_gemv(x_f16, x_row_stride, packed, scale_f16, M, N, K, y_f16, workspace, workspace_bytes, stream);
     if (workspace == nullptr || workspace_bytes < 256 || !aligned(workspace, 256)) return AO_ERR_WORKSPACE;
     {
@@ -504,6 +507,8 @@ extern "C" int ao_fp6_linear(const void* x_f16, int64_t x_row_stride, const uint
                                              workspace_bytes, as_stream(stream));
         if (rc != AO_ERR_UNSUPPORTED) return rc;
     }
+    if (M <= 16)
+        return ao_fp6_gemv(x_f16, x_row_stride, packed, scale_f16, M, N, K, y_f16, workspace, workspace_bytes, stream);
     const auto* x = static_cast<const __half*>(x_f16);
     auto* y = static_cast<__half*>(y_f16);
     for (int64_t m0 = 0; m0 < M; m0 += 16) {

@@ -1,4 +1,4 @@
-// Prefill-shaped FP6 (e3m2) weight-only linear (M > 16) on the tensor-core pre-packed weight of
+// Prefill-shaped FP6 (e3m2) weight-only linear (M > 8) on the tensor-core pre-packed weight of
 // torchao/prototype/quant_llm/quant_llm.py:90-106, replacing torchao::quant_llm_linear
 // (torchao/csrc/cuda/fp6_llm/fp6_linear.cu:139-196) for large batches.  The pipeline is umma_linear.cuh.
 //
@@ -69,7 +69,7 @@ struct Fp6Policy {
 };
 
 static bool fp6_shape_ok(int64_t M, int64_t N, int64_t K) {
-    if (M <= 16 || N < kRows || N % 64 != 0 || K % 128 != 0 || K < 128) return false;
+    if (M <= 8 || N < kRows || N % 64 != 0 || K % 128 != 0 || K < 128) return false;
     if (M > (1 << 30) || N > (1 << 30) || K > (1 << 22)) return false;
     return true;
 }

@@ -1,4 +1,4 @@
-// Dispatcher of the int4 tensor_core_tiled linear: decode shapes (M <= 16) go to the GEMV kernel, larger
+// Dispatcher of the int4 tensor_core_tiled linear: decode shapes (M <= 8) go to the GEMV kernel, larger
 // batches to the tcgen05 kernel; shapes that kernel does not take run as row blocks of 16 through the GEMV.
 #include "common.cuh"
 
@@ -12,8 +12,8 @@ int int4_umma_linear(const void* x, int64_t ldx, int64_t x_cols, const int32_t* 
 
 extern "C" size_t ao_int4_tinygemm_linear_workspace_bytes(int64_t M, int64_t N, int64_t K, int group,
                                                           int inner_k_tiles) {
-    if (M <= 16) return ao_int4_gemv_workspace_bytes(M, N, K, group, inner_k_tiles);
-    // large batches: the tcgen05 kernel's need, and the decode kernel's for shapes that fall back to row blocks
+    if (M <= 8) return ao_int4_gemv_workspace_bytes(M, N, K, group, inner_k_tiles);
+    // larger batches: the tcgen05 kernel's need, and the decode kernel's for shapes that fall back to row blocks
     size_t need = ao::umma::int4_umma_workspace_bytes(M, N, K, group, inner_k_tiles);
     for (int m = 1; m <= 16; m *= 2) {
         const size_t b = ao_int4_gemv_workspace_bytes(m, N, K, group, inner_k_tiles);
@@ -28,7 +28,7 @@ extern "C" int ao_int4_tinygemm_linear(const void* x_bf16, int64_t x_row_stride,
                                        int64_t K, int group, int inner_k_tiles, void* y_bf16, void* workspace,
                                        size_t workspace_bytes, ao_stream_t stream) {
     if (M < 0 || N < 0) return AO_ERR_SHAPE;
-    if (M <= 16)
+    if (M <= 8)
         return ao_int4_gemv(x_bf16, x_row_stride, x_cols, packed, scale_and_zero, M, N, K, group, inner_k_tiles, y_bf16,
                             workspace, workspace_bytes, stream);
     if (workspace == nullptr || workspace_bytes < 256 || !ao::aligned(workspace, 256)) return AO_ERR_WORKSPACE;
@@ -37,6 +37,9 @@ extern "C" int ao_int4_tinygemm_linear(const void* x_bf16, int64_t x_row_stride,
                                                   inner_k_tiles, y_bf16, workspace, workspace_bytes, ao::as_stream(stream));
         if (rc != AO_ERR_UNSUPPORTED) return rc;
     }
+    if (M <= 16)
+        return ao_int4_gemv(x_bf16, x_row_stride, x_cols, packed, scale_and_zero, M, N, K, group, inner_k_tiles, y_bf16,
+                            workspace, workspace_bytes, stream);
     // row blocks of 16 through the same kernel, back to back on the stream
     const auto* x = static_cast<const __nv_bfloat16*>(x_bf16);
     auto* y = static_cast<__nv_bfloat16*>(y_bf16);

@@ -411,6 +411,102 @@ def run_ours(args):
         killer.cancel()
 
 
+
+# ----------------------------------------------------------------------------------------------
+# secondary workloads (one kernel family each; used for the profiles, not the headline line)
+# ----------------------------------------------------------------------------------------------
+def run_secondary(args):
+    """--workload fp6_decode | int4_prefill | hqq_prefill | fp6_prefill: one layer shape, rotating weight copies,
+    CUDA-graph replay; reports GB/s against the HBM peak (M <= 16) or TFLOP/s against the bf16 tensor peak."""
+    from ao_b200 import _cabi, ops
+    from ao_b200.prototype.hqq import mixed_mm, pack_hqq_from_rowmajor
+    from ao_b200.prototype.quant_llm.quant_llm import to_scaled_tc_fpx
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device (sm_100a); there is no CPU fallback.")
+    _cabi.lib()
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    wl, M, g = args.workload, args.m, args.group
+    N, K = (int(v) for v in args.shape.split("x"))
+    gen = torch.Generator().manual_seed(SEED)
+    copies = max(1, min(8, int(300e6 // (N * K // 2)) + 1)) if M <= 16 else 1
+    calls = []
+    if wl in ("int4_prefill", "hqq_prefill"):
+        w = (torch.randn(N, K, generator=gen) * 0.02).to(torch.bfloat16).to(dev)
+        x = torch.randn(M, K, generator=gen).to(torch.bfloat16).to(dev)
+        y = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+        if wl == "int4_prefill":
+            packed, sz = ops.int4_quantize_pack(w, g, 8)
+            ws = torch.zeros(max(ops.int4_workspace_bytes(M, N, K, g, 8), 256), dtype=torch.uint8, device=dev)
+            calls.append(lambda: ops.weight_int4pack_mm(x, packed, g, sz, out=y, workspace=ws))
+            kernel = "umma_linear_kernel<MT, TinygemmPolicy>"
+        else:
+            s, z, codes = ops.int4_groupwise_quantize(w, g, want_codes=torch.uint8)
+            zh = (8.0 - z.float() / s.float()).to(torch.bfloat16).T.contiguous()
+            b, sT = pack_hqq_from_rowmajor(codes), s.T.contiguous()
+            calls.append(lambda: mixed_mm(x, b, sT, zh, g))
+            kernel = "umma_linear_kernel<MT, HqqPolicy>"
+        nbytes = N * K // 2 + (K // g) * N * 4 + M * K * 2 + M * N * 2
+        dtype = "bf16"
+    else:
+        w = (torch.randn(N, K, generator=gen) * 0.02).to(torch.float16).to(dev)
+        x = torch.randn(M, K, generator=gen).to(torch.float16).to(dev)
+        for _ in range(copies):
+            packed, scale = to_scaled_tc_fpx(w, 3, 2)
+            calls.append(lambda packed=packed, scale=scale: ops.fp6_llm_linear(x, packed, scale))
+        kernel = "fp6_gemv_kernel" if M <= 16 else "umma_linear_kernel<MT, Fp6Policy>"
+        nbytes = N * K * 3 // 4 + N * 2 + M * K * 2 + M * N * 2
+        dtype = "f16"
+    for c in calls:
+        c()
+    torch.cuda.synchronize()
+    graphs = []
+    for c in calls:
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr):
+            c()
+        graphs.append(gr)
+    for i in range(max(args.warmup, 3)):
+        graphs[i % len(graphs)].replay()
+    sampler = ClockSampler(0)
+    sampler.start()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    start.record()
+    for i in range(args.steps):
+        graphs[i % len(graphs)].replay()
+    stop.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(stop)
+    t_end = time.perf_counter() + 0.4
+    while time.perf_counter() < t_end:
+        for i in range(50):
+            graphs[i % len(graphs)].replay()
+        torch.cuda.synchronize()
+    clocks = sampler.stop()
+    sec = ms * 1e-3 / args.steps
+    flops = 2.0 * M * N * K
+    if M <= 16:
+        peak, kind = peaks()
+        value, unit = nbytes / sec / 1e9, "GB/s"
+        roof = {"bound": "hbm", "achieved": value, "peak": peak, "unit": "GB/s", "frac": value / peak, "traffic": None,
+                "peak_kind": f"of {kind}", "kernel": kernel}
+    else:
+        path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+        peak = json.load(open(path))["bf16_tflops"] if os.path.exists(path) else 1590.0
+        value, unit = flops / sec / 1e12, "TFLOP/s"
+        roof = {"bound": "tensor", "achieved": value, "peak": peak, "unit": "TFLOP/s", "frac": value / peak, "traffic": None,
+                "peak_kind": "of measured (burst)" if os.path.exists(path) else "of fallback", "kernel": kernel,
+                "gbs": nbytes / sec / 1e9}
+    print(json.dumps({
+        "metric": f"{wl} {unit}", "value": value, "unit": unit, "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": dtype,
+        "data": "synthetic", "config": {"workload": wl, "N": N, "K": K, "M": M, "group_size": g if "fp6" not in wl else None,
+                                        "l2": f"{len(graphs)} weight copies rotate" if len(graphs) > 1 else
+                                        "single weight copy (compute-bound shape)"},
+        "roofline": roof, "gpu_launches": args.steps, "clocks": clocks, "cpu_baseline": None, "e2e": None}), flush=True)
+
+
 # DRAM bytes (read + written) per launch of int4_gemv_kernel averaged over the layer set, from the ncu capture
 # summarised under profiles/; keyed by (M, group size).  Missing key: not captured.
 TRAFFIC_BYTES_PER_LAUNCH = {(1, 64): 30775744}
@@ -427,12 +523,19 @@ def main():
     ap.add_argument("--copies", type=int, default=3, help="distinct instances of the weights that rotate (L2)")
     ap.add_argument("--no-graph", action="store_true", help="plain launches instead of CUDA-graph replay")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="decode_int4",
+                    choices=["decode_int4", "fp6_decode", "int4_prefill", "hqq_prefill", "fp6_prefill"],
+                    help="decode_int4 is the headline layer set; the others time one layer shape (--shape NxK, --m)")
+    ap.add_argument("--shape", default="8192x8192", help="N x K of the secondary workloads")
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.impl == "reference":
         if args.steps > 30:
             args.steps = 30  # ~0.1-0.2 s per step on the host
         run_reference(args)
+        return
+    if args.workload != "decode_int4":
+        run_secondary(args)
         return
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} needs {args.gpus} ranks (launch with torch.distributed.run); got {world}")

@@ -162,7 +162,7 @@ int ao_from_scaled_tc_fp6(const uint8_t* packed, int64_t M, int64_t N, const voi
  * stands in for the reference's per-call zero padding of the activation to the padded K,
  * affine_quantized_tensor.py:625-627), packed int32 tensor_core_tiled (inner_k_tiles 8/4/2),
  * scale_and_zero bf16 [K/group][N][2] -> y bf16 [M][N] contiguous.
- * M <= 16 runs the HBM-bound GEMV kernel; larger M the tcgen05 kernel (inner_k_tiles 8, N >= 128, 16-byte
+ * M <= 8 runs the HBM-bound GEMV kernel; larger M the tcgen05 kernel (inner_k_tiles 8, N >= 128, 16-byte
  * aligned activation rows), anything else is processed in row blocks of 16 by the GEMV kernel.
  *
  * Workspace: ao_int4_tinygemm_linear_workspace_bytes(...) bytes, 256-byte aligned.  It holds a

@@ -34,7 +34,12 @@ def test_static_scratch_matches_regular_entry_point(N, K, g, M):
     packed, sz, x = _setup(N, K, g, M, seed=N + K + M)
     need = lib.ao_int4_gemv_workspace_bytes(M, N, K, g, 8)
     assert 0 < need <= lib.ao_int4_gemv_static_scratch_max_bytes()
-    y_ref = ops.weight_int4pack_mm(x, packed, g, sz)
+    # the regular entry point of the same kernel, with a caller-owned workspace
+    ws = torch.zeros(need, dtype=torch.uint8, device="cuda")
+    y_ref = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+    rc = lib.ao_int4_gemv(_cabi.ptr(x), x.stride(0), K, _cabi.ptr(packed), _cabi.ptr(sz), M, N, K, g, 8, _cabi.ptr(y_ref),
+                          _cabi.ptr(ws), ws.numel(), _cabi.stream_ptr())
+    assert rc == 0
     for _ in range(2):  # the second call finds the first call's contents in the shared array
         rc, y = _static(lib, x, packed, sz, M, N, K, g)
         assert rc == 0, lib.ao_status_string(rc)
