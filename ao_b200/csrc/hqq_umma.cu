@@ -42,18 +42,18 @@ struct HqqPolicy {
         const uint32_t magic = BF16 ? 0x43004300u : 0x64006400u;
         const uint32_t one2 = BF16 ? 0x3F803F80u : 0x3C003C00u;
         const uint32_t moff = BF16 ? 0xC300C300u : 0xE400E400u;
-        const int td = dw * 32 + lane;
+        const int td = dw * 32 + lane;    // 512 threads, two items each
         const int c = td & 15;            // 8-byte chunk of the 128 n: n = 8c .. 8c + 7
-        const int r_lo = td >> 4;         // byte row inside a group of 16
+        const int r_lo = td >> 4;         // byte row inside a group of 32
         const uint32_t sc_addr = raw + kWBytes + c * 16;
-        const uint32_t blk_off = (c >> 3) * 8192 + 0;   // 64-wide n block
+        const uint32_t blk_off = (c >> 3) * 8192;   // 64-wide n block
         const int cc = c & 7;
-        uint32_t s[4] = {0, 0, 0, 0}, nzs[4] = {0, 0, 0, 0};
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            const int r = q * 16 + r_lo;   // byte row 0..63: k = 2r, 2r + 1 of the 128-k stage
-            if (q == 0 || GSHIFT == 5 || (GSHIFT == 6 && q == 2)) {
-                const int gi = GSHIFT >= 7 ? 0 : (q * 32) >> GSHIFT;
+        for (int q = 0; q < 2; ++q) {
+            const int r = q * 32 + r_lo;   // byte row 0..63: k = 2r, 2r + 1 of the 128-k stage
+            uint32_t s[4], nzs[4];
+            {
+                const int gi = GSHIFT >= 7 ? 0 : (2 * r) >> GSHIFT;
                 const uint4 sv = ptx::lds128(sc_addr + gi * 256);
                 const uint4 zv = ptx::lds128(sc_addr + 1024 + gi * 256);
                 s[0] = sv.x; s[1] = sv.y; s[2] = sv.z; s[3] = sv.w;

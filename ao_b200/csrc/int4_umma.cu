@@ -40,9 +40,8 @@ struct TinygemmPolicy {
         const int st_r = lane & 7, st_c = lane >> 3;
         const uint32_t st_off0 = st_r * 128 + ((st_c ^ st_r) << 4);          // word 0 of a 64-k block: chunks 0..3
         const uint32_t st_off1 = st_r * 128 + (((st_c + 4) ^ st_r) << 4);    // word 1: chunks 4..7
-#pragma unroll
-        for (int tt = 0; tt < 2; ++tt) {
-            const int tile = 2 * dw + tt;
+        {
+            const int tile = dw;   // one tile of 8 rows x 128 k per warp
             const uint4 w4 = ptx::lds128(raw + tile * 512 + lane * 16);
             const uint32_t w[4] = {w4.x, w4.y, w4.z, w4.w};
             const uint32_t sc_addr = raw + kWBytes + tile * 32 + (lane >> 2) * 4;

@@ -61,14 +61,25 @@ __device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity
     return ok != 0;
 }
 
-// Bounded wait: returns false if the phase did not complete within `limit` polls.  Each poll may
-// suspend the thread (no issue slots used) for up to ~0.1 ms, so the bound is limit * 0.1 ms.
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Bounded wait: returns false if the phase did not complete within about limit * 0.1 ms.  mbarrier.try_wait blocks
+// inside the hardware for a short, implementation-defined time and returns as soon as the phase completes, so the
+// loop issues few instructions and wakes up without the latency of a sleep.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, int limit) {
     if (mbar_try_wait(bar, parity)) return true;
-    for (int i = 0; i < limit; ++i) {
-        if (mbar_try_wait_hint(bar, parity, 100000u)) return true;
+    const uint64_t t0 = globaltimer_ns();
+    const uint64_t budget = static_cast<uint64_t>(limit) * 100000ull;
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 16; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (globaltimer_ns() - t0 > budget) return false;
     }
-    return false;
 }
 
 // 1-D bulk copy global -> this CTA's shared memory, completion counted in bytes on an mbarrier.
@@ -233,6 +244,12 @@ __device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&v)
           "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
         : "r"(taddr)
         : "memory");
+}
+__device__ __forceinline__ void tmem_ld_32x32b_x8(uint32_t taddr, uint32_t (&v)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+                 : "r"(taddr)
+                 : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");

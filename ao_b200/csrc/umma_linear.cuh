@@ -1,4 +1,4 @@
-// Skeleton of the prefill-shaped weight-only linears (M > 16) on the 5th-generation tensor cores:
+// Skeleton of the prefill-shaped weight-only linears (M > 8) on the 5th-generation tensor cores:
 //   y[M][N] = x[M][K] @ dequant(W)[N][K]^T,   tcgen05.mma with the accumulator in tensor memory.
 //
 // The product is computed transposed: a CTA owns 128 weight rows (the MMA's M dimension, one tensor-memory lane
@@ -8,7 +8,7 @@
 //   warp 1     streams x tiles [MT][64] with TMA in the 128-byte-swizzle K-major layout the MMA reads;
 //   warp 2     owns the tensor memory and issues the MMAs: four K=16 instructions per operand stage, then a
 //              commit that frees the stage;
-//   warps 3-10 dequantise raw bytes in registers and write the 16-bit operand tile (layout chosen by the weight
+//   warps 3-18 dequantise raw bytes in registers and write the 16-bit operand tile (layout chosen by the weight
 //              format's policy); after the K loop the same warps read the accumulator from tensor memory and
 //              store y.
 // When the tiles alone would leave SMs idle, K is cut into slabs over gridDim.z; fp32 partial tiles meet in the
@@ -20,7 +20,7 @@
 //   kBF16                          operands are bf16 (else fp16); y has the same type
 //   kAMajorMN                      the dequantised operand tile is MN-major (else K-major), both 128-byte swizzle
 //   issue_raw(p, dst, bar, k0, n0) one thread: expect_tx + the async copies of a raw stage
-//   dequant(raw, a_tiles, dw, lane) 8 warps: raw stage -> two consecutive 16 KiB operand tiles (k 0..63, 64..127)
+//   dequant(raw, a_tiles, dw, lane) 16 warps: raw stage -> two consecutive 16 KiB operand tiles (k 0..63, 64..127)
 //   out_row(lane_row)              weight row (inside the CTA's 128) that tensor-memory lane `lane_row` holds
 //   row_scale(p, n)                factor applied to the accumulator of weight row n
 #pragma once
@@ -35,8 +35,7 @@ constexpr int kRows = 128;            // weight rows per CTA
 constexpr int kKB = 64;               // k per operand stage (one 128-byte swizzle atom of 16-bit elements)
 constexpr int kRawK = 128;            // k per raw stage / dequant iteration
 constexpr int kABytes = kRows * kKB * 2;       // 16 KiB
-constexpr int kS = 4;                 // operand stages
-constexpr int kDequantWarps = 8;
+constexpr int kDequantWarps = 16;
 constexpr int kThreads = (3 + kDequantWarps) * 32;
 constexpr int kWaitPolls = 2000;
 constexpr int kHeaderBytes = 256;
@@ -59,7 +58,14 @@ struct alignas(64) Params {
 template <int MT, class Policy>
 struct Cfg {
     static constexpr int XBytes = MT * kKB * 2;
-    static constexpr int Fixed = 1024 + kS * (kABytes + XBytes) + 256;
+    // activation stages: the ring has to cover the TMA latency, so small tiles get more of them (a power of two)
+    static constexpr int SX = MT <= 32 ? 8 : 4;
+    static constexpr int SXShift = MT <= 32 ? 3 : 2;
+    // operand stages: with small token tiles the MMAs are short and the ring has to cover the latency from the last
+    // dequantised byte to the commit that frees the stage
+    static constexpr int SA = MT <= 64 ? 8 : 4;
+    static constexpr int SAShift = MT <= 64 ? 3 : 2;
+    static constexpr int Fixed = 1024 + SA * kABytes + SX * XBytes + 512;
     static constexpr int Rfit = (kSmemLimit - Fixed) / Policy::kRawBytes;
     static constexpr int R = Rfit > 4 ? 4 : Rfit;         // raw stages
     static_assert(R >= 2, "raw ring needs two stages");
@@ -107,10 +113,11 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_kernel(const __grid_c
     const uint32_t raw_addr = ptx::smem_addr(smem_raw);
     const uint32_t base = (raw_addr + 1023u) & ~1023u;   // operand tiles need 1024-byte alignment
     uint8_t* sbase = smem_raw + (base - raw_addr);
-    const uint32_t a_base = base, x_base = a_base + kS * kABytes, raw_base = x_base + kS * C::XBytes;
+    constexpr int SX = C::SX, kS = C::SA;
+    const uint32_t a_base = base, x_base = a_base + kS * kABytes, raw_base = x_base + SX * C::XBytes;
     const uint32_t bar_base = raw_base + R * Policy::kRawBytes;
-    const uint32_t full_a = bar_base, full_x = full_a + 8 * kS, empty = full_x + 8 * kS;
-    const uint32_t raw_full = empty + 8 * kS, raw_empty = raw_full + 8 * 4, acc_full = raw_empty + 8 * 4;
+    const uint32_t full_a = bar_base, empty = full_a + 8 * kS, full_x = empty + 8 * kS, x_empty = full_x + 8 * SX;
+    const uint32_t raw_full = x_empty + 8 * SX, raw_empty = raw_full + 8 * 4, acc_full = raw_empty + 8 * 4;
     const uint32_t tmem_slot = acc_full + 8, flag_slot = tmem_slot + 4;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int M = p.M, N = p.N;
@@ -124,8 +131,11 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_kernel(const __grid_c
     if (tid == 0) {
         for (int s = 0; s < kS; ++s) {
             ptx::mbar_init(full_a + 8 * s, kDequantWarps);
-            ptx::mbar_init(full_x + 8 * s, 1);
             ptx::mbar_init(empty + 8 * s, 1);
+        }
+        for (int s = 0; s < SX; ++s) {
+            ptx::mbar_init(full_x + 8 * s, 1);
+            ptx::mbar_init(x_empty + 8 * s, 1);
         }
         for (int b = 0; b < R; ++b) {
             ptx::mbar_init(raw_full + 8 * b, 1);
@@ -165,8 +175,8 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_kernel(const __grid_c
         // ---------------- activations: one operand stage per 64 k ----------------
         if (lane == 0) {
             for (int kb = 0; kb < 2 * nit; ++kb) {
-                const int s = kb & (kS - 1);
-                if (!ptx::mbar_wait_bounded(empty + 8 * s, (static_cast<uint32_t>(kb >> 2) & 1u) ^ 1u, kWaitPolls)) {
+                const int s = kb & (SX - 1);
+                if (!ptx::mbar_wait_bounded(x_empty + 8 * s, (static_cast<uint32_t>(kb >> C::SXShift) & 1u) ^ 1u, kWaitPolls)) {
                     ok = false;
                     break;
                 }
@@ -180,21 +190,22 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_kernel(const __grid_c
             constexpr uint32_t idesc = ptx::umma_idesc(kRows, MT, Policy::kBF16, Policy::kAMajorMN);
             constexpr uint32_t a_step = Policy::kAMajorMN ? (2048 >> 4) : (32 >> 4);   // descriptor units per k16
             for (int kb = 0; kb < 2 * nit; ++kb) {
-                const int s = kb & (kS - 1);
-                const uint32_t ph = static_cast<uint32_t>(kb >> 2) & 1u;
+                const int s = kb & (kS - 1), sx = kb & (SX - 1);
+                const uint32_t ph = static_cast<uint32_t>(kb >> C::SAShift) & 1u;
                 if (!ptx::mbar_wait_bounded(full_a + 8 * s, ph, kWaitPolls) ||
-                    !ptx::mbar_wait_bounded(full_x + 8 * s, ph, kWaitPolls)) {
+                    !ptx::mbar_wait_bounded(full_x + 8 * sx, static_cast<uint32_t>(kb >> C::SXShift) & 1u, kWaitPolls)) {
                     ok = false;
                     break;
                 }
                 ptx::tcgen05_fence_after_thread_sync();
                 const uint64_t da = Policy::kAMajorMN ? ptx::umma_desc_mn_sw128(a_base + s * kABytes)
                                                       : ptx::umma_desc_k_sw128(a_base + s * kABytes);
-                const uint64_t db = ptx::umma_desc_k_sw128(x_base + s * C::XBytes);
+                const uint64_t db = ptx::umma_desc_k_sw128(x_base + sx * C::XBytes);
 #pragma unroll
                 for (int k4 = 0; k4 < kKB / 16; ++k4)
                     ptx::umma_f16_ss(tmem_base, da + a_step * k4, db + 2 * k4, idesc, (kb | k4) != 0 ? 1u : 0u);
                 ptx::umma_commit(empty + 8 * s);
+                ptx::umma_commit(x_empty + 8 * sx);
             }
             if (ok) ptx::umma_commit(acc_full);
         }
@@ -205,7 +216,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_kernel(const __grid_c
         uint32_t rph = 0;
         for (int it = 0; it < nit && ok; ++it) {
             const int s0 = (2 * it) & (kS - 1);
-            const uint32_t eph = (static_cast<uint32_t>(it >> 1) & 1u) ^ 1u;
+            const uint32_t eph = (static_cast<uint32_t>(it >> (C::SAShift - 1)) & 1u) ^ 1u;
             if (!ptx::mbar_wait_bounded(raw_full + 8 * rb, rph, kWaitPolls) ||
                 !ptx::mbar_wait_bounded(empty + 8 * s0, eph, kWaitPolls) ||
                 !ptx::mbar_wait_bounded(empty + 8 * (s0 + 1), eph, kWaitPolls)) {
@@ -225,27 +236,27 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_kernel(const __grid_c
                 rph ^= 1u;
             }
         }
-        // ---------------- epilogue: lane quarter (warp % 4) x column half (dw / 4) ----------------
+        // ---------------- epilogue: lane quarter (warp % 4) x column quarter (dw / 4) ----------------
         if (ok && !ptx::mbar_wait_bounded(acc_full, 0u, kWaitPolls)) ok = false;
-        const int q = warp & 3, half = dw >> 2;
+        const int q = warp & 3, part = dw >> 2;
         const int row = q * 32 + lane;              // tensor-memory lane
         const int n = n0 + Policy::out_row(row);    // the weight row it holds
         const float rs = n < N ? Policy::row_scale(p, n) : 0.f;
-        constexpr int kColsPerWarp = MT / 2;
-        const int c_begin = half * kColsPerWarp;
+        constexpr int kColsPerWarp = MT / 4;
+        const int c_begin = part * kColsPerWarp;
         const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
         if (nsplit == 1) {
             if (ok) {
                 ptx::tcgen05_fence_after_thread_sync();
 #pragma unroll 1
-                for (int c0 = c_begin; c0 < c_begin + kColsPerWarp; c0 += 16) {
+                for (int c0 = c_begin; c0 < c_begin + kColsPerWarp; c0 += 8) {
                     if (m0 + c0 >= M) break;   // uniform across the warp
-                    uint32_t v[16];
-                    ptx::tmem_ld_32x32b_x16(t_lane + c0, v);
+                    uint32_t v[8];
+                    ptx::tmem_ld_32x32b_x8(t_lane + c0, v);
                     ptx::tmem_ld_wait();
                     if (n < N) {
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) {
+                        for (int j = 0; j < 8; ++j) {
                             const int m = m0 + c0 + j;
                             if (m < M) store_out<Policy::kBF16>(p.y, (size_t)m * N + n, __uint_as_float(v[j]) * rs);
                         }
@@ -262,13 +273,13 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_kernel(const __grid_c
             if (ok) {
                 ptx::tcgen05_fence_after_thread_sync();
 #pragma unroll 1
-                for (int c0 = c_begin; c0 < c_begin + kColsPerWarp; c0 += 16) {
+                for (int c0 = c_begin; c0 < c_begin + kColsPerWarp; c0 += 8) {
                     if (m0 + c0 >= M) break;
-                    uint32_t v[16];
-                    ptx::tmem_ld_32x32b_x16(t_lane + c0, v);
+                    uint32_t v[8];
+                    ptx::tmem_ld_32x32b_x8(t_lane + c0, v);
                     ptx::tmem_ld_wait();
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) mine[(size_t)(c0 + j) * kRows + row] = __uint_as_float(v[j]);
+                    for (int j = 0; j < 8; ++j) mine[(size_t)(c0 + j) * kRows + row] = __uint_as_float(v[j]);
                 }
             }
             __threadfence();
