@@ -163,6 +163,19 @@ def workspace(nbytes, device):
     return buf
 
 
+def workspace_for(cache, query_fn, shape_args, device, raw_stream):
+    """Hot-path variant of workspace(): `cache` (a dict owned by the caller) maps (raw stream, shape) to the buffer."""
+    key = (raw_stream,) + shape_args
+    buf = cache.get(key)
+    if buf is None:
+        nbytes = query_fn(*shape_args)
+        if nbytes <= 0:
+            raise RuntimeError(f"unsupported linear shape {shape_args}")
+        buf = workspace(nbytes, device)
+        cache[key] = buf
+    return buf
+
+
 def workspace_status(device):
     """Status word the kernels leave in the workspace of the current stream (syncs)."""
     device = torch.device(device)

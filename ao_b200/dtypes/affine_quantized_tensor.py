@@ -14,7 +14,7 @@ from typing import Optional, Tuple
 import torch
 from torch.utils._python_dispatch import return_and_correct_aliasing
 
-from .. import ops
+from .. import _cabi, ops
 from ..quantization.quant_primitives import (
     MappingType,
     ZeroPointDomain,
@@ -330,6 +330,55 @@ class TensorCoreTiledAQTLayout(AQTLayout):
         return int_data, scale.reshape(scale.shape[:-1]), zero.reshape(zero.shape[:-1])
 
 
+
+class _Int4LinearPlan:
+    """Everything F.linear needs for one int4 tensor_core_tiled weight, resolved once: raw pointers, sizes, the C
+    entry point.  Calling it is the per-token cost of a decode step, so it touches no tensor-subclass attribute
+    (each of those goes through __torch_function__) and does no argument validation beyond what changes per call."""
+
+    __slots__ = ("packed", "sz", "group", "ikt", "N", "K", "n_out", "k_in", "device", "dev_index", "fn", "ws_fn",
+                 "p_packed", "p_sz", "ws_cache")
+
+    def __init__(self, w):
+        lt = w.layout_tensor
+        self.packed, self.sz = lt.packed_weight, lt.scale_and_zero
+        self.group = int(w.block_size[1])
+        self.ikt = int(self.packed.shape[3]) * 2
+        self.N = int(self.packed.shape[0]) * 8
+        self.K = int(self.packed.shape[1]) * self.ikt * 16
+        shape = torch.Tensor.size(w)
+        self.n_out, self.k_in = int(shape[0]), int(shape[1])
+        self.device = self.packed.device
+        self.dev_index = self.device.index
+        lib = _cabi.lib()
+        self.fn = lib.ao_int4_tinygemm_linear
+        self.ws_fn = lib.ao_int4_tinygemm_linear_workspace_bytes
+        self.p_packed = self.packed.data_ptr()
+        self.p_sz = self.sz.data_ptr()
+        self.ws_cache = {}
+
+    def __call__(self, x, bias):
+        k_in = self.k_in
+        x2 = x.reshape(-1, k_in)
+        if x2.stride(1) != 1 or (x2.stride(0) & 1) or (x2.data_ptr() & 3) or (k_in & 1):
+            x2 = torch.nn.functional.pad(x2, (0, k_in & 1)).contiguous()
+        M = x2.shape[0]
+        y = torch.empty((M, self.N), dtype=torch.bfloat16, device=self.device)
+        if M:
+            stream = torch._C._cuda_getCurrentRawStream(self.dev_index)
+            ws = _cabi.workspace_for(self.ws_cache, self.ws_fn, (M, self.N, self.K, self.group, self.ikt), self.device, stream)
+            rc = self.fn(x2.data_ptr(), x2.stride(0), x2.shape[1], self.p_packed, self.p_sz, M, self.N, self.K, self.group,
+                         self.ikt, y.data_ptr(), ws.data_ptr(), ws.numel(), stream)
+            if rc:
+                _cabi.check(rc, "int4 weight-only linear")
+        if self.n_out != self.N:
+            y = y[:, : self.n_out]
+        y = y.reshape(*x.shape[:-1], self.n_out)
+        if bias is not None:
+            y += bias
+        return y
+
+
 def _quantized_linear_op(input_tensor, weight_qtensor, bias):
     """Quantized F.linear (:539-671): the int4 tensor_core_tiled branch runs the sm_100a kernels."""
     if isinstance(weight_qtensor, AffineQuantizedTensor):
@@ -349,6 +398,8 @@ def _quantized_linear_op(input_tensor, weight_qtensor, bias):
             orig_dtype = input_tensor.dtype
             act_mat = input_tensor.reshape(-1, input_tensor.shape[-1]).to(torch.bfloat16)
             groupsize = weight_qtensor.block_size[1]
+            if type(weight_qtensor) is AffineQuantizedTensor and "_linear_plan" not in weight_qtensor.__dict__:
+                weight_qtensor.__dict__["_linear_plan"] = _Int4LinearPlan(weight_qtensor)   # later calls skip the checks
             # the kernel reads the activation's missing (padded) columns as zero
             y = ops.weight_int4pack_mm(act_mat, packed_weight, groupsize, scale_and_zero)
             orig_out_features = weight_qtensor.shape[-2]
@@ -385,6 +436,11 @@ def _dense_route(func, input_tensor, weight_tensor, *rest):
 @implements(torch.nn.functional.linear)
 def functional_linear(*args, **kwargs):
     input_tensor, weight_tensor, bias = args[0], args[1], args[2] if len(args) > 2 else kwargs.get("bias")
+    # decode fast path: plain bf16 CUDA activation on an int4 tensor_core_tiled weight whose plan is cached
+    plan = weight_tensor.__dict__.get("_linear_plan") if type(weight_tensor) is AffineQuantizedTensor else None
+    if plan is not None and type(input_tensor) is torch.Tensor and input_tensor.dtype is torch.bfloat16 and \
+            input_tensor.device == plan.device:
+        return plan(input_tensor, bias)
     try:
         return _quantized_linear_op(input_tensor, weight_tensor, bias)
     except NotImplementedError:

@@ -210,10 +210,26 @@ class GpuLayerSet:
                 lin.weight = torch.nn.Parameter(model[name].weight.clone(), requires_grad=False)
                 clone[name] = lin
             self.models.append(clone)
-        self.x_host = [make_x_cpu(M, K, SEED + 100 + i).pin_memory() for i, (_, N, K) in enumerate(LAYERS)]
-        self.x = [x.to(device) for x in self.x_host]
-        self.y = [torch.empty(M, N, dtype=torch.bfloat16, device=device) for _, N, K in LAYERS]
-        self.y_host = [torch.empty(M, N, dtype=torch.bfloat16).pin_memory() for _, N, K in LAYERS]
+        # one pinned staging buffer for the step's activations and one for its results (a single copy each way per
+        # step); per-layer tensors are views
+        def carve(flat, shapes):
+            views, off = [], 0
+            for r, c in shapes:
+                views.append(flat[off:off + r * c].view(r, c))
+                off += (r * c + 127) // 128 * 128   # keep every view 256-byte aligned
+            return views
+        x_shapes = [(M, K) for _, N, K in LAYERS]
+        y_shapes = [(M, N) for _, N, K in LAYERS]
+        total = lambda shapes: sum((r * c + 127) // 128 * 128 for r, c in shapes)
+        self.x_host_all = torch.empty(total(x_shapes), dtype=torch.bfloat16).pin_memory()
+        self.x_all = torch.empty(total(x_shapes), dtype=torch.bfloat16, device=device)
+        self.y_host_all = torch.empty(total(y_shapes), dtype=torch.bfloat16).pin_memory()
+        self.y_all = torch.empty(total(y_shapes), dtype=torch.bfloat16, device=device)
+        self.x_host, self.x = carve(self.x_host_all, x_shapes), carve(self.x_all, x_shapes)
+        self.y_host, self.y = carve(self.y_host_all, y_shapes), carve(self.y_all, y_shapes)
+        for i, (_, N, K) in enumerate(LAYERS):
+            self.x_host[i].copy_(make_x_cpu(M, K, SEED + 100 + i))
+        self.x_all.copy_(self.x_host_all)
         nbytes = max(ops.int4_workspace_bytes(M, N, K, g, 8) for _, N, K in LAYERS)
         if nbytes <= 0:
             raise RuntimeError("the int4 linear does not support this workload")
@@ -230,15 +246,19 @@ class GpuLayerSet:
             if gather is not None:
                 gather(i, self.y[i])
 
-    def end_to_end(self, copy, gather=None):
-        """What a user runs per decode step: host activations in, F.linear on the quantized modules, results out."""
+    def end_to_end_enqueue(self, copy, gather=None):
+        """What a user runs per decode step: host activations in, module(x) on the quantized modules, results out."""
         model = self.models[copy]
+        self.x_all.copy_(self.x_host_all, non_blocking=True)
         for i, (name, N, K) in enumerate(LAYERS):
-            self.x[i].copy_(self.x_host[i], non_blocking=True)
             y = model[name](self.x[i])
             if gather is not None:
                 gather(i, y)
-            self.y_host[i].copy_(y, non_blocking=True)
+            self.y[i].copy_(y)
+        self.y_host_all.copy_(self.y_all, non_blocking=True)
+
+    def end_to_end(self, copy, gather=None):
+        self.end_to_end_enqueue(copy, gather)
         torch.cuda.current_stream().synchronize()
 
     def status(self):
@@ -340,7 +360,8 @@ def run_ours(args):
     if ls.status() != 0:
         raise RuntimeError(f"kernel status word {ls.status()} (a bounded wait ran out)")
 
-    # end to end through the public API with host buffers
+    # end to end through the public API with host buffers: eagerly, and with the same step (pinned-host copies in,
+    # module calls, copies out) captured once per weight copy in a CUDA graph and replayed, one synchronise per step
     for i in range(max(args.warmup, 3)):
         ls.end_to_end(i % copies, gather)
     barrier()
@@ -348,14 +369,38 @@ def run_ours(args):
     for i in range(args.steps):
         ls.end_to_end(i % copies, gather)
     torch.cuda.synchronize()
-    e2e_s = time.perf_counter() - t0
+    e2e_eager_s = time.perf_counter() - t0
     barrier()
+    e2e_s, e2e_graph = e2e_eager_s, False
+    if graphs is not None:
+        try:
+            e2e_graphs = []
+            for c in range(copies):
+                gr = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gr):
+                    ls.end_to_end_enqueue(c, gather)
+                e2e_graphs.append(gr)
+            for i in range(max(args.warmup, 3)):
+                e2e_graphs[i % copies].replay()
+                torch.cuda.current_stream().synchronize()
+            barrier()
+            t0 = time.perf_counter()
+            for i in range(args.steps):
+                e2e_graphs[i % copies].replay()
+                torch.cuda.current_stream().synchronize()
+            e2e_s = time.perf_counter() - t0
+            e2e_graph = True
+            barrier()
+        except Exception as e:
+            print(f"[bench] end-to-end graph capture failed ({type(e).__name__}: {e}); reporting the eager run",
+                  file=sys.stderr)
+            torch.cuda.synchronize()
     _note("end-to-end region done")
 
-    times = torch.tensor([ms, e2e_s * 1e3], dtype=torch.float64, device=device)
+    times = torch.tensor([ms, e2e_s * 1e3, e2e_eager_s * 1e3], dtype=torch.float64, device=device)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    ms, e2e_ms = float(times[0]), float(times[1])
+    ms, e2e_ms, e2e_eager_ms = float(times[0]), float(times[1]), float(times[2])
 
     if rank == 0:
         per_rank = step_bytes(M, g)
@@ -377,8 +422,10 @@ def run_ours(args):
                          "traffic": TRAFFIC_BYTES_PER_LAUNCH.get((M, g)), "peak_kind": f"of {peak_kind}",
                          "kernel": "int4_gemv_kernel", "algorithmic_bytes_per_launch": per_rank / ls.launches_per_step,
                          "avg_launch_us": kernel_s * 1e6},
-            "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": sum(M * K * 2 for _, N, K in LAYERS),
-                    "d2h_bytes_per_step": sum(M * N * 2 for _, N, K in LAYERS), "ms_per_step": e2e_ms / args.steps},
+            "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": ls.x_host_all.numel() * 2,
+                    "d2h_bytes_per_step": ls.y_host_all.numel() * 2, "ms_per_step": e2e_ms / args.steps,
+                    "mode": "CUDA-graph replay of the public-API step" if e2e_graph else "eager public-API calls",
+                    "eager_ms_per_step": e2e_eager_ms / args.steps},
             "gpu_launches": launches,
             "clocks": clocks,
             "graph": graphs is not None,
