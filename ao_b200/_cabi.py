@@ -61,6 +61,11 @@ PROTOTYPES = {
     "ao_int4_gemv_workspace_bytes": (_size, [_i64, _i64, _i64, _int, _int]),
     "ao_int4_gemv_static_scratch_max_bytes": (_size, []),
     "ao_int4_gemv_static_scratch": (_int, [_ptr, _i64, _i64, _ptr, _ptr, _i64, _i64, _i64, _int, _int, _ptr, _ptr]),
+    "ao_int4_gemv_gather": (_int, [_ptr, _i64, _i64, _ptr, _ptr, _i64, _i64, _i64, _int, _int, _int, _int,
+                                   _c.POINTER(_ptr), _c.POINTER(_ptr), _ptr, _ptr, _size, _ptr]),
+    "ao_comm_export": (_int, [_ptr, _ptr, _i64p]),
+    "ao_comm_import": (_int, [_ptr, _c.POINTER(_ptr)]),
+    "ao_comm_close": (_int, [_ptr]),
     "ao_hqq_int4_linear_workspace_bytes": (_size, [_i64, _i64, _i64, _int]),
     "ao_hqq_int4_linear": (_int, [_ptr, _int, _i64, _ptr, _ptr, _ptr, _i64, _i64, _i64, _int, _ptr, _ptr, _size, _ptr]),
     "ao_fp6_linear_workspace_bytes": (_size, [_i64, _i64, _i64]),

@@ -87,6 +87,17 @@ int make_plan(int64_t M, int64_t N, int64_t K, int g, int ikt, Plan* P) {
     off += nbuf * nslots * P->NB * 512;
     P->bar_off = off;
     off += 2 * kMaxStages * 8 + 2 * kMaxPairBufs * 8;
+    // staging of the CTA's output rows for the peer exchange (used only when nranks > 1; small)
+    P->rows_cta_max = 16 * ((P->NP + G - 1) / G);
+    P->ystage_off = (off + 15) / 16 * 16;
+    off = P->ystage_off + ((P->M * P->rows_cta_max * 2 + 15) / 16) * 16;
+    P->nranks = 1;
+    P->rank = 0;
+    P->local_state = nullptr;
+    for (int r = 0; r < kMaxRanks; ++r) {
+        P->peer_y[r] = nullptr;
+        P->peer_flags[r] = nullptr;
+    }
     P->smem_bytes = off;
     P->nib_mask = 0x000F000Fu;
     P->magic = 0x43004300u;
@@ -131,6 +142,45 @@ extern "C" int ao_int4_gemv(const void* x_bf16, int64_t x_row_stride, int64_t x_
         case 8: return gemv::launch_ikt<8>(P, x_bf16, x_row_stride, (int)x_cols, packed, scale_and_zero, y_bf16, workspace, st);
         case 4: return gemv::launch_ikt<4>(P, x_bf16, x_row_stride, (int)x_cols, packed, scale_and_zero, y_bf16, workspace, st);
         case 2: return gemv::launch_ikt<2>(P, x_bf16, x_row_stride, (int)x_cols, packed, scale_and_zero, y_bf16, workspace, st);
+    }
+    return AO_ERR_ARG;
+}
+
+// The same kernel with the output exchange in its epilogue: this rank's y block lands in every rank's gathered
+// buffer through peer-mapped pointers (NVLink), followed by per-source arrival counters; the kernel returns
+// once every rank's block has arrived on this GPU.
+extern "C" int ao_int4_gemv_gather(const void* x_bf16, int64_t x_row_stride, int64_t x_cols, const int32_t* packed,
+                                   const void* scale_and_zero, int64_t M, int64_t N, int64_t K, int group,
+                                   int inner_k_tiles, int nranks, int rank, void* const* peer_y,
+                                   void* const* peer_flags, void* local_state, void* workspace,
+                                   size_t workspace_bytes, ao_stream_t stream) {
+    if (M == 0 || N == 0) return AO_OK;
+    if (nranks < 1 || nranks > gemv::kMaxRanks || rank < 0 || rank >= nranks || !peer_y || !peer_flags || !local_state)
+        return AO_ERR_ARG;
+    gemv::Plan P;
+    int rc = gemv::make_plan(M, N, K, group, inner_k_tiles, &P);
+    if (rc) return rc;
+    if (P.nslabs != 1) return AO_ERR_UNSUPPORTED;   // the exchange epilogue needs whole rows per CTA
+    if (P.smem_bytes > 227 * 1024) return AO_ERR_UNSUPPORTED;
+    if (x_cols < 2 || x_cols > K || x_cols % 2 != 0 || x_row_stride < x_cols || x_row_stride % 2 != 0) return AO_ERR_SHAPE;
+    if (!aligned(x_bf16, 4) || !aligned(packed, 16) || !aligned(scale_and_zero, 16) || !aligned(workspace, 256) ||
+        !aligned(local_state, 8))
+        return AO_ERR_ALIGN;
+    if (workspace == nullptr || workspace_bytes < P.ws_bytes) return AO_ERR_WORKSPACE;
+    P.nranks = nranks;
+    P.rank = rank;
+    P.local_state = static_cast<unsigned*>(local_state);
+    for (int r = 0; r < nranks; ++r) {
+        if (!aligned(peer_y[r], 16) || !aligned(peer_flags[r], 4) || !peer_y[r] || !peer_flags[r]) return AO_ERR_ALIGN;
+        P.peer_y[r] = peer_y[r];
+        P.peer_flags[r] = static_cast<unsigned*>(peer_flags[r]);
+    }
+    cudaStream_t st = as_stream(stream);
+    void* y_unused = peer_y[rank];
+    switch (inner_k_tiles) {
+        case 8: return gemv::launch_ikt<8>(P, x_bf16, x_row_stride, (int)x_cols, packed, scale_and_zero, y_unused, workspace, st);
+        case 4: return gemv::launch_ikt<4>(P, x_bf16, x_row_stride, (int)x_cols, packed, scale_and_zero, y_unused, workspace, st);
+        case 2: return gemv::launch_ikt<2>(P, x_bf16, x_row_stride, (int)x_cols, packed, scale_and_zero, y_unused, workspace, st);
     }
     return AO_ERR_ARG;
 }

@@ -36,6 +36,7 @@ constexpr int kMaxStages = 4;
 constexpr int kMaxSubs = 32;             // sub-units per stage
 constexpr int kWaitPolls = 2000;          // suspending polls (<= 0.1 ms each) of one mbarrier phase
 constexpr int kHeaderBytes = 256;
+constexpr int kMaxRanks = 8;
 constexpr int kMaxPairs = 16384;          // completion counters live in a fixed region so that calls of
                                           // different shapes can share one workspace
 
@@ -56,6 +57,15 @@ struct Plan {
     int xs_off, zero_off, sx_off, p32_off, part_off, bar_off, smem_bytes;
     uint32_t nib_mask, magic;  // 0x000F000F, bf16x2 (128, 128): runtime values so they stay in registers
     size_t ws_counters_off, ws_slots_off, ws_bytes;
+    // output exchange over peer memory (nranks > 1): this rank's y block is written into every rank's gathered
+    // buffer; peer_y[r] is where it goes in rank r's memory, peer_flags[r] rank r's arrival counters (one per source
+    // rank), local_state this rank's {CTA counter, arrivals expected so far}
+    int nranks, rank;
+    int ystage_off;     // shared-memory staging of the CTA's output rows [M][16 * pairs per CTA]
+    int rows_cta_max;   // 16 * max pairs per CTA
+    void* peer_y[kMaxRanks];
+    unsigned* peer_flags[kMaxRanks];
+    unsigned* local_state;
 };
 
 int make_plan(int64_t M, int64_t N, int64_t K, int g, int ikt, Plan* P);
@@ -131,6 +141,79 @@ __device__ __noinline__ void finish_pair(const Plan& P, const float (&v)[NB][4],
     }
     store_rows<NB>(P, sum, p, lane, y);
     if (lane == 0) *counter = 0;  // ready for the next call
+}
+
+
+// ---- output exchange over peer memory -------------------------------------------------------------------------
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void red_add_release_sys(unsigned* p, unsigned v) {
+    asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// The reducer warp keeps the CTA's finished rows in shared memory ([M][rows_cta_max] bf16) instead of storing them.
+template <int NB>
+__device__ __forceinline__ void stage_rows(const Plan& P, __nv_bfloat16* ys, const float (&v)[NB][4], int pi, int lane) {
+    const int row = lane >> 2, c = lane & 3;
+    const int r_a = 16 * pi + row, r_b = r_a + 8;
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb) {
+        const int m0 = nb * 8 + 2 * c;
+        if (m0 < P.M) {
+            ys[m0 * P.rows_cta_max + r_a] = __float2bfloat16_rn(v[nb][0]);
+            ys[m0 * P.rows_cta_max + r_b] = __float2bfloat16_rn(v[nb][2]);
+        }
+        if (m0 + 1 < P.M) {
+            ys[(m0 + 1) * P.rows_cta_max + r_a] = __float2bfloat16_rn(v[nb][1]);
+            ys[(m0 + 1) * P.rows_cta_max + r_b] = __float2bfloat16_rn(v[nb][3]);
+        }
+    }
+}
+
+// One warp: copies the CTA's staged rows (output rows 16 * pbeg .. of every batch row) into every rank's gathered
+// buffer with 16-byte stores, then tells every rank that one more CTA of this rank has delivered.  The CTA that
+// finishes last on this GPU waits (bounded) until all CTAs of all ranks have delivered here, so that the kernel's
+// completion means "the gathered output is complete on this GPU".
+static __device__ __noinline__ bool exchange_rows(const Plan& P, const __nv_bfloat16* ys, int pbeg, int npairs, int lane) {
+    const int nrows = min(16 * npairs, P.N - 16 * pbeg);     // a lone last 8-row tile ends the matrix
+    const int vec = nrows / 8;                               // 16-byte pieces per batch row (N is a multiple of 8)
+    __syncwarp();
+    for (int i = 0; i < P.nranks; ++i) {
+        const int r = (P.rank + i) % P.nranks;                // start with the local copy, spread the peers
+        __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(P.peer_y[r]) + 16 * pbeg;
+        for (int m = 0; m < P.M; ++m) {
+            const uint4* src = reinterpret_cast<const uint4*>(ys + m * P.rows_cta_max);
+            uint4* d = reinterpret_cast<uint4*>(dst + (size_t)m * P.N);
+            for (int j = lane; j < vec; j += 32) d[j] = src[j];
+        }
+    }
+    __threadfence_system();
+    __syncwarp();
+    if (lane < P.nranks) red_add_release_sys(P.peer_flags[lane] + P.rank, 1u);
+    bool ok = true;
+    if (lane == 0) {
+        const unsigned done = atomicAdd(P.local_state, 1u);
+        if (done + 1 == gridDim.x) {
+            // last CTA of this GPU: every source rank delivers gridDim.x arrivals per call
+            P.local_state[0] = 0u;
+            const unsigned expected = P.local_state[1] + gridDim.x;
+            P.local_state[1] = expected;
+            const unsigned* mine = P.peer_flags[P.rank];
+            const uint64_t t0 = ptx::globaltimer_ns();
+            for (int src = 0; src < P.nranks && ok; ++src) {
+                while (static_cast<int>(ld_acquire_sys(mine + src) - expected) < 0) {
+                    if (ptx::globaltimer_ns() - t0 > 200000000ull) {   // 0.2 s
+                        ok = false;
+                        break;
+                    }
+                }
+            }
+        }
+    }
+    return __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
 }
 
 template <int N_WORDS>
@@ -357,7 +440,15 @@ int4_gemv_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int Kx, con
             }
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(pair_free_bar + 8 * buf);
-            finish_pair<NB>(P, sum, pbeg + pi, slab, lane, y, ws);
+            if (P.nranks > 1)
+                stage_rows<NB>(P, reinterpret_cast<__nv_bfloat16*>(smem + P.ystage_off), sum, pi, lane);
+            else
+                finish_pair<NB>(P, sum, pbeg + pi, slab, lane, y, ws);
+        }
+        if (P.nranks > 1) {
+            // even after a failed wait the exchange runs, so that the other ranks are not left waiting for this one
+            if (!exchange_rows(P, reinterpret_cast<const __nv_bfloat16*>(smem + P.ystage_off), pbeg, pend - pbeg, lane))
+                ok = false;
         }
         if (!ok && lane == 0) atomicExch(status, AO_ERR_TIMEOUT);
         return;

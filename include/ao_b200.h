@@ -184,6 +184,31 @@ int ao_int4_gemv(const void* x_bf16, int64_t x_row_stride, int64_t x_cols, const
                  int inner_k_tiles, void* y_bf16, void* workspace, size_t workspace_bytes,
                  ao_stream_t stream);
 
+/* The GEMV with the output exchange of a row-sharded layer in its epilogue (no counterpart in the reference, which
+ * has no multi-GPU path for this operator).  Rank `rank` of `nranks` holds N rows of the weight; its y block [M][N]
+ * is written into every rank's gathered buffer through peer-mapped pointers (NVLink), 16 bytes per store, followed
+ * by one arrival per CTA on every rank's counters; the last CTA to finish on this GPU waits (at most 0.2 s, then
+ * AO_ERR_TIMEOUT in the status word) until all CTAs of all ranks have delivered here, so kernel completion means
+ * "the gathered output is complete on this GPU".
+ *   peer_y[r]      where this rank's block goes in rank r's memory (r = rank: the local copy); 16-byte aligned,
+ *                  row stride N elements
+ *   peer_flags[r]  rank r's arrival counters, unsigned[nranks] indexed by source rank, zero before the first call
+ *   local_state    this rank's unsigned[2] {CTA counter, arrivals expected so far}, zero before the first call
+ * Every rank must issue the same sequence of calls with the same shapes.  A buffer may be reused as a destination
+ * once two other exchanges of the same group have been issued after the kernels that read it.  Needs K small
+ * enough for the activations to fit in shared memory (otherwise AO_ERR_UNSUPPORTED). */
+int ao_int4_gemv_gather(const void* x_bf16, int64_t x_row_stride, int64_t x_cols, const int32_t* packed,
+                        const void* scale_and_zero, int64_t M, int64_t N, int64_t K, int group,
+                        int inner_k_tiles, int nranks, int rank, void* const* peer_y,
+                        void* const* peer_flags, void* local_state, void* workspace,
+                        size_t workspace_bytes, ao_stream_t stream);
+
+/* Set-up helpers for the exchange (CUDA IPC): export the 64-byte handle of the allocation that contains ptr and
+ * ptr's offset in it; map another process's allocation; unmap it.  Not for the hot path. */
+int ao_comm_export(const void* ptr, void* handle_out, int64_t* offset_out);
+int ao_comm_import(const void* handle, void** base_out);
+int ao_comm_close(void* base);
+
 /* The same GEMV without a workspace argument.  This entry point has no counterpart in the reference.
  * It is for callers that cannot pass scratch memory and must not allocate (a fixed operator signature,
  * a C serving loop without a device allocator): the scratch is a device array inside the library, one per
