@@ -2,9 +2,8 @@
 
 Every rank allocates one device buffer, exports its CUDA IPC handle, and maps the buffers of all other ranks, so that a
 kernel on this GPU can store into them over NVLink.  Layout of each rank's buffer:
-    [0, 32)    arrival counters, unsigned[8], one per source rank (written by the peers' kernels)
-    [64, 72)   this rank's {CTA counter, arrivals expected so far}
-    [256, ...) payload: gathered outputs, carved by the caller
+    [64, 72)   this rank's {finished-CTA counter, calls so far} (used by the kernels)
+    [256, ...) payload: gathered outputs and landing areas, carved by the caller
 torch.distributed is used only to exchange the handles.
 """
 import ctypes
@@ -52,8 +51,6 @@ class PeerExchange:
                 self._mapped.append(out.value)
                 self.base.append(out.value + off)
         dist.barrier(group=group)
-        ptr_array = ctypes.c_void_p * self.world
-        self.flags_array = ptr_array(*[b for b in self.base])
         self.local_state = ctypes.c_void_p(self.base[self.rank] + 64)
 
     def payload(self, offset_bytes: int, shape, dtype) -> torch.Tensor:

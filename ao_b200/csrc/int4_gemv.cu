@@ -94,10 +94,8 @@ int make_plan(int64_t M, int64_t N, int64_t K, int g, int ikt, Plan* P) {
     P->nranks = 1;
     P->rank = 0;
     P->local_state = nullptr;
-    for (int r = 0; r < kMaxRanks; ++r) {
-        P->peer_y[r] = nullptr;
-        P->peer_flags[r] = nullptr;
-    }
+    P->y_gathered = nullptr;
+    for (int r = 0; r < kMaxRanks; ++r) P->peer_ll[r] = nullptr;
     P->smem_bytes = off;
     P->nib_mask = 0x000F000Fu;
     P->magic = 0x43004300u;
@@ -146,16 +144,16 @@ extern "C" int ao_int4_gemv(const void* x_bf16, int64_t x_row_stride, int64_t x_
     return AO_ERR_ARG;
 }
 
-// The same kernel with the output exchange in its epilogue: this rank's y block lands in every rank's gathered
-// buffer through peer-mapped pointers (NVLink), followed by per-source arrival counters; the kernel returns
-// once every rank's block has arrived on this GPU.
+// The same kernel with the output exchange in its epilogue: every CTA sends its rows to the same CTA of every peer
+// through peer-mapped memory (NVLink) and collects the peers' rows; the kernel returns once this GPU's gathered
+// output [nranks][M][N] is complete.
 extern "C" int ao_int4_gemv_gather(const void* x_bf16, int64_t x_row_stride, int64_t x_cols, const int32_t* packed,
                                    const void* scale_and_zero, int64_t M, int64_t N, int64_t K, int group,
-                                   int inner_k_tiles, int nranks, int rank, void* const* peer_y,
-                                   void* const* peer_flags, void* local_state, void* workspace,
-                                   size_t workspace_bytes, ao_stream_t stream) {
+                                   int inner_k_tiles, int nranks, int rank, void* const* peer_landing,
+                                   void* y_gathered, void* local_state, void* workspace, size_t workspace_bytes,
+                                   ao_stream_t stream) {
     if (M == 0 || N == 0) return AO_OK;
-    if (nranks < 1 || nranks > gemv::kMaxRanks || rank < 0 || rank >= nranks || !peer_y || !peer_flags || !local_state)
+    if (nranks < 1 || nranks > gemv::kMaxRanks || rank < 0 || rank >= nranks || !peer_landing || !y_gathered || !local_state)
         return AO_ERR_ARG;
     gemv::Plan P;
     int rc = gemv::make_plan(M, N, K, group, inner_k_tiles, &P);
@@ -164,23 +162,22 @@ extern "C" int ao_int4_gemv_gather(const void* x_bf16, int64_t x_row_stride, int
     if (P.smem_bytes > 227 * 1024) return AO_ERR_UNSUPPORTED;
     if (x_cols < 2 || x_cols > K || x_cols % 2 != 0 || x_row_stride < x_cols || x_row_stride % 2 != 0) return AO_ERR_SHAPE;
     if (!aligned(x_bf16, 4) || !aligned(packed, 16) || !aligned(scale_and_zero, 16) || !aligned(workspace, 256) ||
-        !aligned(local_state, 8))
+        !aligned(local_state, 8) || !aligned(y_gathered, 16))
         return AO_ERR_ALIGN;
     if (workspace == nullptr || workspace_bytes < P.ws_bytes) return AO_ERR_WORKSPACE;
     P.nranks = nranks;
     P.rank = rank;
     P.local_state = static_cast<unsigned*>(local_state);
+    P.y_gathered = static_cast<__nv_bfloat16*>(y_gathered);
     for (int r = 0; r < nranks; ++r) {
-        if (!aligned(peer_y[r], 16) || !aligned(peer_flags[r], 4) || !peer_y[r] || !peer_flags[r]) return AO_ERR_ALIGN;
-        P.peer_y[r] = peer_y[r];
-        P.peer_flags[r] = static_cast<unsigned*>(peer_flags[r]);
+        if (!peer_landing[r] || !aligned(peer_landing[r], 16)) return AO_ERR_ALIGN;
+        P.peer_ll[r] = static_cast<uint2*>(peer_landing[r]);
     }
     cudaStream_t st = as_stream(stream);
-    void* y_unused = peer_y[rank];
     switch (inner_k_tiles) {
-        case 8: return gemv::launch_ikt<8>(P, x_bf16, x_row_stride, (int)x_cols, packed, scale_and_zero, y_unused, workspace, st);
-        case 4: return gemv::launch_ikt<4>(P, x_bf16, x_row_stride, (int)x_cols, packed, scale_and_zero, y_unused, workspace, st);
-        case 2: return gemv::launch_ikt<2>(P, x_bf16, x_row_stride, (int)x_cols, packed, scale_and_zero, y_unused, workspace, st);
+        case 8: return gemv::launch_ikt<8>(P, x_bf16, x_row_stride, (int)x_cols, packed, scale_and_zero, y_gathered, workspace, st);
+        case 4: return gemv::launch_ikt<4>(P, x_bf16, x_row_stride, (int)x_cols, packed, scale_and_zero, y_gathered, workspace, st);
+        case 2: return gemv::launch_ikt<2>(P, x_bf16, x_row_stride, (int)x_cols, packed, scale_and_zero, y_gathered, workspace, st);
     }
     return AO_ERR_ARG;
 }

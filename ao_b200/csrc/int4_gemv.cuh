@@ -57,14 +57,15 @@ struct Plan {
     int xs_off, zero_off, sx_off, p32_off, part_off, bar_off, smem_bytes;
     uint32_t nib_mask, magic;  // 0x000F000F, bf16x2 (128, 128): runtime values so they stay in registers
     size_t ws_counters_off, ws_slots_off, ws_bytes;
-    // output exchange over peer memory (nranks > 1): this rank's y block is written into every rank's gathered
-    // buffer; peer_y[r] is where it goes in rank r's memory, peer_flags[r] rank r's arrival counters (one per source
-    // rank), local_state this rank's {CTA counter, arrivals expected so far}
+    // output exchange over peer memory (nranks > 1): every CTA sends its rows to every peer as 8-byte
+    // {two bf16 rows, call number} words (peer_ll[r]: rank r's landing area [source rank][M][N/2] of such words) and
+    // collects the same rows of every peer from its own landing area into y_gathered [rank][M][N];
+    // local_state = this rank's {finished-CTA counter, number of calls so far}
     int nranks, rank;
     int ystage_off;     // shared-memory staging of the CTA's output rows [M][16 * pairs per CTA]
     int rows_cta_max;   // 16 * max pairs per CTA
-    void* peer_y[kMaxRanks];
-    unsigned* peer_flags[kMaxRanks];
+    uint2* peer_ll[kMaxRanks];
+    __nv_bfloat16* y_gathered;
     unsigned* local_state;
 };
 
@@ -145,13 +146,13 @@ __device__ __noinline__ void finish_pair(const Plan& P, const float (&v)[NB][4],
 
 
 // ---- output exchange over peer memory -------------------------------------------------------------------------
-__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
-    unsigned v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+__device__ __forceinline__ uint2 ld_volatile_u2(const uint2* p) {
+    uint2 v;
+    asm volatile("ld.volatile.global.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
     return v;
 }
-__device__ __forceinline__ void red_add_release_sys(unsigned* p, unsigned v) {
-    asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ void st_volatile_u2(uint2* p, uint32_t a, uint32_t b) {
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(a), "r"(b) : "memory");
 }
 
 // The reducer warp keeps the CTA's finished rows in shared memory ([M][rows_cta_max] bf16) instead of storing them.
@@ -173,47 +174,66 @@ __device__ __forceinline__ void stage_rows(const Plan& P, __nv_bfloat16* ys, con
     }
 }
 
-// One warp: copies the CTA's staged rows (output rows 16 * pbeg .. of every batch row) into every rank's gathered
-// buffer with 16-byte stores, then tells every rank that one more CTA of this rank has delivered.  The CTA that
-// finishes last on this GPU waits (bounded) until all CTAs of all ranks have delivered here, so that the kernel's
-// completion means "the gathered output is complete on this GPU".
-static __device__ __noinline__ bool exchange_rows(const Plan& P, const __nv_bfloat16* ys, int pbeg, int npairs, int lane) {
+// One warp exchanges the CTA's rows (output rows 16 * pbeg .. of every batch row) with the same CTA of every peer.
+// Data and "it has arrived" travel in the same 8-byte store (two bf16 rows + the call number), which the hardware
+// writes as one unit, so no fence and no separate flag are needed: the receiver polls each word of its landing
+// area until it carries this call's number (bounded), and copies the rows into the gathered output.  Every rank
+// runs the same grid on the same shape, so CTA c of a peer owns exactly the rows CTA c collects here.
+static __device__ __noinline__ bool exchange_rows(const Plan& P, const __nv_bfloat16* ys, int pbeg, int npairs, int lane,
+                                                  unsigned call) {
     const int nrows = min(16 * npairs, P.N - 16 * pbeg);     // a lone last 8-row tile ends the matrix
-    const int vec = nrows / 8;                               // 16-byte pieces per batch row (N is a multiple of 8)
+    const int n2 = nrows / 2, half_n = P.N / 2;              // 4-byte row pairs
+    const size_t block = (size_t)P.M * half_n;                // words per source rank in a landing area
     __syncwarp();
-    for (int i = 0; i < P.nranks; ++i) {
-        const int r = (P.rank + i) % P.nranks;                // start with the local copy, spread the peers
-        __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(P.peer_y[r]) + 16 * pbeg;
+    // send
+    for (int i = 1; i < P.nranks; ++i) {
+        const int r = (P.rank + i) % P.nranks;
+        uint2* dst = P.peer_ll[r] + (size_t)P.rank * block + 8 * pbeg;
+        for (int m = 0; m < P.M; ++m) {
+            const uint32_t* src = reinterpret_cast<const uint32_t*>(ys + m * P.rows_cta_max);
+            for (int j = lane; j < n2; j += 32) st_volatile_u2(dst + (size_t)m * half_n + j, src[j], call);
+        }
+    }
+    // local block
+    {
+        __nv_bfloat16* dst = P.y_gathered + (size_t)P.rank * P.M * P.N + 16 * pbeg;
         for (int m = 0; m < P.M; ++m) {
             const uint4* src = reinterpret_cast<const uint4*>(ys + m * P.rows_cta_max);
             uint4* d = reinterpret_cast<uint4*>(dst + (size_t)m * P.N);
-            for (int j = lane; j < vec; j += 32) d[j] = src[j];
+            for (int j = lane; j < nrows / 8; j += 32) d[j] = src[j];
         }
     }
-    __threadfence_system();
-    __syncwarp();
-    if (lane < P.nranks) red_add_release_sys(P.peer_flags[lane] + P.rank, 1u);
+    // receive
     bool ok = true;
-    if (lane == 0) {
-        const unsigned done = atomicAdd(P.local_state, 1u);
-        if (done + 1 == gridDim.x) {
-            // last CTA of this GPU: every source rank delivers gridDim.x arrivals per call
-            P.local_state[0] = 0u;
-            const unsigned expected = P.local_state[1] + gridDim.x;
-            P.local_state[1] = expected;
-            const unsigned* mine = P.peer_flags[P.rank];
-            const uint64_t t0 = ptx::globaltimer_ns();
-            for (int src = 0; src < P.nranks && ok; ++src) {
-                while (static_cast<int>(ld_acquire_sys(mine + src) - expected) < 0) {
+    const uint64_t t0 = ptx::globaltimer_ns();
+    for (int i = 1; i < P.nranks && ok; ++i) {
+        const int r = (P.rank + P.nranks - i) % P.nranks;
+        const uint2* src = P.peer_ll[P.rank] + (size_t)r * block + 8 * pbeg;
+        uint32_t* dst = reinterpret_cast<uint32_t*>(P.y_gathered + (size_t)r * P.M * P.N + 16 * pbeg);
+        for (int m = 0; m < P.M && ok; ++m) {
+            for (int j = lane; j < n2; j += 32) {
+                uint2 v = ld_volatile_u2(src + (size_t)m * half_n + j);
+                while (v.y != call) {
                     if (ptx::globaltimer_ns() - t0 > 200000000ull) {   // 0.2 s
                         ok = false;
                         break;
                     }
+                    v = ld_volatile_u2(src + (size_t)m * half_n + j);
                 }
+                dst[(size_t)m * half_n + j] = v.x;
             }
+            ok = __all_sync(0xffffffffu, ok);
         }
     }
-    return __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+    // the last CTA to finish advances the call number for the next launch
+    if (lane == 0) {
+        const unsigned done = atomicAdd(P.local_state, 1u);
+        if (done + 1 == gridDim.x) {
+            P.local_state[0] = 0u;
+            P.local_state[1] = call;
+        }
+    }
+    return ok;
 }
 
 template <int N_WORDS>
@@ -411,6 +431,9 @@ int4_gemv_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int Kx, con
         const int nbuf_mask = P.nbuf - 1, nbuf_shift = P.nbuf_shift;
         const float4* parts = reinterpret_cast<const float4*>(smem + P.part_off);
         bool ok = true;
+        // number of this call of the exchange (all CTAs of a launch read the same value: it changes when the last
+        // CTA of the launch finishes)
+        const unsigned call = P.nranks > 1 ? *reinterpret_cast<volatile unsigned*>(P.local_state + 1) + 1u : 0u;
         for (int pi = 0; pi < pend - pbeg; ++pi) {
             const int buf = pi & nbuf_mask;
             if (!ptx::mbar_wait_bounded(pair_full_bar + 8 * buf, static_cast<uint32_t>(pi >> nbuf_shift) & 1u, kWaitPolls)) {
@@ -447,7 +470,7 @@ int4_gemv_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int Kx, con
         }
         if (P.nranks > 1) {
             // even after a failed wait the exchange runs, so that the other ranks are not left waiting for this one
-            if (!exchange_rows(P, reinterpret_cast<const __nv_bfloat16*>(smem + P.ystage_off), pbeg, pend - pbeg, lane))
+            if (!exchange_rows(P, reinterpret_cast<const __nv_bfloat16*>(smem + P.ystage_off), pbeg, pend - pbeg, lane, call))
                 ok = false;
         }
         if (!ok && lane == 0) atomicExch(status, AO_ERR_TIMEOUT);

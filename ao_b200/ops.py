@@ -100,29 +100,37 @@ def weight_int4pack_mm(x: Tensor, packed: Tensor, group_size: int, scale_and_zer
     return y
 
 
+def gather_slot_bytes(world: int, M: int, N: int) -> int:
+    """Payload bytes one call site of weight_int4pack_mm_gather needs: output [world][M][N] bf16 + landing area."""
+    return (6 * world * M * N + 255) // 256 * 256
+
+
 def weight_int4pack_mm_gather(x: Tensor, packed: Tensor, group_size: int, scale_and_zero: Tensor, exchange,
                               slot_offset_bytes: int = 0, workspace: Tensor = None) -> Tensor:
     """Row-sharded weight_int4pack_mm with the output exchange fused into the kernel's epilogue.
 
-    This rank's y[M][N_local] is stored into every rank's payload (ao_b200.comm.PeerExchange) at
-    slot_offset_bytes + rank * M * N_local * 2; returns this rank's gathered view [world][M][N_local], complete when
-    the kernel completes.  Every rank must make the same calls in the same order; M <= 16."""
+    Uses gather_slot_bytes(world, M, N_local) bytes of the exchange's payload (ao_b200.comm.PeerExchange) at
+    slot_offset_bytes on every rank: the gathered output [world][M][N_local] followed by the landing area the
+    peers' kernels store into.  Returns this rank's gathered view, complete when the kernel completes.  Every rank
+    must make the same calls in the same order; M <= 16; give consecutive call sites different slots."""
     _cabi.require_cuda(x, packed, scale_and_zero)
     torch._check(x.dim() == 2 and x.dtype == torch.bfloat16 and x.stride(1) == 1, lambda: "x must be 2-D bfloat16")
     ikt = packed.shape[3] * 2
     N, K = packed.shape[0] * 8, packed.shape[1] * ikt * 16
     M = x.shape[0]
     world, rank = exchange.world, exchange.rank
-    block = M * N * 2
     out = exchange.payload(slot_offset_bytes, (world, M, N), torch.bfloat16)
+    landing_off = slot_offset_bytes + 2 * world * M * N
+    torch._check(landing_off % 16 == 0 and slot_offset_bytes + gather_slot_bytes(world, M, N) <= exchange.payload_bytes,
+                 lambda: "exchange payload too small for this call site")
     lib = _cabi.lib()
     nbytes = lib.ao_int4_gemv_workspace_bytes(M, N, K, group_size, ikt)
     torch._check(nbytes > 0, lambda: f"unsupported shape M={M} N={N} K={K} group={group_size}")
-    peer_y = exchange.peer_pointers(slot_offset_bytes + rank * block)
+    landing = exchange.peer_pointers(landing_off)
     with torch.cuda.device(x.device):
         ws = _cabi.workspace(nbytes, x.device) if workspace is None else workspace
         rc = lib.ao_int4_gemv_gather(_cabi.ptr(x), x.stride(0), x.shape[1], _cabi.ptr(packed), _cabi.ptr(scale_and_zero), M, N,
-                                     K, group_size, ikt, world, rank, peer_y, exchange.flags_array, exchange.local_state,
+                                     K, group_size, ikt, world, rank, landing, _cabi.ptr(out), exchange.local_state,
                                      _cabi.ptr(ws), ws.numel(), _stream(x))
     _cabi.check(rc, "weight_int4pack_mm_gather")
     return out

@@ -54,16 +54,22 @@ class RowShardedLinear(torch.nn.Module):
     `quantize_fn(shard)` (e.g. lambda m: quantize(m, int4_weight_only(128))) on the shard only, and forward returns the
     full-width output on every rank."""
 
-    def __init__(self, shard: torch.nn.Linear, out_features: int, multiple: int, group=None):
+    def __init__(self, shard: torch.nn.Linear, out_features: int, multiple: int, group=None, exchange=None,
+                 slot_offset_bytes: int = 0):
         super().__init__()
         self.shard = shard
         self.out_features = out_features
         self.multiple = multiple
         self.group = group
+        # optional fused exchange (ao_b200.comm.PeerExchange): decode batches of an int4 tensor_core_tiled shard
+        # store their outputs straight into every rank's buffer from the kernel's epilogue
+        self.exchange = exchange
+        self.slot_offset_bytes = slot_offset_bytes
 
     @classmethod
     def from_linear(cls, linear: torch.nn.Linear, multiple: int = 8, group=None,
-                    quantize_fn: Optional[Callable[[torch.nn.Module], object]] = None) -> "RowShardedLinear":
+                    quantize_fn: Optional[Callable[[torch.nn.Module], object]] = None, exchange=None,
+                    slot_offset_bytes: int = 0) -> "RowShardedLinear":
         world, rank = dist.get_world_size(group), dist.get_rank(group)
         lo, hi = row_shard_bounds(linear.out_features, world, rank, multiple)
         shard = torch.nn.Linear(linear.in_features, hi - lo, bias=linear.bias is not None, device=linear.weight.device,
@@ -74,7 +80,30 @@ class RowShardedLinear(torch.nn.Module):
                 shard.bias.copy_(linear.bias[lo:hi])
         if quantize_fn is not None:
             quantize_fn(shard)
-        return cls(shard, linear.out_features, multiple, group)
+        return cls(shard, linear.out_features, multiple, group, exchange, slot_offset_bytes)
+
+    def _fused(self, x: torch.Tensor):
+        """The fused path, or None when it does not apply (then forward uses the collective)."""
+        if self.exchange is None or self.shard.bias is not None or x.dtype != torch.bfloat16 or not x.is_cuda:
+            return None
+        w = self.shard.weight
+        lt = getattr(w, "layout_tensor", None)
+        packed = getattr(lt, "packed_weight", None)
+        world = self.exchange.world
+        if packed is None or self.out_features % world != 0 or self.out_features // world != w.shape[0]:
+            return None
+        x2 = x.reshape(-1, x.shape[-1])
+        if x2.shape[0] > 8 or packed.shape[0] * 8 != w.shape[0] or x2.stride(1) != 1:
+            return None
+        from . import ops
+        out = ops.weight_int4pack_mm_gather(x2, packed, int(w.block_size[1]), lt.scale_and_zero, self.exchange,
+                                            self.slot_offset_bytes)            # [world][M][N / world]
+        M = x2.shape[0]
+        y = out.reshape(-1) if M == 1 else out.permute(1, 0, 2).reshape(M, -1)
+        return y.reshape(*x.shape[:-1], self.out_features)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        y = self._fused(x)
+        if y is not None:
+            return y
         return all_gather_rows(self.shard(x), self.out_features, self.multiple, self.group)

@@ -181,7 +181,10 @@ def workload_config(args, world):
             "layers_NxK": {n: [N, K] for n, N, K in LAYERS}, "M": args.m, "group_size": args.group,
             "weights": "bf16 N(0,0.02), 0.1% entries x20, quantised on device",
             "l2": f"{args.copies} distinct copies of the layer set rotate ({args.copies} x 117 MB > 2 x L2)",
-            "parallelism": "single GPU" if world == 1 else f"row shards on {world} GPUs, all-gather of outputs per layer"}
+            "parallelism": "single GPU" if world == 1 else
+            f"row shards on {world} GPUs, outputs of every layer gathered on every rank "
+            f"({'stores over peer memory in the GEMV epilogue' if args.exchange == 'fused' and args.m <= 8 else 'NCCL all-gather'}; "
+            "the end-to-end leg uses the NCCL all-gather)"}
 
 
 # ----------------------------------------------------------------------------------------------
@@ -235,12 +238,27 @@ class GpuLayerSet:
             raise RuntimeError("the int4 linear does not support this workload")
         self.ws = torch.zeros(nbytes, dtype=torch.uint8, device=device)
         self.launches_per_step = len(LAYERS) * ((M + 15) // 16)
+        self.slot_offsets = []
 
-    def kernels_only(self, copy, gather=None):
-        """The hot path alone: one kernel per layer on resident inputs (and the per-layer exchange if sharded)."""
+    def exchange_bytes(self, world):
+        """Carves one gathered-output slot per layer in a PeerExchange payload; returns the payload size."""
+        off = 0
+        self.slot_offsets = []
+        for _, N, K in LAYERS:
+            self.slot_offsets.append(off)
+            off += self.ops.gather_slot_bytes(world, self.M, N)
+        return off
+
+    def kernels_only(self, copy, gather=None, exchange=None):
+        """The hot path alone: one kernel per layer on resident inputs; sharded runs exchange the outputs per layer,
+        in the kernel's epilogue (exchange) or with a collective after it (gather)."""
         model = self.models[copy]
         for i, (name, N, K) in enumerate(LAYERS):
             lt = model[name].weight.layout_tensor
+            if exchange is not None:
+                self.ops.weight_int4pack_mm_gather(self.x[i], lt.packed_weight, self.g, lt.scale_and_zero, exchange,
+                                                   slot_offset_bytes=self.slot_offsets[i], workspace=self.ws)
+                continue
             self.ops.weight_int4pack_mm(self.x[i], lt.packed_weight, self.g, lt.scale_and_zero, out=self.y[i],
                                         workspace=self.ws)
             if gather is not None:
@@ -295,12 +313,17 @@ def run_ours(args):
     ls = GpuLayerSet(M, g, copies, device, rank)
     _note("layer set ready")
 
-    gather = None
+    gather, exchange = None, None
     if world > 1:
         gathered = [torch.empty(world, M, N, dtype=torch.bfloat16, device=device) for _, N, K in LAYERS]
 
         def gather(i, y):
             dist.all_gather_into_tensor(gathered[i], y)
+
+        if args.exchange == "fused" and M <= 8:
+            from ao_b200.comm import PeerExchange
+            exchange = PeerExchange(ls.exchange_bytes(world))
+            _note("peer buffers mapped")
 
     def barrier():
         if world > 1:
@@ -309,7 +332,7 @@ def run_ours(args):
 
     # warm up eagerly (module load, attribute set-up, NCCL channels), then capture one graph per copy
     for c in range(copies):
-        ls.kernels_only(c, gather)
+        ls.kernels_only(c, gather, exchange)
     torch.cuda.synchronize()
     _note("eager warm-up done")
     graphs = None
@@ -319,7 +342,7 @@ def run_ours(args):
             for c in range(copies):
                 gr = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(gr):
-                    ls.kernels_only(c, gather)
+                    ls.kernels_only(c, gather, exchange)
                 graphs.append(gr)
         except Exception as e:  # capture of the collective can be refused; time plain launches then
             print(f"[bench] CUDA graph capture failed ({type(e).__name__}: {e}); timing plain launches", file=sys.stderr)
@@ -450,6 +473,8 @@ def run_ours(args):
         graphs = None
         gc.collect()
         torch.cuda.synchronize()
+        if exchange is not None:
+            exchange.close()
         dist.barrier()
         torch.cuda.synchronize()
         _note("destroying the process group")
@@ -570,6 +595,8 @@ def main():
     ap.add_argument("--copies", type=int, default=3, help="distinct instances of the weights that rotate (L2)")
     ap.add_argument("--no-graph", action="store_true", help="plain launches instead of CUDA-graph replay")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--exchange", choices=["fused", "nccl"], default="fused",
+                    help="N > 1: outputs exchanged by the GEMV epilogue over peer memory, or by an NCCL all-gather")
     ap.add_argument("--workload", default="decode_int4",
                     choices=["decode_int4", "fp6_decode", "int4_prefill", "hqq_prefill", "fp6_prefill"],
                     help="decode_int4 is the headline layer set; the others time one layer shape (--shape NxK, --m)")

@@ -185,23 +185,24 @@ int ao_int4_gemv(const void* x_bf16, int64_t x_row_stride, int64_t x_cols, const
                  ao_stream_t stream);
 
 /* The GEMV with the output exchange of a row-sharded layer in its epilogue (no counterpart in the reference, which
- * has no multi-GPU path for this operator).  Rank `rank` of `nranks` holds N rows of the weight; its y block [M][N]
- * is written into every rank's gathered buffer through peer-mapped pointers (NVLink), 16 bytes per store, followed
- * by one arrival per CTA on every rank's counters; the last CTA to finish on this GPU waits (at most 0.2 s, then
- * AO_ERR_TIMEOUT in the status word) until all CTAs of all ranks have delivered here, so kernel completion means
- * "the gathered output is complete on this GPU".
- *   peer_y[r]      where this rank's block goes in rank r's memory (r = rank: the local copy); 16-byte aligned,
- *                  row stride N elements
- *   peer_flags[r]  rank r's arrival counters, unsigned[nranks] indexed by source rank, zero before the first call
- *   local_state    this rank's unsigned[2] {CTA counter, arrivals expected so far}, zero before the first call
- * Every rank must issue the same sequence of calls with the same shapes.  A buffer may be reused as a destination
- * once two other exchanges of the same group have been issued after the kernels that read it.  Needs K small
- * enough for the activations to fit in shared memory (otherwise AO_ERR_UNSUPPORTED). */
+ * has no multi-GPU path for this operator).  Rank `rank` of `nranks` holds N rows of the weight.  Every CTA sends
+ * its finished rows to every peer through peer-mapped memory (NVLink) as 8-byte words {two bf16 rows, call number}
+ * - data and arrival in one store, no fence - and collects the same rows of every peer from its own landing area
+ * (bounded polling: at most 0.2 s, then AO_ERR_TIMEOUT in the status word); when the kernel completes, y_gathered
+ * [nranks][M][N] is complete on this GPU.
+ *   peer_landing[r]  rank r's landing area for this call site: nranks * M * N / 2 words of 8 bytes, zero before the
+ *                    first call; the entry of `rank` itself is this rank's own area (read here)
+ *   y_gathered       this rank's output, bf16 [nranks][M][N], 16-byte aligned
+ *   local_state      this rank's unsigned[2] {finished-CTA counter, calls so far}, zero before the first call,
+ *                    shared by all call sites of the group
+ * Every rank must issue the same sequence of calls with the same shapes.  A landing area / output may be reused
+ * once two other exchanges of the group have been issued in between (e.g. one area per layer of a decoder block).
+ * Needs K small enough for the activations to fit in shared memory (otherwise AO_ERR_UNSUPPORTED). */
 int ao_int4_gemv_gather(const void* x_bf16, int64_t x_row_stride, int64_t x_cols, const int32_t* packed,
                         const void* scale_and_zero, int64_t M, int64_t N, int64_t K, int group,
-                        int inner_k_tiles, int nranks, int rank, void* const* peer_y,
-                        void* const* peer_flags, void* local_state, void* workspace,
-                        size_t workspace_bytes, ao_stream_t stream);
+                        int inner_k_tiles, int nranks, int rank, void* const* peer_landing,
+                        void* y_gathered, void* local_state, void* workspace, size_t workspace_bytes,
+                        ao_stream_t stream);
 
 /* Set-up helpers for the exchange (CUDA IPC): export the 64-byte handle of the allocation that contains ptr and
  * ptr's offset in it; map another process's allocation; unmap it.  Not for the hot path. */

@@ -34,7 +34,7 @@ def _worker(rank, world, port, out_path):
         g = 64
         shapes = [(1, 1024, 4096), (4, 2048, 4096), (1, 14336 // 2, 4096)]
         slot = 0
-        exch = PeerExchange(4 << 20)
+        exch = PeerExchange(sum(ops.gather_slot_bytes(world, M, N) for M, N, K in shapes))
         for it, (M, N, K) in enumerate(shapes):
             w = tu.make_weight((N, K), seed=100 * rank + it).to(dev)      # every rank has its own rows
             packed, sz = ops.int4_quantize_pack(w, g, 8)
@@ -49,7 +49,7 @@ def _worker(rank, world, port, out_path):
                     if not torch.equal(out[r], ref[r]):
                         ok, why = False, f"shape {(M, N, K)} rep {rep}: block {r} differs on rank {rank}"
                 dist.barrier()
-            slot += (world * M * N * 2 + 255) // 256 * 256
+            slot += ops.gather_slot_bytes(world, M, N)
         if _cabi.workspace_status(dev) != 0:
             ok, why = False, "status word set"
         exch.close()
