@@ -184,7 +184,7 @@ def workload_config(args, world):
             "parallelism": "single GPU" if world == 1 else
             f"row shards on {world} GPUs, outputs of every layer gathered on every rank "
             f"({'stores over peer memory in the GEMV epilogue' if args.exchange == 'fused' and args.m <= 8 else 'NCCL all-gather'}; "
-            "the end-to-end leg uses the NCCL all-gather)"}
+            "the end-to-end leg goes through RowShardedLinear with the same exchange)"}
 
 
 # ----------------------------------------------------------------------------------------------
@@ -239,6 +239,17 @@ class GpuLayerSet:
         self.ws = torch.zeros(nbytes, dtype=torch.uint8, device=device)
         self.launches_per_step = len(LAYERS) * ((M + 15) // 16)
         self.slot_offsets = []
+        self.sharded = None
+
+    def use_exchange(self, exchange, world):
+        """Public-API form of the sharded step: RowShardedLinear modules whose forward runs the fused exchange."""
+        from ao_b200.sharding import RowShardedLinear
+        self.sharded = []
+        for model in self.models:
+            mods = {}
+            for i, (name, N, K) in enumerate(LAYERS):
+                mods[name] = RowShardedLinear(model[name], N * world, 8, None, exchange, self.slot_offsets[i])
+            self.sharded.append(mods)
 
     def exchange_bytes(self, world):
         """Carves one gathered-output slot per layer in a PeerExchange payload; returns the payload size."""
@@ -269,9 +280,12 @@ class GpuLayerSet:
         model = self.models[copy]
         self.x_all.copy_(self.x_host_all, non_blocking=True)
         for i, (name, N, K) in enumerate(LAYERS):
-            y = model[name](self.x[i])
-            if gather is not None:
-                gather(i, y)
+            if self.sharded is not None:
+                y = self.sharded[copy][name](self.x[i])[..., :N]   # full-width output; keep this rank's N columns' worth
+            else:
+                y = model[name](self.x[i])
+                if gather is not None:
+                    gather(i, y)
             self.y[i].copy_(y)
         self.y_host_all.copy_(self.y_all, non_blocking=True)
 
@@ -323,6 +337,7 @@ def run_ours(args):
         if args.exchange == "fused" and M <= 8:
             from ao_b200.comm import PeerExchange
             exchange = PeerExchange(ls.exchange_bytes(world))
+            ls.use_exchange(exchange, world)
             _note("peer buffers mapped")
 
     def barrier():
