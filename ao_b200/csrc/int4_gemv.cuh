@@ -23,9 +23,10 @@
 //    that completes the pair (atomic counter) adds the slots in slab order and leaves the counter at
 //    zero for the next call.
 #pragma once
+#include <cstdlib>
+
 #include "common.cuh"
 #include "ptx.cuh"
-
 
 namespace ao {
 namespace gemv {
@@ -358,6 +359,9 @@ int4_gemv_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int Kx, con
     const int pend = static_cast<int>((static_cast<unsigned>(cta + 1) * static_cast<unsigned>(P.NP)) / static_cast<unsigned>(P.G));
     const int nstage_total = (pend - pbeg) * cpp;
 
+    // the next kernel of the stream may start its own weight prefetch as soon as SMs free up; whatever it reads or
+    // writes besides weights comes after its grid_dependency_wait()
+    ptx::grid_launch_dependents();
     if (tid == nconsumers) {
         for (int s = 0; s < nstages; ++s) {
             ptx::mbar_init(full_bar + 8 * s, 33);       // expect_tx arrival + one cp.async arrival per producer lane
@@ -419,12 +423,16 @@ int4_gemv_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int Kx, con
                 phase ^= 1u;
             }
         }
-        if (!ok && lane == 0) atomicExch(status, AO_ERR_TIMEOUT);
+        if (!ok && lane == 0) {
+            ptx::grid_dependency_wait();
+            atomicExch(status, AO_ERR_TIMEOUT);
+        }
         return;
     }
 
     if (warp == nwarps + 1) {
         // =============================== reducer warp ==================================================
+        ptx::grid_dependency_wait();   // y, the workspace and the exchange state may be in use by earlier kernels
         // adds the consumer warps' partial sums of each finished pair in slot order and stores the rows
         const int NGr = nwarps >> P.gw_shift;
         const int nslots = min(NGr, cpp) << P.gw_shift;
@@ -478,6 +486,7 @@ int4_gemv_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int Kx, con
     }
 
     // ================================= consumer warps ==================================================
+    ptx::grid_dependency_wait();       // x may be the output of the previous kernel
     // ---- activation prologue: x slab -> MMA fragment order, plus per-group sums of x -------------------
     {
         const int steps = P.KS / 32;
@@ -603,17 +612,40 @@ int4_gemv_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int Kx, con
     if (!ok && lane == 0) atomicExch(status, AO_ERR_TIMEOUT);
 }
 
+// AO_B200_NO_PDL=1 turns programmatic dependent launch off (plain stream order)
+inline bool pdl_enabled() {
+    static const bool on = []() {
+        const char* e = getenv("AO_B200_NO_PDL");
+        return !(e && e[0] == '1');
+    }();
+    return on;
+}
+
 template <int IKT, int NB, int MR, int G32>
 int launch_one(const Plan& P, const void* x, long long ldx, int Kx, const void* wq, const void* sz, void* y,
                void* ws, cudaStream_t st) {
     auto kern = int4_gemv_kernel<IKT, NB, MR, G32>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P.smem_bytes) != cudaSuccess)
         return AO_ERR_LAUNCH;
-    dim3 grid(P.G, P.nslabs);
-    kern<<<grid, (P.nwarps + 2) * 32, P.smem_bytes, st>>>(static_cast<const __nv_bfloat16*>(x), ldx, Kx,
-                                                    static_cast<const uint8_t*>(wq), static_cast<const uint8_t*>(sz),
-                                                    static_cast<__nv_bfloat16*>(y), static_cast<uint8_t*>(ws), P);
-    return launch_status();
+    // programmatic dependent launch: this kernel may begin (barrier set-up, weight prefetch) while the previous
+    // kernel of the stream drains; everything else waits inside the kernel
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(P.G, P.nslabs);
+    cfg.blockDim = dim3((P.nwarps + 2) * 32);
+    cfg.dynamicSmemBytes = P.smem_bytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, kern, static_cast<const __nv_bfloat16*>(x), ldx, Kx, static_cast<const uint8_t*>(wq),
+                           static_cast<const uint8_t*>(sz), static_cast<__nv_bfloat16*>(y), static_cast<uint8_t*>(ws),
+                           P) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return AO_ERR_LAUNCH;
+    }
+    return AO_OK;
 }
 
 template <int IKT, int NB, int MR>
