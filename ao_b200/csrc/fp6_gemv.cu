@@ -21,6 +21,8 @@
 // slabs over CTAs when there are too few row blocks to fill the machine or the activations do not fit
 // in shared memory; slab partial sums meet in workspace slots and the CTA that completes a row block
 // (atomic counter) adds them in slab order.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "ptx.cuh"
 #include "fp6_decode.cuh"
@@ -232,6 +234,9 @@ fp6_gemv_kernel(const __half* __restrict__ x, long long ldx, const uint8_t* __re
     constexpr int NG = kConsumerWarps / kGroupWarps;
     const int ncontrib = min(NG, cpb), nslots = ncontrib * kGroupWarps;
 
+    // programmatic dependent launch: the next kernel of the stream may start its weight prefetch while this one
+    // drains; everything it reads or writes besides weights comes after its grid_dependency_wait()
+    ptx::grid_launch_dependents();
     if (tid == nconsumers) {
         for (int s = 0; s < nstages; ++s) {
             ptx::mbar_init(full_bar + 8 * s, 1);
@@ -277,7 +282,10 @@ fp6_gemv_kernel(const __half* __restrict__ x, long long ldx, const uint8_t* __re
                     phase ^= 1u;
                 }
             }
-            if (!ok) atomicExch(status, AO_ERR_TIMEOUT);
+            if (!ok) {
+                ptx::grid_dependency_wait();
+                atomicExch(status, AO_ERR_TIMEOUT);
+            }
         }
         return;
     }
@@ -285,6 +293,7 @@ fp6_gemv_kernel(const __half* __restrict__ x, long long ldx, const uint8_t* __re
     const float4* parts_ro = reinterpret_cast<const float4*>(smem + P.part_off);
     if (warp == nwarps + 1) {
         // =============================== reducer warp ==================================================
+        ptx::grid_dependency_wait();   // y and the workspace may be in use by earlier kernels
         bool ok = true;
         for (int ai = 0; ai < aend - abeg; ++ai) {
             const int buf = ai & (P.nbuf - 1);
@@ -318,6 +327,7 @@ fp6_gemv_kernel(const __half* __restrict__ x, long long ldx, const uint8_t* __re
     }
 
     // ================================= consumer warps ==================================================
+    ptx::grid_dependency_wait();       // x may be the output of the previous kernel
     // x slab -> MMA B-fragment order: per k16 tile and lane (batch column m = lane/4, c = lane%4) the words
     // x[m][k0+2c .. +1] and x[m][k0+2c+8 .. +9]
     {
@@ -421,11 +431,24 @@ static int launch(const Plan& P, const void* x, long long ldx, const void* wq, c
     auto kern = fp6_gemv_kernel<NB, MR>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P.smem_bytes) != cudaSuccess)
         return AO_ERR_LAUNCH;
-    dim3 grid(P.G, P.nslabs);
-    kern<<<grid, kThreads, P.smem_bytes, st>>>(static_cast<const __half*>(x), ldx, static_cast<const uint8_t*>(wq),
-                                               static_cast<const __half*>(scale), static_cast<__half*>(y),
-                                               static_cast<uint8_t*>(ws), P);
-    return launch_status();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(P.G, P.nslabs);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = P.smem_bytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    const char* off = getenv("AO_B200_NO_PDL");
+    attr[0].val.programmaticStreamSerializationAllowed = (off && off[0] == '1') ? 0 : 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, kern, static_cast<const __half*>(x), ldx, static_cast<const uint8_t*>(wq),
+                           static_cast<const __half*>(scale), static_cast<__half*>(y), static_cast<uint8_t*>(ws),
+                           P) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return AO_ERR_LAUNCH;
+    }
+    return AO_OK;
 }
 
 }  // namespace fp6
