@@ -188,6 +188,42 @@ extern "C" int ao_pack_2xint4(const uint8_t* t, int64_t R, int64_t C, uint8_t* o
     return launch_status();
 }
 
+// hqq_quants_to_torch_quants (torchao/prototype/hqq/hqq_tinygemm_linear.py:173-208): HQQ's (W_q, scale, zero) with
+// W = (W_q - zero) * scale  ->  the tinygemm convention W = (q - 8) * scale + new_zero, every operation rounded to the
+// compute dtype as the reference's tensor expressions do.
+__global__ void hqq_to_tinygemm_kernel(const uint8_t* __restrict__ wq, const void* __restrict__ scales,
+                                       const void* __restrict__ zeros, int dt, int64_t groups, int g,
+                                       int32_t* __restrict__ q_out, void* __restrict__ new_zeros) {
+    const int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+    if (idx >= groups * g) return;
+    const int64_t gi = idx / g;
+    const float s = load_as_f32(scales, dt, gi), z = load_as_f32(zeros, dt, gi);
+    const float s8 = round_to(dt, __fmul_rn(s, 8.f));
+    const float nz = round_to(dt, __fsub_rn(s8, round_to(dt, __fmul_rn(z, s))));
+    const float min_val = round_to(dt, __fsub_rn(nz, s8));
+    const float w = static_cast<float>(wq[idx]);
+    const float wr = round_to(dt, __fmul_rn(round_to(dt, __fsub_rn(w, z)), s));
+    float t = round_to(dt, __fsub_rn(wr, min_val));
+    t = round_to(dt, __fdiv_rn(t, s));
+    t = rintf(t);
+    t = fminf(fmaxf(t, 0.f), 15.f);
+    q_out[idx] = static_cast<int32_t>(t);
+    if (idx % g == 0) store_from_f32(new_zeros, dt, gi, nz);
+}
+
+extern "C" int ao_hqq_quants_to_tinygemm(const uint8_t* wq, const void* scales, const void* zeros, int dtype,
+                                         int64_t groups, int group_size, int32_t* q_out, void* new_zeros_out,
+                                         ao_stream_t stream) {
+    if (groups < 0 || group_size < 1) return AO_ERR_SHAPE;
+    if (dtype != AO_BF16 && dtype != AO_F16 && dtype != AO_F32) return AO_ERR_DTYPE;
+    if (groups == 0) return AO_OK;
+    const int64_t n = groups * group_size;
+    if ((n + 255) / 256 > 2147483647LL) return AO_ERR_SHAPE;
+    hqq_to_tinygemm_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, as_stream(stream)>>>(
+        wq, scales, zeros, dtype, groups, group_size, q_out, new_zeros_out);
+    return launch_status();
+}
+
 extern "C" int ao_pack_hqq_int4_from_rowmajor(const uint8_t* codes, int64_t N, int64_t K, uint8_t* out,
                                               ao_stream_t stream) {
     if (N < 1 || K < 2 || K % 2 != 0 || (N + 31) / 32 > 65535) return AO_ERR_SHAPE;

@@ -224,6 +224,14 @@ int ao_int4_gemv_static_scratch(const void* x_bf16, int64_t x_row_stride, int64_
                                 const int32_t* packed, const void* scale_and_zero, int64_t M, int64_t N,
                                 int64_t K, int group, int inner_k_tiles, void* y_bf16, ao_stream_t stream);
 
+/* hqq_quants_to_torch_quants — torchao/prototype/hqq/hqq_tinygemm_linear.py:173-208 (4 bits).  HQQ codes wq uint8
+ * [groups][group_size] with scale / zero per group (dtype = AO_BF16, AO_F16 or AO_F32: the reference's compute dtype)
+ * -> int32 codes of the tinygemm convention and new_zeros = scale * 8 - zero * scale; the scales are unchanged.
+ * Every operation is rounded to the dtype like the reference's tensor expressions. */
+int ao_hqq_quants_to_tinygemm(const uint8_t* wq, const void* scales, const void* zeros, int dtype,
+                              int64_t groups, int group_size, int32_t* q_out, void* new_zeros_out,
+                              ao_stream_t stream);
+
 /* triton_mixed_mm(a, b, scales, zeros, group_size) — torchao/prototype/hqq/mixed_mm.py:36-173 with the kernel
  * torchao/prototype/hqq/kernels.py:162-387 (non-transposed form): c[M][N] = a[M][K] @ ((q - zeros) * scales)[K][N].
  * a: bf16 or fp16 (a_dtype = AO_BF16 / AO_F16) [M][K], row stride a_row_stride elements; b_packed uint8 [K/2][N]

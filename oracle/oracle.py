@@ -259,6 +259,28 @@ def from_scaled_tc_fp6(packed, scale_bits=None, ebits=3, mbits=2):
     return out
 
 
+def hqq_quants_to_torch_quants(wq, scale_bits, zero_bits, dt):
+    """torchao/prototype/hqq/hqq_tinygemm_linear.py:173-208 for 4 bits: wq uint8 [groups][g], scale / zero bit
+    patterns [groups] of dtype dt (BF16 or F16) -> (int32 codes [groups][g], new_zero bit patterns [groups]);
+    every operation rounded to dt."""
+    if dt == BF16:
+        to_f, rnd = bf16_bits_to_f32, lambda v: bf16_bits_to_f32(f32_to_bf16_bits(v))
+        to_bits = f32_to_bf16_bits
+    else:
+        to_f, rnd = f16_bits_to_f32, lambda v: np.asarray(v, np.float32).astype(np.float16).astype(np.float32)
+        to_bits = lambda v: np.asarray(v, np.float32).astype(np.float16).view(np.uint16)
+    s = to_f(np.asarray(scale_bits).reshape(-1, 1)).astype(np.float32)
+    z = to_f(np.asarray(zero_bits).reshape(-1, 1)).astype(np.float32)
+    w = np.asarray(wq, np.float32)
+    s8 = rnd(s * np.float32(8))
+    nz = rnd(s8 - rnd(z * s))
+    min_val = rnd(nz - s8)
+    wr = rnd(rnd(w - z) * s)
+    t = rnd(rnd(wr - min_val) / s)
+    q = np.clip(np.rint(t), 0, 15).astype(np.int32)
+    return q, to_bits(nz.reshape(-1))
+
+
 # ----------------------------------------------------------------------------
 # GEMM oracles
 # ----------------------------------------------------------------------------

@@ -73,3 +73,39 @@ def test_mixed_mm_argument_checks():
         mixed_mm(a, b, s.half(), s.half(), 64)
     with pytest.raises(NotImplementedError):
         mixed_mm(a, b, s, s, 64, transposed=True)
+
+
+@pytest.mark.parametrize("key", ["bf16_g64", "bf16_g128", "f16_g64", "f16_g128"])
+def test_hqq_quants_to_torch_quants_bit_exact(key):
+    from ao_b200.prototype.hqq import hqq_quants_to_torch_quants
+    from tests import golden_util as gu
+    from tests import gpu_util as tu
+    A = gu.load("hqq_convert.npz")
+    dt = "bf16" if key.startswith("bf16") else "f16"
+    tdt = torch.bfloat16 if dt == "bf16" else torch.float16
+    W_q = torch.from_numpy(A[f"{key}/W_q"]).cuda()
+    scales, zeros = tu.to_torch(A[f"{key}/scales"], dt), tu.to_torch(A[f"{key}/zeros"], dt)
+    shape = tuple(A[f"{key}/q"].shape)
+    q, s, nz = hqq_quants_to_torch_quants(W_q, scales, zeros, shape, compute_dtype=tdt)
+    assert q.dtype == torch.int32 and tuple(q.shape) == shape
+    assert np.array_equal(q.cpu().numpy(), A[f"{key}/q"])
+    assert np.array_equal(tu.bits(nz), A[f"{key}/new_zeros"])
+    assert np.array_equal(tu.bits(s).reshape(-1), A[f"{key}/scales"].reshape(-1))
+
+
+def test_hqq_weight_through_both_int4_linears():
+    """The same HQQ-convention weight through mixed_mm (HQQ layout) and, converted, through the tinygemm linear."""
+    from ao_b200 import ops
+    from ao_b200.prototype.hqq import hqq_to_tinygemm_weight, mixed_mm, pack_2xint4
+    N, K, g, M = 512, 1024, 64, 48
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    W_q = torch.randint(0, 16, (N, K), dtype=torch.uint8, device="cuda", generator=gen)
+    scales = (torch.rand(N, K // g, device="cuda", generator=gen) * 0.01 + 0.002).bfloat16()
+    zeros = (torch.rand(N, K // g, device="cuda", generator=gen) * 15).bfloat16()
+    x = torch.randn(M, K, device="cuda", generator=gen).bfloat16()
+    ref = _reference(x, W_q, scales, zeros, g)
+    y_hqq = mixed_mm(x, pack_2xint4(W_q.T), scales.T, zeros.T, g)
+    packed, sz = hqq_to_tinygemm_weight(W_q.reshape(-1, g), scales.reshape(-1, 1), zeros.reshape(-1, 1), (N, K))
+    y_tg = ops.weight_int4pack_mm(x, packed, g, sz)
+    for y in (y_hqq, y_tg):
+        assert float((y.float() - ref).abs().max() / ref.abs().max()) <= 2e-2

@@ -168,3 +168,12 @@ def test_tinygemm_pack_roundtrip():
         p = orc.pack_tinygemm(codes, ikt)
         assert p.shape == (2, 256 // (ikt * 16), 32, ikt // 2)
         assert np.array_equal(orc.unpack_tinygemm(p), codes)
+
+
+@pytest.mark.parametrize("key", ["bf16_g64", "bf16_g128", "f16_g64", "f16_g128"])
+def test_hqq_quants_to_torch_quants_matches_reference_expressions(key):
+    A = gu.load("hqq_convert.npz")
+    dt = orc.BF16 if key.startswith("bf16") else orc.F16
+    q, nz = orc.hqq_quants_to_torch_quants(A[f"{key}/W_q"], A[f"{key}/scales"], A[f"{key}/zeros"], dt)
+    assert np.array_equal(q.reshape(A[f"{key}/q"].shape), A[f"{key}/q"])
+    assert np.array_equal(nz.reshape(A[f"{key}/new_zeros"].shape), A[f"{key}/new_zeros"])
