@@ -66,6 +66,9 @@ PROTOTYPES = {
     "ao_comm_export": (_int, [_ptr, _ptr, _i64p]),
     "ao_comm_import": (_int, [_ptr, _c.POINTER(_ptr)]),
     "ao_comm_close": (_int, [_ptr]),
+    "ao_hqq_int4_linear_transposed_workspace_bytes": (_size, [_i64, _i64, _i64, _int]),
+    "ao_hqq_int4_linear_transposed": (_int, [_ptr, _int, _i64, _ptr, _ptr, _ptr, _i64, _i64, _i64, _int, _ptr, _ptr, _size,
+                                             _ptr]),
     "ao_hqq_quants_to_tinygemm": (_int, [_ptr, _ptr, _ptr, _int, _i64, _int, _ptr, _ptr, _ptr]),
     "ao_hqq_int4_linear_workspace_bytes": (_size, [_i64, _i64, _i64, _int]),
     "ao_hqq_int4_linear": (_int, [_ptr, _int, _i64, _ptr, _ptr, _ptr, _i64, _i64, _i64, _int, _ptr, _ptr, _size, _ptr]),

@@ -21,19 +21,24 @@ __device__ __forceinline__ uint32_t fma2(uint32_t a, uint32_t b, uint32_t c) {
     return d;
 }
 
-template <int GSHIFT, bool BF16>
+// TRANSPOSED: the backward form c[M][K] = a[M][N] @ W[N][K] (reduction along N): the CTA's 128 output rows are k
+// values, the packed bytes run along the reduction dimension, and the operand tile is K-major again.
+template <int GSHIFT, bool BF16, bool TRANSPOSED = false>
 struct HqqPolicy {
     static constexpr int kWBytes = (kRawK / 2) * kRows;   // 64 byte rows x 128 n = 8 KiB
     static constexpr int kScaleRows = (kRawK >> GSHIFT) > 0 ? (kRawK >> GSHIFT) : 1;
     static constexpr int kRawBytes = kWBytes + 2048;       // + scales (<= 4 x 256 B) + zeros (<= 4 x 256 B)
     static constexpr bool kBF16 = BF16;
-    static constexpr bool kAMajorMN = true;
+    static constexpr bool kAMajorMN = !TRANSPOSED;
 
+    // k0: offset along the reduction dimension, n0: first of the CTA's 128 output rows
     static __device__ __forceinline__ void issue_raw(const Params& p, uint32_t dst, uint32_t bar, int k0, int n0) {
         ptx::mbar_arrive_expect_tx(bar, kWBytes + 2 * kScaleRows * 256);
-        ptx::tma_load_2d(dst, &p.map_w, n0, k0 / 2, bar);
-        ptx::tma_load_2d(dst + kWBytes, &p.map_s, n0, k0 >> GSHIFT, bar);
-        ptx::tma_load_2d(dst + kWBytes + 1024, &p.map_z, n0, k0 >> GSHIFT, bar);
+        const int col = TRANSPOSED ? k0 : n0;     // position along N (the bytes' fast dimension)
+        const int kk = TRANSPOSED ? n0 : k0;      // position along K (two per byte row, one scale row per group)
+        ptx::tma_load_2d(dst, &p.map_w, col, kk / 2, bar);
+        ptx::tma_load_2d(dst + kWBytes, &p.map_s, col, kk >> GSHIFT, bar);
+        ptx::tma_load_2d(dst + kWBytes + 1024, &p.map_z, col, kk >> GSHIFT, bar);
     }
 
     static __device__ __forceinline__ void dequant(uint32_t raw, uint32_t a_tiles, int dw, int lane) {
@@ -75,11 +80,19 @@ struct HqqPolicy {
                 lo[i] = fma2<BF16>(fma2<BF16>(lo[i], one2, moff), s[i], nzs[i]);
                 hi[i] = fma2<BF16>(fma2<BF16>(hi[i], one2, moff), s[i], nzs[i]);
             }
-            // operand tile of this 64-k block, MN-major: [n block of 64][k group of 8][k % 8][chunk ^ (k % 8)]
-            const int kl = (2 * r) & 63, kg = kl >> 3, kr = kl & 7;
-            const uint32_t t = a_tiles + (r >> 5) * kABytes + blk_off + kg * 1024;
-            ptx::sts128(t + kr * 128 + ((cc ^ kr) << 4), lo[0], lo[1], lo[2], lo[3]);
-            ptx::sts128(t + (kr + 1) * 128 + ((cc ^ (kr + 1)) << 4), hi[0], hi[1], hi[2], hi[3]);
+            if constexpr (TRANSPOSED) {
+                // K-major tile of the 64 reduction elements that hold n = 8c..: rows are k = 2r, 2r + 1
+                const uint32_t t = a_tiles + (c >> 3) * kABytes;
+                const int row = 2 * r;
+                ptx::sts128(t + row * 128 + ((cc ^ (row & 7)) << 4), lo[0], lo[1], lo[2], lo[3]);
+                ptx::sts128(t + (row + 1) * 128 + ((cc ^ ((row + 1) & 7)) << 4), hi[0], hi[1], hi[2], hi[3]);
+            } else {
+                // operand tile of this 64-k block, MN-major: [n block of 64][k group of 8][k % 8][chunk ^ (k % 8)]
+                const int kl = (2 * r) & 63, kg = kl >> 3, kr = kl & 7;
+                const uint32_t t = a_tiles + (r >> 5) * kABytes + blk_off + kg * 1024;
+                ptx::sts128(t + kr * 128 + ((cc ^ kr) << 4), lo[0], lo[1], lo[2], lo[3]);
+                ptx::sts128(t + (kr + 1) * 128 + ((cc ^ (kr + 1)) << 4), hi[0], hi[1], hi[2], hi[3]);
+            }
         }
     }
 
@@ -87,13 +100,13 @@ struct HqqPolicy {
     static __device__ __forceinline__ float row_scale(const Params&, int) { return 1.f; }
 };
 
-template <bool BF16>
+template <bool BF16, bool TRANSPOSED>
 static int launch_g(const Plan& P, int g, const Params& prm, cudaStream_t st) {
     switch (g) {
-        case 32: return launch_mt<HqqPolicy<5, BF16>>(P, prm, st);
-        case 64: return launch_mt<HqqPolicy<6, BF16>>(P, prm, st);
-        case 128: return launch_mt<HqqPolicy<7, BF16>>(P, prm, st);
-        default: return launch_mt<HqqPolicy<8, BF16>>(P, prm, st);
+        case 32: return launch_mt<HqqPolicy<5, BF16, TRANSPOSED>>(P, prm, st);
+        case 64: return launch_mt<HqqPolicy<6, BF16, TRANSPOSED>>(P, prm, st);
+        case 128: return launch_mt<HqqPolicy<7, BF16, TRANSPOSED>>(P, prm, st);
+        default: return launch_mt<HqqPolicy<8, BF16, TRANSPOSED>>(P, prm, st);
     }
 }
 
@@ -101,6 +114,14 @@ static bool hqq_shape_ok(int64_t M, int64_t N, int64_t K, int g) {
     if (M < 1 || N < kRows || N % 16 != 0 || K % 128 != 0 || K < 128) return false;
     if (!(g == 32 || g == 64 || g == 128 || g == 256) || K % g != 0) return false;
     if (M > (1 << 30) || N > (1 << 30) || K > (1 << 24)) return false;
+    return true;
+}
+
+// transposed form: output rows = K (>= 128, a multiple of the group), reduction = N (a multiple of 128)
+static bool hqq_transposed_shape_ok(int64_t M, int64_t N, int64_t K, int g) {
+    if (M < 1 || K < kRows || K % 2 != 0 || N % 128 != 0 || N < 128) return false;
+    if (!(g == 32 || g == 64 || g == 128 || g == 256) || K % g != 0) return false;
+    if (M > (1 << 30) || N > (1 << 24) || K > (1 << 30)) return false;
     return true;
 }
 
@@ -149,5 +170,52 @@ extern "C" int ao_hqq_int4_linear(const void* a, int a_dtype, int64_t a_row_stri
     prm.N = (int)N;
     prm.K = (int)K;
     cudaStream_t st = as_stream(stream);
-    return bf16 ? umma::launch_g<true>(P, group, prm, st) : umma::launch_g<false>(P, group, prm, st);
+    return bf16 ? umma::launch_g<true, false>(P, group, prm, st) : umma::launch_g<false, false>(P, group, prm, st);
+}
+
+// transposed=True of the reference: c[M][K] = a[M][N] @ ((q - zeros) * scales)[N][K]^T-free form, i.e. the reduction
+// runs along N.  Same operands as ao_hqq_int4_linear.
+extern "C" size_t ao_hqq_int4_linear_transposed_workspace_bytes(int64_t M, int64_t N, int64_t K, int group) {
+    umma::Plan P;
+    if (!umma::hqq_transposed_shape_ok(M, N, K, group) || !umma::make_plan(M, K, N, &P)) return 0;
+    return P.ws_bytes;
+}
+
+extern "C" int ao_hqq_int4_linear_transposed(const void* a, int a_dtype, int64_t a_row_stride, const uint8_t* b_packed,
+                                             const void* scales, const void* zeros, int64_t M, int64_t N, int64_t K,
+                                             int group, void* c, void* workspace, size_t workspace_bytes,
+                                             ao_stream_t stream) {
+    if (M == 0 || K == 0) return AO_OK;
+    if (a_dtype != AO_BF16 && a_dtype != AO_F16) return AO_ERR_DTYPE;
+    if (!umma::hqq_transposed_shape_ok(M, N, K, group)) return AO_ERR_SHAPE;
+    umma::Plan P;
+    if (!umma::make_plan(M, K, N, &P)) return AO_ERR_UNSUPPORTED;
+    if (!aligned(a, 16) || (a_row_stride * 2) % 16 != 0 || a_row_stride < N || !aligned(b_packed, 16) ||
+        !aligned(scales, 16) || !aligned(zeros, 16) || !aligned(c, 2))
+        return AO_ERR_ALIGN;
+    if (workspace == nullptr || workspace_bytes < P.ws_bytes || !aligned(workspace, 256)) return AO_ERR_WORKSPACE;
+    const bool bf16 = a_dtype == AO_BF16;
+    umma::Params prm{};
+    const uint32_t scale_rows = umma::kRows / group > 0 ? umma::kRows / group : 1;
+    const CUtensorMapDataType dt16 = bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    if (!umma::make_x_map(&prm.map_x, bf16, a, N, M, a_row_stride, P.MT)) return AO_ERR_LAUNCH;
+    // boxes: 128 reduction bytes x 64 byte rows (= the CTA's 128 k); scale rows of the CTA's groups x 128 n
+    if (!make_tensor_map_2d(&prm.map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, b_packed, (uint64_t)N, (uint64_t)(K / 2), (uint64_t)N,
+                            umma::kRawK, umma::kRows / 2))
+        return AO_ERR_LAUNCH;
+    if (!make_tensor_map_2d(&prm.map_s, dt16, scales, (uint64_t)N, (uint64_t)(K / group), (uint64_t)N * 2, umma::kRawK,
+                            scale_rows))
+        return AO_ERR_LAUNCH;
+    if (!make_tensor_map_2d(&prm.map_z, dt16, zeros, (uint64_t)N, (uint64_t)(K / group), (uint64_t)N * 2, umma::kRawK,
+                            scale_rows))
+        return AO_ERR_LAUNCH;
+    prm.w = b_packed;
+    prm.scale = scales;
+    prm.y = c;
+    prm.ws = static_cast<uint8_t*>(workspace);
+    prm.M = (int)M;
+    prm.N = (int)K;   // output rows of the pipeline
+    prm.K = (int)N;   // its reduction length
+    cudaStream_t st = as_stream(stream);
+    return bf16 ? umma::launch_g<true, true>(P, group, prm, st) : umma::launch_g<false, true>(P, group, prm, st);
 }

@@ -43,18 +43,21 @@ def mixed_mm(a, b, scales, zeros, group_size, transposed=False, acc_dtype=None, 
     a: bf16 / fp16 [M][K];  b: uint8 [K/2][N] from pack_2xint4;  scales, zeros: [K/group_size][N] in a's dtype
     (any strides: a transposed view of an [N][K/group_size] tensor is accepted, as the reference's tests pass it).
     The tuning arguments of the Triton version (acc_dtype, input_precision, fp8_fast_accum, kernel_type, BLOCK_*)
-    are accepted and ignored: the tcgen05 kernel picks its own tiles.  transposed=True (the backward form) is not
-    implemented."""
-    if transposed:
-        raise NotImplementedError("mixed_mm: transposed=True is not implemented")
+    are accepted and ignored: the tcgen05 kernel picks its own tiles.  transposed=True is the backward form
+    (M x N) x (K x N) -> (M x K): a is [M][N] and the reduction runs along N."""
     _cabi.require_cuda(a, b, scales, zeros)
     assert b.dtype == torch.int8 or b.dtype == torch.uint8, "b must be int8 or uint8"
     assert a.dim() == 2 and b.dim() == 2 and scales.ndim == 2
-    assert a.shape[1] == b.shape[0] * 2, "incompatible dimensions"
+    if not transposed:
+        assert a.shape[1] == b.shape[0] * 2, "incompatible dimensions"
+    else:
+        assert a.shape[1] == b.shape[1], "transpose requires (M x N) x (K x N), where reduction dim is N"
     assert scales.dtype == a.dtype
     assert scales.shape == zeros.shape
     assert zeros.dtype == a.dtype
     torch._check(a.dtype in (torch.bfloat16, torch.float16), lambda: "mixed_mm: a must be bfloat16 or float16")
+    if transposed:
+        return _mixed_mm_transposed(a, b, scales, zeros, group_size)
     M, K = a.shape
     N = b.shape[1]
     torch._check(scales.shape == (K // group_size, N),
@@ -76,6 +79,29 @@ def mixed_mm(a, b, scales, zeros, group_size, transposed=False, acc_dtype=None, 
                                     _cabi.ptr(zeros), M, N, K, group_size, _cabi.ptr(c), _cabi.ptr(ws), ws.numel(),
                                     _cabi.stream_ptr(a.device))
     _cabi.check(rc, "mixed_mm")
+    return c
+
+
+def _mixed_mm_transposed(a, b, scales, zeros, group_size):
+    M, N = a.shape
+    K = b.shape[0] * 2
+    torch._check(scales.shape == (K // group_size, N),
+                 lambda: f"scales must be [K/group_size][N] = {(K // group_size, N)}, got {tuple(scales.shape)}")
+    if a.stride(1) != 1 or a.stride(0) % 8 != 0 or a.data_ptr() % 16 != 0:
+        a = a.contiguous()
+    b, scales, zeros = b.contiguous(), scales.contiguous(), zeros.contiguous()
+    c = torch.empty((M, K), device=a.device, dtype=a.dtype)
+    if M == 0:
+        return c
+    lib = _cabi.lib()
+    nbytes = lib.ao_hqq_int4_linear_transposed_workspace_bytes(M, N, K, group_size)
+    torch._check(nbytes > 0, lambda: f"mixed_mm(transposed): unsupported shape M={M} N={N} K={K} group_size={group_size}")
+    with torch.cuda.device(a.device):
+        ws = _cabi.workspace(nbytes, a.device)
+        rc = lib.ao_hqq_int4_linear_transposed(_cabi.ptr(a), _cabi.dtype_code(a.dtype), a.stride(0), _cabi.ptr(b),
+                                               _cabi.ptr(scales), _cabi.ptr(zeros), M, N, K, group_size, _cabi.ptr(c),
+                                               _cabi.ptr(ws), ws.numel(), _cabi.stream_ptr(a.device))
+    _cabi.check(rc, "mixed_mm(transposed)")
     return c
 
 

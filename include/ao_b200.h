@@ -243,6 +243,15 @@ int ao_hqq_int4_linear(const void* a, int a_dtype, int64_t a_row_stride, const u
                        const void* scales, const void* zeros, int64_t M, int64_t N, int64_t K, int group,
                        void* c, void* workspace, size_t workspace_bytes, ao_stream_t stream);
 
+/* The transposed form of triton_mixed_mm (transposed=True, used for the backward pass): c[M][K] = a[M][N] @ W[N][K]
+ * with the same b_packed [K/2][N], scales and zeros [K/group][N]; the reduction runs along N.  N % 128 == 0,
+ * K >= 128, K % group == 0. */
+size_t ao_hqq_int4_linear_transposed_workspace_bytes(int64_t M, int64_t N, int64_t K, int group);
+int ao_hqq_int4_linear_transposed(const void* a, int a_dtype, int64_t a_row_stride, const uint8_t* b_packed,
+                                  const void* scales, const void* zeros, int64_t M, int64_t N, int64_t K,
+                                  int group, void* c, void* workspace, size_t workspace_bytes,
+                                  ao_stream_t stream);
+
 /* torchao::quant_llm_linear(3, 2, x, w, s, splitK) — torchao/ops.py:15-37, schema
  * torchao/csrc/fp6_llm.cpp:5-8, CUDA entry torchao/csrc/cuda/fp6_llm/fp6_linear.cu:139-196.
  * x fp16 [M][K] (row stride x_row_stride), packed uint8 [N][K*6/8] as produced by

@@ -71,8 +71,29 @@ def test_mixed_mm_argument_checks():
         mixed_mm(a[:, :128], b, s, s, 64)
     with pytest.raises(AssertionError):
         mixed_mm(a, b, s.half(), s.half(), 64)
-    with pytest.raises(NotImplementedError):
-        mixed_mm(a, b, s, s, 64, transposed=True)
+    with pytest.raises(AssertionError, match="transpose requires"):
+        mixed_mm(a[:, :100], b, s, s, 64, transposed=True)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16], ids=["bf16", "fp16"])
+@pytest.mark.parametrize("group_size", [32, 64, 128, 256])
+@pytest.mark.parametrize("shape", [(16, 128, 256), (16, 4096, 4096), (100, 1024, 2048), (300, 512, 1024)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_mixed_mm_transposed(shape, group_size, dtype):
+    """transposed=True: (M x N) x (K x N) -> (M x K), reduction along N (test/hqq/test_triton_mm.py:115-127)."""
+    from ao_b200.prototype.hqq import pack_2xint4, triton_mixed_mm
+    M, N, K = shape
+    g = torch.Generator(device="cuda").manual_seed(M + N + K + group_size)
+    W_q = torch.randint(0, 16, (N, K), dtype=torch.uint8, device="cuda", generator=g)
+    scales = (torch.rand(N, K // group_size, device="cuda", generator=g) * 0.01 + 0.002).to(dtype)
+    zeros = (torch.rand(N, K // group_size, device="cuda", generator=g) * 15).to(dtype)
+    x = torch.randn(M, N, device="cuda", generator=g).to(dtype)
+    out = triton_mixed_mm(x, pack_2xint4(W_q.T), scales.T, zeros.T, transposed=True, group_size=group_size)
+    assert out.shape == (M, K) and out.dtype == dtype
+    s = scales.float().repeat_interleave(group_size, dim=1)
+    z = zeros.float().repeat_interleave(group_size, dim=1)
+    ref = x.float() @ ((W_q.float() - z) * s)
+    assert float((out.float() - ref).abs().max() / ref.abs().max()) <= 1e-2
 
 
 @pytest.mark.parametrize("key", ["bf16_g64", "bf16_g128", "f16_g64", "f16_g128"])
