@@ -150,3 +150,22 @@ def test_clone_makes_independent_storage():
     assert torch.equal(c.layout_tensor.packed_weight, w.layout_tensor.packed_weight)
     x = torch.randn(2, 1024, device="cuda", dtype=torch.bfloat16)
     assert torch.equal(torch.nn.functional.linear(x, c), lin(x))
+
+
+def test_dispatcher_ops_opcheck():
+    """torch.ops.ao_b200.*: schema, fake-tensor and dispatch checks (test/test_ops.py:24-45 of the reference)."""
+    import ao_b200._torch_ops  # noqa: F401
+    from ao_b200 import ops
+    from torch.library import opcheck
+    utils = ["test_schema", "test_autograd_registration", "test_faketensor"]
+    w = torch.randint(256, (256, 512 // 8 * 6), dtype=torch.uint8, device="cuda")
+    s = torch.rand(256, dtype=torch.float16, device="cuda") + 0.5
+    x = torch.rand(5, 512, dtype=torch.float16, device="cuda") + 0.5
+    opcheck(torch.ops.ao_b200.quant_llm_linear, (3, 2, x, w, s, 1), test_utils=utils)
+    assert torch.equal(torch.ops.ao_b200.quant_llm_linear(3, 2, x, w, s, 1), ops.quant_llm_linear(3, 2, x, w, s, 1))
+    codes = torch.randint(0, 16, (64, 1024), dtype=torch.int32, device="cuda")
+    opcheck(torch.ops.ao_b200.convert_weight_to_int4pack, (codes, 8), test_utils=utils)
+    packed = torch.ops.ao_b200.convert_weight_to_int4pack(codes, 8)
+    sz = torch.rand(1024 // 64, 64, 2, device="cuda").bfloat16()
+    xb = torch.randn(3, 1024, device="cuda").bfloat16()
+    opcheck(torch.ops.ao_b200.weight_int4pack_mm, (xb, packed, 64, sz), test_utils=utils)
