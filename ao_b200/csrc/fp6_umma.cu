@@ -33,18 +33,19 @@ struct Fp6Policy {
         }
     }
 
-    // warp dw takes k16 tile (dw % 8) of 64-row block (dw / 8): 4 fragments of 16 rows
-    static __device__ __forceinline__ void dequant(uint32_t raw, uint32_t a_tiles, int dw, int lane) {
+    // 16 units = (k16 tile, 64-row block) of 4 fragments of 16 rows each, dealt to the GW warps of a group
+    template <int GW>
+    static __device__ __forceinline__ void dequant(uint32_t raw, uint32_t a_tiles, int wi, int lane) {
         const uint32_t m4 = 0x0F000F00u, mh = 0x90009000u, f_hi = 0x00C000C0u, f_lo = 0x00300030u;
         const uint32_t k_hi = 0x140u, k_lo = 0x500u;
-        const int j = dw & 7;
         // stmatrix: lane 8i + rr gives row rr of matrix i; matrix i = rows (i & 1) * 8.., k chunk (i >> 1)
         const int i = lane >> 3, rr = lane & 7;
-        const int chunk = (j & 3) * 2 + (i >> 1);
-        const uint32_t st_lane = ((i & 1) * 8 + rr) * 128 + ((chunk ^ rr) << 4);
-        const uint32_t tile = a_tiles + (j >> 2) * kABytes;
-        {
-            const int blk = dw >> 3;
+#pragma unroll
+        for (int u = wi; u < 16; u += GW) {
+            const int j = u & 7, blk = u >> 3;
+            const int chunk = (j & 3) * 2 + (i >> 1);
+            const uint32_t st_lane = ((i & 1) * 8 + rr) * 128 + ((chunk ^ rr) << 4);
+            const uint32_t tile = a_tiles + (j >> 2) * kABytes;
             const uint32_t p2 = raw + blk * kBlk + j * 256 + lane * 4;
             const uint32_t p4 = raw + blk * kBlk + kP2 + j * 512 + lane * 4;
 #pragma unroll

@@ -41,21 +41,22 @@ struct HqqPolicy {
         ptx::tma_load_2d(dst + kWBytes + 1024, &p.map_z, col, kk >> GSHIFT, bar);
     }
 
-    static __device__ __forceinline__ void dequant(uint32_t raw, uint32_t a_tiles, int dw, int lane) {
+    template <int GW>
+    static __device__ __forceinline__ void dequant(uint32_t raw, uint32_t a_tiles, int wi, int lane) {
         // 128 + q (bf16) or 1024 + q (fp16), exact; minus the offset gives q
         const uint32_t nib = 0x000F000Fu;
         const uint32_t magic = BF16 ? 0x43004300u : 0x64006400u;
         const uint32_t one2 = BF16 ? 0x3F803F80u : 0x3C003C00u;
         const uint32_t moff = BF16 ? 0xC300C300u : 0xE400E400u;
-        const int td = dw * 32 + lane;    // 512 threads, two items each
+        const int td = wi * 32 + lane;    // GW * 32 threads share the 1024 items (64 byte rows x 16 chunks)
         const int c = td & 15;            // 8-byte chunk of the 128 n: n = 8c .. 8c + 7
-        const int r_lo = td >> 4;         // byte row inside a group of 32
+        const int r_lo = td >> 4;         // byte row inside a group of GW * 2
         const uint32_t sc_addr = raw + kWBytes + c * 16;
         const uint32_t blk_off = (c >> 3) * 8192;   // 64-wide n block
         const int cc = c & 7;
 #pragma unroll
-        for (int q = 0; q < 2; ++q) {
-            const int r = q * 32 + r_lo;   // byte row 0..63: k = 2r, 2r + 1 of the 128-k stage
+        for (int q = 0; q < 32 / GW; ++q) {
+            const int r = q * (GW * 2) + r_lo;   // byte row 0..63: k = 2r, 2r + 1 of the 128-k stage
             uint32_t s[4], nzs[4];
             {
                 const int gi = GSHIFT >= 7 ? 0 : (2 * r) >> GSHIFT;

@@ -34,14 +34,16 @@ struct TinygemmPolicy {
         ptx::tma_load_2d(dst + kWBytes, &p.map_s, n0, k0 >> GSHIFT, bar);
     }
 
-    static __device__ __forceinline__ void dequant(uint32_t raw, uint32_t a_tiles, int dw, int lane) {
+    template <int GW>
+    static __device__ __forceinline__ void dequant(uint32_t raw, uint32_t a_tiles, int wi, int lane) {
         const uint32_t nib = 0x000F000Fu, magic = 0x43004300u, one2 = 0x3F803F80u, m136 = 0xC308C308u;
         // stmatrix row addresses: lane 8i + j gives row j of matrix i (k chunk i of the word's 32 k)
         const int st_r = lane & 7, st_c = lane >> 3;
         const uint32_t st_off0 = st_r * 128 + ((st_c ^ st_r) << 4);          // word 0 of a 64-k block: chunks 0..3
         const uint32_t st_off1 = st_r * 128 + (((st_c + 4) ^ st_r) << 4);    // word 1: chunks 4..7
-        {
-            const int tile = dw;   // one tile of 8 rows x 128 k per warp
+#pragma unroll
+        for (int tt = 0; tt < 16 / GW; ++tt) {
+            const int tile = wi * (16 / GW) + tt;   // tiles of 8 rows x 128 k
             const uint4 w4 = ptx::lds128(raw + tile * 512 + lane * 16);
             const uint32_t w[4] = {w4.x, w4.y, w4.z, w4.w};
             const uint32_t sc_addr = raw + kWBytes + tile * 32 + (lane >> 2) * 4;

@@ -9,8 +9,8 @@
 //   warp 2     owns the tensor memory and issues the MMAs: four K=16 instructions per operand stage, then a
 //              commit that frees the stage;
 //   warps 3-18 dequantise raw bytes in registers and write the 16-bit operand tile (layout chosen by the weight
-//              format's policy); after the K loop the same warps read the accumulator from tensor memory and
-//              store y.
+//              format's policy), in groups that take alternate iterations whole; after the K loop the same warps
+//              read the accumulator from tensor memory and store y.
 // When the tiles alone would leave SMs idle, K is cut into slabs over gridDim.z; fp32 partial tiles meet in the
 // workspace and the CTA that completes a tile (atomic counter) adds them in slab order (deterministic).
 // Every wait is bounded; a wait that runs out sets the status word and the CTA still frees its tensor memory.
@@ -20,7 +20,8 @@
 //   kBF16                          operands are bf16 (else fp16); y has the same type
 //   kAMajorMN                      the dequantised operand tile is MN-major (else K-major), both 128-byte swizzle
 //   issue_raw(p, dst, bar, k0, n0) one thread: expect_tx + the async copies of a raw stage
-//   dequant(raw, a_tiles, dw, lane) 16 warps: raw stage -> two consecutive 16 KiB operand tiles (k 0..63, 64..127)
+//   dequant<GW>(raw, a_tiles, wi, lane) warp wi of a group of GW warps: raw stage -> two consecutive 16 KiB
+//                                  operand tiles (k 0..63, 64..127)
 //   out_row(lane_row)              weight row (inside the CTA's 128) that tensor-memory lane `lane_row` holds
 //   row_scale(p, n)                factor applied to the accumulator of weight row n
 #pragma once
@@ -65,9 +66,13 @@ struct Cfg {
     // dequantised byte to the commit that frees the stage
     static constexpr int SA = MT <= 64 ? 8 : 4;
     static constexpr int SAShift = MT <= 64 ? 3 : 2;
+    // dequant warp groups: each group takes every NG-th iteration whole, so that the latency of one iteration
+    // (copy wait, dequant, proxy fence, barrier) overlaps with the other groups' iterations; 2 * NG <= SA
+    static constexpr int NG = MT <= 64 ? 4 : 2;
+    static constexpr int GW = kDequantWarps / NG;
     static constexpr int Fixed = 1024 + SA * kABytes + SX * XBytes + 512;
     static constexpr int Rfit = (kSmemLimit - Fixed) / Policy::kRawBytes;
-    static constexpr int R = Rfit > 4 ? 4 : Rfit;         // raw stages
+    static constexpr int R = Rfit > 8 ? 8 : Rfit;         // raw stages (each covers 128 k; the ring covers the copy latency)
     static_assert(R >= 2, "raw ring needs two stages");
     static constexpr int TmemCols = MT < 32 ? 32 : MT;
     static constexpr int SmemBytes = Fixed + R * Policy::kRawBytes;
@@ -117,7 +122,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_kernel(const __grid_c
     const uint32_t a_base = base, x_base = a_base + kS * kABytes, raw_base = x_base + SX * C::XBytes;
     const uint32_t bar_base = raw_base + R * Policy::kRawBytes;
     const uint32_t full_a = bar_base, empty = full_a + 8 * kS, full_x = empty + 8 * kS, x_empty = full_x + 8 * SX;
-    const uint32_t raw_full = x_empty + 8 * SX, raw_empty = raw_full + 8 * 4, acc_full = raw_empty + 8 * 4;
+    const uint32_t raw_full = x_empty + 8 * SX, raw_empty = raw_full + 8 * 8, acc_full = raw_empty + 8 * 8;
     const uint32_t tmem_slot = acc_full + 8, flag_slot = tmem_slot + 4;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int M = p.M, N = p.N;
@@ -130,7 +135,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_kernel(const __grid_c
 
     if (tid == 0) {
         for (int s = 0; s < kS; ++s) {
-            ptx::mbar_init(full_a + 8 * s, kDequantWarps);
+            ptx::mbar_init(full_a + 8 * s, C::GW);
             ptx::mbar_init(empty + 8 * s, 1);
         }
         for (int s = 0; s < SX; ++s) {
@@ -139,7 +144,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_kernel(const __grid_c
         }
         for (int b = 0; b < R; ++b) {
             ptx::mbar_init(raw_full + 8 * b, 1);
-            ptx::mbar_init(raw_empty + 8 * b, kDequantWarps);
+            ptx::mbar_init(raw_empty + 8 * b, C::GW);
         }
         ptx::mbar_init(acc_full, 1);
         ptx::fence_mbar_init();
@@ -212,9 +217,10 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_kernel(const __grid_c
     } else {
         // ---------------- dequantise (128 rows x 128 k per iteration), then epilogue ----------------
         const int dw = warp - 3;
-        int rb = 0;
-        uint32_t rph = 0;
-        for (int it = 0; it < nit && ok; ++it) {
+        const int grp = dw / C::GW, wi = dw % C::GW;
+        for (int it = grp; it < nit && ok; it += C::NG) {
+            const int rb = it % R;
+            const uint32_t rph = static_cast<uint32_t>(it / R) & 1u;
             const int s0 = (2 * it) & (kS - 1);
             const uint32_t eph = (static_cast<uint32_t>(it >> (C::SAShift - 1)) & 1u) ^ 1u;
             if (!ptx::mbar_wait_bounded(raw_full + 8 * rb, rph, kWaitPolls) ||
@@ -223,17 +229,13 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_kernel(const __grid_c
                 ok = false;
                 break;
             }
-            Policy::dequant(raw_base + rb * Policy::kRawBytes, a_base + s0 * kABytes, dw, lane);
+            Policy::template dequant<C::GW>(raw_base + rb * Policy::kRawBytes, a_base + s0 * kABytes, wi, lane);
             ptx::fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
                 ptx::mbar_arrive(full_a + 8 * s0);
                 ptx::mbar_arrive(full_a + 8 * (s0 + 1));
                 ptx::mbar_arrive(raw_empty + 8 * rb);
-            }
-            if (++rb == R) {
-                rb = 0;
-                rph ^= 1u;
             }
         }
         // ---------------- epilogue: lane quarter (warp % 4) x column quarter (dw / 4) ----------------
