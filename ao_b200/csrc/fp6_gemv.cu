@@ -51,11 +51,11 @@ struct Plan {
     int nbuf;          // ring of per-row-block partial-sum buffers (a power of two)
     int stage_shift, nbuf_shift;  // log2 of stages and nbuf: no divisions in the per-stage bookkeeping
     int xs_off, zero_off, part_off, bar_off, smem_bytes;
-    uint32_t m4, mh, f_hi, f_lo, k_hi, k_lo;  // masks / multipliers as runtime values (kept in registers)
+    Format fmt;        // decode constants of the 6-bit format, runtime values (kept in registers)
     size_t ws_counters_off, ws_slots_off, ws_bytes;
 };
 
-static int make_plan(int64_t M, int64_t N, int64_t K, Plan* P) {
+static int make_plan(int64_t M, int64_t N, int64_t K, bool e2m3, Plan* P) {
     if (M < 1 || M > 16) return AO_ERR_SHAPE;
     if (N < 64 || N % 64 != 0 || K < 64 || K % 64 != 0) return AO_ERR_SHAPE;
     if (N > 64 * kMaxBlocks || K > (1 << 22)) return AO_ERR_SHAPE;
@@ -128,12 +128,7 @@ static int make_plan(int64_t M, int64_t N, int64_t K, Plan* P) {
     P->bar_off = off;
     off += 2 * kMaxStages * 8 + 2 * kMaxBlockBufs * 8;
     P->smem_bytes = off;
-    P->m4 = 0x0F000F00u;
-    P->mh = 0x90009000u;
-    P->f_hi = 0x00C000C0u;
-    P->f_lo = 0x00300030u;
-    P->k_hi = 0x140u;   // 2^8 + 2^6
-    P->k_lo = 0x500u;   // 2^10 + 2^8
+    P->fmt = e2m3 ? format_e2m3() : format_e3m2();
     P->ws_counters_off = kHeaderBytes;
     P->ws_slots_off = kHeaderBytes + (size_t)kMaxBlocks * 4;
     P->ws_bytes = P->ws_slots_off + (best > 1 ? (size_t)best * P->NA * 4 * P->NB * 512 : 0);
@@ -148,7 +143,7 @@ __device__ __forceinline__ void store_block(const Plan& P, const float (&v)[4][N
 #pragma unroll
     for (int fr = 0; fr < 4; ++fr) {
         const int n0 = a * 64 + fr * 16 + row, n1 = n0 + 8;
-        const float s0 = 4096.f * __half2float(scale[n0]), s1 = 4096.f * __half2float(scale[n1]);
+        const float s0 = P.fmt.post_scale * __half2float(scale[n0]), s1 = P.fmt.post_scale * __half2float(scale[n1]);
 #pragma unroll
         for (int nb = 0; nb < NB; ++nb) {
             const int m0 = nb * 8 + 2 * c;
@@ -352,7 +347,7 @@ fp6_gemv_kernel(const __half* __restrict__ x, long long ldx, const uint8_t* __re
     const bool x_lane = lane < MRL;
     const uint32_t x_base = x_lane ? smem_base + P.xs_off + lane * 8 : smem_base + P.zero_off;
     const uint32_t x_tile_stride = x_lane ? static_cast<uint32_t>(XT) : 0u;
-    const uint32_t m4 = P.m4, mh = P.mh, f_hi = P.f_hi, f_lo = P.f_lo, k_hi = P.k_hi, k_lo = P.k_lo;
+    const Format fmt = P.fmt;
     float4* parts = reinterpret_cast<float4*>(smem + P.part_off);
     const int grp = warp / kGroupWarps, wi = warp - grp * kGroupWarps;
     float acc[4][NB][4];
@@ -394,7 +389,7 @@ fp6_gemv_kernel(const __half* __restrict__ x, long long ldx, const uint8_t* __re
                     for (int cc = 0; cc < 2; ++cc) {
                         const uint32_t w4 = ptx::lds32(p4 + (b * 2 + cc) * 128);
                         uint32_t a[4];
-                        decode_fragment(w4, cc == 0 ? w2 : (w2 << 4), m4, mh, f_hi, f_lo, k_hi, k_lo, a);
+                        decode_fragment(w4, cc == 0 ? w2 : (w2 << 4), fmt, a);
 #pragma unroll
                         for (int nb = 0; nb < NB; ++nb)
                             ptx::mma_f16_16816(acc[b * 2 + cc][nb], a[0], a[1], a[2], a[3], xb[nb].x, xb[nb].y);
@@ -457,36 +452,38 @@ static int launch(const Plan& P, const void* x, long long ldx, const void* wq, c
 namespace ao {
 namespace umma {
 size_t fp6_umma_workspace_bytes(int64_t M, int64_t N, int64_t K);
-int fp6_umma_linear(const void* x, int64_t ldx, const uint8_t* packed, const void* scale, int64_t M, int64_t N, int64_t K,
-                    void* y, void* ws, size_t ws_bytes, cudaStream_t st);
+int fp6_umma_linear(bool e2m3, const void* x, int64_t ldx, const uint8_t* packed, const void* scale, int64_t M, int64_t N,
+                    int64_t K, void* y, void* ws, size_t ws_bytes, cudaStream_t st);
 }  // namespace umma
 }  // namespace ao
 
 using namespace ao;
+using ao::fp6::Format;
+
+namespace {
 
 // A 9..16-row call whose activations and partial sums cannot share one SM's shared memory with the stage ring
 // runs as two calls of at most 8 rows.
-extern "C" size_t ao_fp6_gemv_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+size_t gemv_workspace_bytes(int64_t M, int64_t N, int64_t K) {
     fp6::Plan P;
-    int rc = fp6::make_plan(M, N, K, &P);
+    int rc = fp6::make_plan(M, N, K, false, &P);
     if (rc == AO_ERR_UNSUPPORTED && M > 8) {
-        const size_t a = ao_fp6_gemv_workspace_bytes(8, N, K), b = ao_fp6_gemv_workspace_bytes(M - 8, N, K);
+        const size_t a = gemv_workspace_bytes(8, N, K), b = gemv_workspace_bytes(M - 8, N, K);
         return a == 0 || b == 0 ? 0 : (a > b ? a : b);
     }
     return rc == AO_OK ? P.ws_bytes : 0;
 }
 
-extern "C" int ao_fp6_gemv(const void* x_f16, int64_t x_row_stride, const uint8_t* packed, const void* scale_f16,
-                           int64_t M, int64_t N, int64_t K, void* y_f16, void* workspace, size_t workspace_bytes,
-                           ao_stream_t stream) {
+int gemv(bool e2m3, const void* x_f16, int64_t x_row_stride, const uint8_t* packed, const void* scale_f16, int64_t M,
+         int64_t N, int64_t K, void* y_f16, void* workspace, size_t workspace_bytes, ao_stream_t stream) {
     if (M == 0 || N == 0) return AO_OK;
     fp6::Plan P;
-    int rc = fp6::make_plan(M, N, K, &P);
+    int rc = fp6::make_plan(M, N, K, e2m3, &P);
     if (rc == AO_ERR_UNSUPPORTED && M > 8) {
-        rc = ao_fp6_gemv(x_f16, x_row_stride, packed, scale_f16, 8, N, K, y_f16, workspace, workspace_bytes, stream);
+        rc = gemv(e2m3, x_f16, x_row_stride, packed, scale_f16, 8, N, K, y_f16, workspace, workspace_bytes, stream);
         if (rc) return rc;
-        return ao_fp6_gemv(static_cast<const __half*>(x_f16) + 8 * x_row_stride, x_row_stride, packed, scale_f16, M - 8, N,
-                           K, static_cast<__half*>(y_f16) + 8 * N, workspace, workspace_bytes, stream);
+        return gemv(e2m3, static_cast<const __half*>(x_f16) + 8 * x_row_stride, x_row_stride, packed, scale_f16, M - 8, N, K,
+                    static_cast<__half*>(y_f16) + 8 * N, workspace, workspace_bytes, stream);
     }
     if (rc) return rc;
     if (x_row_stride < K || x_row_stride % 2 != 0) return AO_ERR_SHAPE;
@@ -505,40 +502,65 @@ extern "C" int ao_fp6_gemv(const void* x_f16, int64_t x_row_stride, const uint8_
     return AO_ERR_UNSUPPORTED;
 }
 
-// torchao::quant_llm_linear for e3m2: decode shapes go to the GEMV kernel, larger batches in row blocks of 16.
-extern "C" size_t ao_fp6_linear_workspace_bytes(int64_t M, int64_t N, int64_t K) {
-    if (M <= 8) return ao_fp6_gemv_workspace_bytes(M, N, K);
-    // larger batches: the tcgen05 kernel's need, and the decode kernel's for shapes that fall back to row blocks
+// decode shapes go to the GEMV kernel, larger batches to the tcgen05 kernel, the rest in row blocks of 16
+size_t linear_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+    if (M <= 8) return gemv_workspace_bytes(M, N, K);
     size_t need = umma::fp6_umma_workspace_bytes(M, N, K);
     for (int m = 1; m <= 16; m *= 2) {
-        const size_t b = ao_fp6_gemv_workspace_bytes(m, N, K);
+        const size_t b = gemv_workspace_bytes(m, N, K);
         if (b == 0) return 0;
         need = b > need ? b : need;
     }
     return need;
 }
 
-extern "C" int ao_fp6_linear(const void* x_f16, int64_t x_row_stride, const uint8_t* packed, const void* scale_f16,
-                             int64_t M, int64_t N, int64_t K, void* y_f16, void* workspace, size_t workspace_bytes,
-                             ao_stream_t stream) {
+int linear(bool e2m3, const void* x_f16, int64_t x_row_stride, const uint8_t* packed, const void* scale_f16, int64_t M,
+           int64_t N, int64_t K, void* y_f16, void* workspace, size_t workspace_bytes, ao_stream_t stream) {
     if (M < 0 || N < 0) return AO_ERR_SHAPE;
     if (M <= 8)
-        return ao_fp6_gemv(x_f16, x_row_stride, packed, scale_f16, M, N, K, y_f16, workspace, workspace_bytes, stream);
+        return gemv(e2m3, x_f16, x_row_stride, packed, scale_f16, M, N, K, y_f16, workspace, workspace_bytes, stream);
     if (workspace == nullptr || workspace_bytes < 256 || !aligned(workspace, 256)) return AO_ERR_WORKSPACE;
     {
-        const int rc = umma::fp6_umma_linear(x_f16, x_row_stride, packed, scale_f16, M, N, K, y_f16, workspace,
+        const int rc = umma::fp6_umma_linear(e2m3, x_f16, x_row_stride, packed, scale_f16, M, N, K, y_f16, workspace,
                                              workspace_bytes, as_stream(stream));
         if (rc != AO_ERR_UNSUPPORTED) return rc;
     }
     if (M <= 16)
-        return ao_fp6_gemv(x_f16, x_row_stride, packed, scale_f16, M, N, K, y_f16, workspace, workspace_bytes, stream);
+        return gemv(e2m3, x_f16, x_row_stride, packed, scale_f16, M, N, K, y_f16, workspace, workspace_bytes, stream);
     const auto* x = static_cast<const __half*>(x_f16);
     auto* y = static_cast<__half*>(y_f16);
     for (int64_t m0 = 0; m0 < M; m0 += 16) {
         const int64_t mb = M - m0 < 16 ? M - m0 : 16;
-        int rc = ao_fp6_gemv(x + m0 * x_row_stride, x_row_stride, packed, scale_f16, mb, N, K, y + m0 * N, workspace,
-                             workspace_bytes, stream);
+        int rc = gemv(e2m3, x + m0 * x_row_stride, x_row_stride, packed, scale_f16, mb, N, K, y + m0 * N, workspace,
+                      workspace_bytes, stream);
         if (rc) return rc;
     }
     return AO_OK;
+}
+
+}  // namespace
+
+extern "C" size_t ao_fp6_gemv_workspace_bytes(int64_t M, int64_t N, int64_t K) { return gemv_workspace_bytes(M, N, K); }
+
+extern "C" int ao_fp6_gemv(const void* x_f16, int64_t x_row_stride, const uint8_t* packed, const void* scale_f16,
+                           int64_t M, int64_t N, int64_t K, void* y_f16, void* workspace, size_t workspace_bytes,
+                           ao_stream_t stream) {
+    return gemv(false, x_f16, x_row_stride, packed, scale_f16, M, N, K, y_f16, workspace, workspace_bytes, stream);
+}
+
+// torchao::quant_llm_linear for e3m2
+extern "C" size_t ao_fp6_linear_workspace_bytes(int64_t M, int64_t N, int64_t K) { return linear_workspace_bytes(M, N, K); }
+
+extern "C" int ao_fp6_linear(const void* x_f16, int64_t x_row_stride, const uint8_t* packed, const void* scale_f16,
+                             int64_t M, int64_t N, int64_t K, void* y_f16, void* workspace, size_t workspace_bytes,
+                             ao_stream_t stream) {
+    return linear(false, x_f16, x_row_stride, packed, scale_f16, M, N, K, y_f16, workspace, workspace_bytes, stream);
+}
+
+// torchao::quant_llm_linear for the 6-bit formats: (EXPONENT, MANTISSA) = (3, 2) or (2, 3)
+extern "C" int ao_fpx_linear(int ebits, int mbits, const void* x_f16, int64_t x_row_stride, const uint8_t* packed,
+                             const void* scale_f16, int64_t M, int64_t N, int64_t K, void* y_f16, void* workspace,
+                             size_t workspace_bytes, ao_stream_t stream) {
+    if (!((ebits == 3 && mbits == 2) || (ebits == 2 && mbits == 3))) return AO_ERR_UNSUPPORTED;
+    return linear(ebits == 2, x_f16, x_row_stride, packed, scale_f16, M, N, K, y_f16, workspace, workspace_bytes, stream);
 }

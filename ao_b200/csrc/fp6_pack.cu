@@ -145,8 +145,9 @@ __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return
 // One CTA per 64 rows: pass 1 finds each row's absmax (scale = max(absmax, 1e-12) / max_normal in
 // fp32, quant_llm.py:126-127), pass 2 encodes w / scale and packs tile by tile.
 template <typename T>
-__global__ void __launch_bounds__(512) to_scaled_tc_fp6_kernel(const T* __restrict__ w, int64_t M, int64_t N,
-                                                               uint8_t* __restrict__ packed, __half* __restrict__ scale_out) {
+__global__ void __launch_bounds__(512) to_scaled_tc_fp6_kernel(const T* __restrict__ w, int64_t M, int64_t N, int ebits,
+                                                               int mbits, float max_normal, uint8_t* __restrict__ packed,
+                                                               __half* __restrict__ scale_out) {
     __shared__ __align__(16) uint8_t codes[64][kTileCols + kTilePad];
     __shared__ float s_scale[64];
     const int64_t a = blockIdx.x, F = N / 16;
@@ -157,7 +158,7 @@ __global__ void __launch_bounds__(512) to_scaled_tc_fp6_kernel(const T* __restri
         for (int64_t c = lane; c < N; c += 32) amax = fmaxf(amax, fabsf(to_f32<T>(row[c])));
         amax = warp_max(amax, 32);
         if (lane == 0) {
-            const float s = __fdiv_rn(fmaxf(amax, 1e-12f), 28.0f);
+            const float s = __fdiv_rn(fmaxf(amax, 1e-12f), max_normal);
             s_scale[r] = s;
             scale_out[a * 64 + r] = __float2half_rn(s);
         }
@@ -169,7 +170,7 @@ __global__ void __launch_bounds__(512) to_scaled_tc_fp6_kernel(const T* __restri
         for (int i = threadIdx.x; i < 64 * cols; i += blockDim.x) {
             const int r = i / cols, c = i % cols;
             const float v = __fdiv_rn(to_f32<T>(w[(a * 64 + r) * N + f0 * 16 + c]), s_scale[r]);
-            codes[r][c] = static_cast<uint8_t>(f32_to_fpx_bits(v, 3, 2));
+            codes[r][c] = static_cast<uint8_t>(f32_to_fpx_bits(v, ebits, mbits));
         }
         __syncthreads();
         emit_fp6_tile(codes, a, F, f0, nf, packed, packed + M * N / 4);
@@ -200,12 +201,13 @@ __global__ void __launch_bounds__(256) unpack_tc_fp6_kernel(const uint8_t* __res
 }
 
 __global__ void __launch_bounds__(256) from_scaled_tc_fp6_kernel(const uint8_t* __restrict__ packed, int64_t M, int64_t N,
-                                                                 const __half* __restrict__ scale, float* __restrict__ out) {
+                                                                 int ebits, int mbits, const __half* __restrict__ scale,
+                                                                 float* __restrict__ out) {
     const int64_t total = M * N, F = N / 16;
     const int64_t step = static_cast<int64_t>(gridDim.x) * blockDim.x;
     for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += step) {
         const int64_t row = i / N;
-        float v = fpx_bits_to_f32(fp6_code_at(packed, packed + total / 4, F, row, i % N), 3, 2);
+        float v = fpx_bits_to_f32(fp6_code_at(packed, packed + total / 4, F, row, i % N), ebits, mbits);
         if (scale) v = __fmul_rn(v, __half2float(scale[row]));
         out[i] = v;
     }
@@ -267,28 +269,47 @@ extern "C" int ao_unpack_tc_fp6(const uint8_t* packed, int64_t M, int64_t N, uin
     return launch_status();
 }
 
-extern "C" int ao_to_scaled_tc_fp6(const void* w, int w_dtype, int64_t M, int64_t N, uint8_t* packed_out,
-                                   void* scale_f16_out, ao_stream_t stream) {
+// largest finite value of a sign-magnitude ExMy format without inf / nan (custom_fp_utils.py:62-66)
+static float fpx_max_normal(int ebits, int mbits) {
+    const int exp_bias = (1 << (ebits - 1)) - 1;
+    return ldexpf(1.0f, ((1 << ebits) - 1) - exp_bias) * (static_cast<float>((1 << (mbits + 1)) - 1) / static_cast<float>(1 << mbits));
+}
+
+extern "C" int ao_to_scaled_tc_fpx(const void* w, int w_dtype, int64_t M, int64_t N, int ebits, int mbits,
+                                   uint8_t* packed_out, void* scale_f16_out, ao_stream_t stream) {
+    if (ebits < 1 || mbits < 0 || ebits + mbits != 5) return AO_ERR_UNSUPPORTED;   // 6-bit formats only
     int rc = check_tc_shape(M, N);
     if (rc) return rc;
     if (!aligned(packed_out, 4)) return AO_ERR_ALIGN;
     const unsigned grid = static_cast<unsigned>(M / 64);
     cudaStream_t st = as_stream(stream);
     auto* so = static_cast<__half*>(scale_f16_out);
+    const float mx = fpx_max_normal(ebits, mbits);
     switch (w_dtype) {
-        case AO_F32: to_scaled_tc_fp6_kernel<float><<<grid, 512, 0, st>>>(static_cast<const float*>(w), M, N, packed_out, so); break;
-        case AO_F16: to_scaled_tc_fp6_kernel<__half><<<grid, 512, 0, st>>>(static_cast<const __half*>(w), M, N, packed_out, so); break;
-        case AO_BF16: to_scaled_tc_fp6_kernel<__nv_bfloat16><<<grid, 512, 0, st>>>(static_cast<const __nv_bfloat16*>(w), M, N, packed_out, so); break;
+        case AO_F32: to_scaled_tc_fp6_kernel<float><<<grid, 512, 0, st>>>(static_cast<const float*>(w), M, N, ebits, mbits, mx, packed_out, so); break;
+        case AO_F16: to_scaled_tc_fp6_kernel<__half><<<grid, 512, 0, st>>>(static_cast<const __half*>(w), M, N, ebits, mbits, mx, packed_out, so); break;
+        case AO_BF16: to_scaled_tc_fp6_kernel<__nv_bfloat16><<<grid, 512, 0, st>>>(static_cast<const __nv_bfloat16*>(w), M, N, ebits, mbits, mx, packed_out, so); break;
         default: return AO_ERR_DTYPE;
     }
     return launch_status();
 }
 
-extern "C" int ao_from_scaled_tc_fp6(const uint8_t* packed, int64_t M, int64_t N, const void* scale_f16, float* out,
-                                     ao_stream_t stream) {
+extern "C" int ao_from_scaled_tc_fpx(const uint8_t* packed, int64_t M, int64_t N, int ebits, int mbits,
+                                     const void* scale_f16, float* out, ao_stream_t stream) {
+    if (ebits < 1 || mbits < 0 || ebits + mbits != 5) return AO_ERR_UNSUPPORTED;
     int rc = check_tc_shape(M, N);
     if (rc) return rc;
-    from_scaled_tc_fp6_kernel<<<grid_1d(M * N), 256, 0, as_stream(stream)>>>(packed, M, N,
+    from_scaled_tc_fp6_kernel<<<grid_1d(M * N), 256, 0, as_stream(stream)>>>(packed, M, N, ebits, mbits,
                                                                              static_cast<const __half*>(scale_f16), out);
     return launch_status();
+}
+
+extern "C" int ao_to_scaled_tc_fp6(const void* w, int w_dtype, int64_t M, int64_t N, uint8_t* packed_out,
+                                   void* scale_f16_out, ao_stream_t stream) {
+    return ao_to_scaled_tc_fpx(w, w_dtype, M, N, 3, 2, packed_out, scale_f16_out, stream);
+}
+
+extern "C" int ao_from_scaled_tc_fp6(const uint8_t* packed, int64_t M, int64_t N, const void* scale_f16, float* out,
+                                     ao_stream_t stream) {
+    return ao_from_scaled_tc_fpx(packed, M, N, 3, 2, scale_f16, out, stream);
 }

@@ -1,4 +1,4 @@
-// Prefill-shaped FP6 (e3m2) weight-only linear (M > 8) on the tensor-core pre-packed weight of
+// Prefill-shaped FP6 (e3m2 / e2m3) weight-only linear (M > 8) on the tensor-core pre-packed weight of
 // torchao/prototype/quant_llm/quant_llm.py:90-106, replacing torchao::quant_llm_linear
 // (torchao/csrc/cuda/fp6_llm/fp6_linear.cu:139-196) for large batches.  The pipeline is umma_linear.cuh.
 //
@@ -12,6 +12,7 @@
 namespace ao {
 namespace umma {
 
+template <bool E2M3>
 struct Fp6Policy {
     static constexpr int kTiles = kRawK / 16;              // k16 tiles per raw stage
     static constexpr int kP2 = kTiles * 256, kP4 = kTiles * 512, kBlk = kP2 + kP4;   // per 64-row block
@@ -36,8 +37,7 @@ struct Fp6Policy {
     // 16 units = (k16 tile, 64-row block) of 4 fragments of 16 rows each, dealt to the GW warps of a group
     template <int GW>
     static __device__ __forceinline__ void dequant(uint32_t raw, uint32_t a_tiles, int wi, int lane) {
-        const uint32_t m4 = 0x0F000F00u, mh = 0x90009000u, f_hi = 0x00C000C0u, f_lo = 0x00300030u;
-        const uint32_t k_hi = 0x140u, k_lo = 0x500u;
+        const fp6::Format fmt = E2M3 ? fp6::format_e2m3() : fp6::format_e3m2();
         // stmatrix: lane 8i + rr gives row rr of matrix i; matrix i = rows (i & 1) * 8.., k chunk (i >> 1)
         const int i = lane >> 3, rr = lane & 7;
 #pragma unroll
@@ -55,7 +55,7 @@ struct Fp6Policy {
                 for (int cc = 0; cc < 2; ++cc) {
                     const uint32_t w4 = ptx::lds32(p4 + (b * 2 + cc) * 128);
                     uint32_t a[4];
-                    fp6::decode_fragment(w4, cc == 0 ? w2 : (w2 << 4), m4, mh, f_hi, f_lo, k_hi, k_lo, a);
+                    fp6::decode_fragment(w4, cc == 0 ? w2 : (w2 << 4), fmt, a);
                     // fragment registers: a0 (rows e, k 0..7), a1 (rows e + 8, k 0..7), a2 (rows e, k 8..15), a3
                     ptx::stmatrix_x4(tile + (blk * 64 + (b * 2 + cc) * 16) * 128 + st_lane, a[0], a[1], a[2], a[3]);
                 }
@@ -65,7 +65,7 @@ struct Fp6Policy {
 
     static __device__ __forceinline__ int out_row(int row) { return row; }
     static __device__ __forceinline__ float row_scale(const Params& p, int n) {
-        return 4096.f * __half2float(static_cast<const __half*>(p.scale)[n]);
+        return (E2M3 ? 16384.f : 4096.f) * __half2float(static_cast<const __half*>(p.scale)[n]);
     }
 };
 
@@ -82,8 +82,8 @@ size_t fp6_umma_workspace_bytes(int64_t M, int64_t N, int64_t K) {
 }
 
 // AO_ERR_UNSUPPORTED: the caller falls back to row blocks through the decode kernel.
-int fp6_umma_linear(const void* x, int64_t ldx, const uint8_t* packed, const void* scale, int64_t M, int64_t N, int64_t K,
-                    void* y, void* ws, size_t ws_bytes, cudaStream_t st) {
+int fp6_umma_linear(bool e2m3, const void* x, int64_t ldx, const uint8_t* packed, const void* scale, int64_t M, int64_t N,
+                    int64_t K, void* y, void* ws, size_t ws_bytes, cudaStream_t st) {
     Plan P;
     if (!fp6_shape_ok(M, N, K) || !make_plan(M, N, K, &P)) return AO_ERR_UNSUPPORTED;
     if (!aligned(x, 16) || (ldx * 2) % 16 != 0 || ldx < K || !aligned(packed, 16)) return AO_ERR_UNSUPPORTED;
@@ -100,7 +100,7 @@ int fp6_umma_linear(const void* x, int64_t ldx, const uint8_t* packed, const voi
     prm.M = (int)M;
     prm.N = (int)N;
     prm.K = (int)K;
-    return launch_mt<Fp6Policy>(P, prm, st);
+    return e2m3 ? launch_mt<Fp6Policy<true>>(P, prm, st) : launch_mt<Fp6Policy<false>>(P, prm, st);
 }
 
 }  // namespace umma

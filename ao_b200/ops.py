@@ -195,7 +195,7 @@ def prepack_fp6_weight(codes: Tensor) -> Tensor:
 def quant_llm_linear(EXPONENT: int, MANTISSA: int, _in_feats: Tensor, _weights: Tensor, _scales: Tensor,
                      splitK: int = 1) -> Tensor:
     """Quant-LLM linear layer A @ W.T (torchao/ops.py:15-55).  _in_feats fp16 [BS][IC], _weights packed FPx uint8
-    [OC][IC/8*nbits], _scales fp16 [OC] -> fp16 [BS][OC].  Built for e3m2; `splitK` is accepted and ignored (the
+    [OC][IC/8*nbits], _scales fp16 [OC] -> fp16 [BS][OC].  Built for e3m2 and e2m3; `splitK` is accepted and ignored (the
     kernel chooses its own K split)."""
     torch._check(_in_feats.dim() == 2, lambda: f"input should be a 2d tensor, got {_in_feats.dim()}D")
     torch._check(_in_feats.dtype is torch.float16, lambda: f"weight must be FP16, got {_in_feats.dtype}")
@@ -208,8 +208,9 @@ def quant_llm_linear(EXPONENT: int, MANTISSA: int, _in_feats: Tensor, _weights: 
     N_BITS = 1 + EXPONENT + MANTISSA
     torch._check(IC // 8 * N_BITS == _weights.shape[1], lambda: "Dimensions mismatched")
     torch._check(OC == _scales.shape[0], lambda: "Dimensions mismatched")
-    if (EXPONENT, MANTISSA) != (3, 2):
-        raise NotImplementedError("quant_llm_linear is built for fp6 e3m2 only")
+    if (EXPONENT, MANTISSA) not in ((3, 2), (2, 3)):
+        raise NotImplementedError("quant_llm_linear is built for the 6-bit formats (e3m2, e2m3); "
+                                  f"FP{1 + EXPONENT + MANTISSA} E{EXPONENT}M{MANTISSA} is not supported")
     torch._check(IC % 64 == 0, lambda: f"Expect IC to be a multiple of 64, got {IC}")
     torch._check(OC % 64 == 0, lambda: f"Expect OC to be a multiple of 64, got {OC}")
     _cabi.require_cuda(_in_feats, _weights, _scales)
@@ -225,7 +226,7 @@ def quant_llm_linear(EXPONENT: int, MANTISSA: int, _in_feats: Tensor, _weights: 
     torch._check(nbytes > 0, lambda: f"unsupported fp6 linear shape BS={BS} OC={OC} IC={IC}")
     with torch.cuda.device(x.device):
         ws = _cabi.workspace(nbytes, x.device)
-        rc = lib.ao_fp6_linear(_cabi.ptr(x), x.stride(0), _cabi.ptr(w), _cabi.ptr(s), BS, OC, IC, _cabi.ptr(y),
+        rc = lib.ao_fpx_linear(EXPONENT, MANTISSA, _cabi.ptr(x), x.stride(0), _cabi.ptr(w), _cabi.ptr(s), BS, OC, IC, _cabi.ptr(y),
                                _cabi.ptr(ws), ws.numel(), _stream(x))
     _cabi.check(rc, "quant_llm_linear")
     return y

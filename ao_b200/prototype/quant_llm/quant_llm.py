@@ -42,9 +42,9 @@ def unpack_tc_fpx(tensor: Tensor, nbits: int) -> Tensor:
 
 def to_scaled_tc_fpx(tensor: Tensor, ebits: int, mbits: int) -> Tuple[Tensor, Tensor]:
     """Per-row absmax/max_normal scale (fp32 math, fp16 result), ExMy encode, pre-pack
-    (quant_llm.py:116-130).  Built for e3m2."""
-    if (ebits, mbits) != (3, 2):
-        raise NotImplementedError("to_scaled_tc_fpx is built for fp6 e3m2 only")
+    (quant_llm.py:116-130).  Built for the 6-bit formats e3m2 and e2m3."""
+    if (ebits, mbits) not in ((3, 2), (2, 3)):
+        raise NotImplementedError("to_scaled_tc_fpx is built for the 6-bit formats (e3m2, e2m3) only")
     _cabi.require_cuda(tensor)
     assert tensor.ndim == 2
     M, N = tensor.shape
@@ -55,16 +55,16 @@ def to_scaled_tc_fpx(tensor: Tensor, ebits: int, mbits: int) -> Tuple[Tensor, Te
     packed = torch.empty((M, N * 6 // 8), dtype=torch.uint8, device=t.device)
     scale = torch.empty((M,), dtype=torch.float16, device=t.device)
     with torch.cuda.device(t.device):
-        rc = _cabi.lib().ao_to_scaled_tc_fp6(_cabi.ptr(t), _cabi.dtype_code(t.dtype), M, N, _cabi.ptr(packed),
+        rc = _cabi.lib().ao_to_scaled_tc_fpx(_cabi.ptr(t), _cabi.dtype_code(t.dtype), M, N, ebits, mbits, _cabi.ptr(packed),
                                              _cabi.ptr(scale), _cabi.stream_ptr(t.device))
     _cabi.check(rc, "to_scaled_tc_fpx")
     return packed, scale
 
 
 def from_scaled_tc_fpx(tensor: Tensor, ebits: int, mbits: int, scale=None) -> Tensor:
-    """Unpack, decode to fp32 and apply the per-row scale (quant_llm.py:203-208).  Built for e3m2."""
-    if (ebits, mbits) != (3, 2):
-        raise NotImplementedError("from_scaled_tc_fpx is built for fp6 e3m2 only")
+    """Unpack, decode to fp32 and apply the per-row scale (quant_llm.py:203-208).  Built for e3m2 and e2m3."""
+    if (ebits, mbits) not in ((3, 2), (2, 3)):
+        raise NotImplementedError("from_scaled_tc_fpx is built for the 6-bit formats (e3m2, e2m3) only")
     assert tensor.ndim == 2 and tensor.dtype == torch.uint8
     _cabi.require_cuda(tensor, scale)
     M = tensor.shape[0]
@@ -74,7 +74,7 @@ def from_scaled_tc_fpx(tensor: Tensor, ebits: int, mbits: int, scale=None) -> Te
     s = None if scale is None else scale.to(torch.float16).contiguous()
     out = torch.empty((M, N), dtype=torch.float32, device=t.device)
     with torch.cuda.device(t.device):
-        rc = _cabi.lib().ao_from_scaled_tc_fp6(_cabi.ptr(t), M, N, _cabi.ptr(s), _cabi.ptr(out),
+        rc = _cabi.lib().ao_from_scaled_tc_fpx(_cabi.ptr(t), M, N, ebits, mbits, _cabi.ptr(s), _cabi.ptr(out),
                                                _cabi.stream_ptr(t.device))
     _cabi.check(rc, "from_scaled_tc_fpx")
     return out

@@ -252,6 +252,13 @@ int ao_hqq_int4_linear_transposed(const void* a, int a_dtype, int64_t a_row_stri
                                   int group, void* c, void* workspace, size_t workspace_bytes,
                                   ao_stream_t stream);
 
+/* The same two for either 6-bit format the reference's linear dispatches: (ebits, mbits) = (3, 2) or (2, 3)
+ * (to_scaled_tc_fpx / from_scaled_tc_fpx, quant_llm.py:116-130, 203-208; the bit packing is format-independent). */
+int ao_to_scaled_tc_fpx(const void* w, int w_dtype, int64_t M, int64_t N, int ebits, int mbits,
+                        uint8_t* packed_out, void* scale_f16_out, ao_stream_t stream);
+int ao_from_scaled_tc_fpx(const uint8_t* packed, int64_t M, int64_t N, int ebits, int mbits,
+                          const void* scale_f16, float* out, ao_stream_t stream);
+
 /* torchao::quant_llm_linear(3, 2, x, w, s, splitK) — torchao/ops.py:15-37, schema
  * torchao/csrc/fp6_llm.cpp:5-8, CUDA entry torchao/csrc/cuda/fp6_llm/fp6_linear.cu:139-196.
  * x fp16 [M][K] (row stride x_row_stride), packed uint8 [N][K*6/8] as produced by
@@ -261,6 +268,13 @@ int ao_hqq_int4_linear_transposed(const void* a, int a_dtype, int64_t a_row_stri
 size_t ao_fp6_linear_workspace_bytes(int64_t M, int64_t N, int64_t K);
 int ao_fp6_linear(const void* x_f16, int64_t x_row_stride, const uint8_t* packed, const void* scale_f16,
                   int64_t M, int64_t N, int64_t K, void* y_f16, void* workspace,
+                  size_t workspace_bytes, ao_stream_t stream);
+
+/* torchao::quant_llm_linear(EXPONENT, MANTISSA, ...) for (3, 2) and (2, 3) — the dispatch of
+ * torchao/csrc/cuda/fp6_llm/fp6_linear.cu:175-182 restricted to the 6-bit formats (the 5-bit ones, e2m2 and e3m1,
+ * return AO_ERR_UNSUPPORTED).  Same arguments and workspace (ao_fp6_linear_workspace_bytes) as ao_fp6_linear. */
+int ao_fpx_linear(int ebits, int mbits, const void* x_f16, int64_t x_row_stride, const uint8_t* packed,
+                  const void* scale_f16, int64_t M, int64_t N, int64_t K, void* y_f16, void* workspace,
                   size_t workspace_bytes, ao_stream_t stream);
 
 /* The decode kernel alone (1 <= M <= 16). */

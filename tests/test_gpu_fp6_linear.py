@@ -120,3 +120,46 @@ def test_fp6_prefill_vs_oracle(N, K):
         assert rel_err(tu.f32(y), y_ref) <= TOL, f"M={M}"
         assert torch.equal(y, ops.fp6_llm_linear(x.cuda(), packed, scale))
     assert _cabi.workspace_status("cuda") == 0
+
+
+def test_e2m3_codec_bit_exact_vs_reference_fixture():
+    from ao_b200.prototype.quant_llm.quant_llm import from_scaled_tc_fpx, to_scaled_tc_fpx
+    A = gu.load("e2m3.npz")
+    for name, dt in (("scaled_e2m3_f16", "f16"), ("scaled_e2m3_f32", "f32")):
+        w = tu.to_torch(A[f"{name}/w"], dt)
+        packed, scale = to_scaled_tc_fpx(w, 2, 3)
+        assert np.array_equal(tu.bits(packed), A[f"{name}/packed"])
+        assert np.array_equal(tu.bits(scale), A[f"{name}/scale"])
+        assert np.array_equal(tu.f32(from_scaled_tc_fpx(packed, 2, 3, scale)), A[f"{name}/dequant_f32"])
+
+
+def test_e2m3_linear_vs_reference_fixture_and_oracle():
+    from ao_b200 import _cabi, ops
+    from ao_b200.prototype.quant_llm import quant_llm_fpx_weight_only
+    A = gu.load("e2m3.npz")
+    packed = tu.to_torch(A["e2m3_lin/packed"], "u8")
+    scale = tu.to_torch(A["e2m3_lin/scale"], "f16")
+    for M in (1, 16, 64):
+        x = tu.to_torch(A[f"e2m3_lin/x_m{M}"], "f16")
+        y = ops.quant_llm_linear(2, 3, x, packed, scale, 1)
+        assert rel_err(tu.f32(y), A[f"e2m3_lin/y_m{M}"]) <= TOL, f"M={M}"
+    # larger shapes against the oracle, decode and prefill kernels
+    N, K = 1024, 4096
+    w = tu.make_weight((N, K), seed=77, dtype=torch.float16, outliers=False)
+    packed_ref, scale_ref = orc.to_scaled_tc_fp6(w.float().numpy(), 2, 3)
+    wd = orc.from_scaled_tc_fp6(packed_ref, scale_ref, 2, 3)
+    lin = torch.nn.Linear(K, N, bias=False, device="cuda", dtype=torch.float16)
+    with torch.no_grad():
+        lin.weight.copy_(w)
+    from ao_b200.quantization import quantize
+    quantize(lin, quant_llm_fpx_weight_only(2, 3))
+    assert np.array_equal(tu.bits(lin.weight.fpx_data), packed_ref)
+    g = torch.Generator().manual_seed(5)
+    for M in (1, 3, 8, 17, 100, 256):
+        x = torch.randn(M, K, generator=g).half()
+        y = lin(x.cuda()).detach()
+        assert rel_err(tu.f32(y), orc.linear_f32(x.float().numpy(), wd)) <= TOL, f"M={M}"
+    assert _cabi.workspace_status("cuda") == 0
+    with pytest.raises(NotImplementedError):
+        ops.quant_llm_linear(2, 2, x.cuda(), torch.zeros(N, K // 8 * 5, dtype=torch.uint8, device="cuda"),
+                             torch.ones(N, dtype=torch.float16, device="cuda"), 1)

@@ -177,3 +177,14 @@ def test_hqq_quants_to_torch_quants_matches_reference_expressions(key):
     q, nz = orc.hqq_quants_to_torch_quants(A[f"{key}/W_q"], A[f"{key}/scales"], A[f"{key}/zeros"], dt)
     assert np.array_equal(q.reshape(A[f"{key}/q"].shape), A[f"{key}/q"])
     assert np.array_equal(nz.reshape(A[f"{key}/new_zeros"].shape), A[f"{key}/new_zeros"])
+
+
+@pytest.mark.parametrize("name", ["scaled_e2m3_f16", "scaled_e2m3_f32"])
+def test_e2m3_to_scaled_and_from_scaled_match_reference(name):
+    A = gu.load("e2m3.npz")
+    w = A[f"{name}/w"]
+    wf = orc.f16_bits_to_f32(w) if w.dtype == np.uint16 else w.astype(np.float32)
+    packed, scale = orc.to_scaled_tc_fp6(wf, 2, 3)
+    assert np.array_equal(packed, A[f"{name}/packed"])
+    assert np.array_equal(scale, A[f"{name}/scale"])
+    assert np.array_equal(orc.from_scaled_tc_fp6(packed, scale, 2, 3), A[f"{name}/dequant_f32"])
