@@ -181,7 +181,7 @@ __global__ void __launch_bounds__(256) dequantize_kernel(const void* __restrict_
 // int4 weight-only fast path
 // ---------------------------------------------------------------------------------------------
 struct Int4Params {
-    float s, zp, minv;
+    float s, zp, minv, rs;   // rs = 1 / s, correctly rounded
 };
 
 // the int4_weight_only parameter set: asymmetric, qmin 0, qmax 15, mid 8, eps 1e-6 (as bf16),
@@ -193,12 +193,17 @@ __device__ __forceinline__ Int4Params int4_qparams_bf16(float mn, float mx) {
     p.zp = round_bf16(__fadd_rn(mn, round_bf16(__fmul_rn(s0, 8.0f))));  // uses the unclamped scale
     p.s = fmaxf(s0, __uint_as_float(0x35860000u));                      // bf16(1e-6)
     p.minv = round_bf16(__fsub_rn(p.zp, round_bf16(__fmul_rn(p.s, 8.0f))));
+    p.rs = __frcp_rn(p.s);
     return p;
 }
 
+// round_bf16((x - minv) / s) with the division done as a multiplication by 1 / s.  Both operands are bf16 values
+// (8-bit significands), so the exact quotient is either a bf16 value itself or at least 2^-18 (relative) away from
+// every midpoint between two bf16 values; the product's error (< 2^-22) cannot move it across one: the bf16
+// result is the same as that of the correctly rounded fp32 division the reference performs.
 __device__ __forceinline__ int int4_code_bf16(float x, const Int4Params& p) {
     float r = round_bf16(__fsub_rn(x, p.minv));
-    r = rintf(round_bf16(__fdiv_rn(r, p.s)));
+    r = rintf(round_bf16(__fmul_rn(r, p.rs)));
     return static_cast<int>(fminf(fmaxf(r, 0.f), 15.f));
 }
 
@@ -262,66 +267,92 @@ __global__ void __launch_bounds__(256) int4_groupwise_quantize_kernel(const uint
     }
 }
 
-// Fused W -> tensor_core_tiled packed weight + interleaved scale/zero.  One CTA owns one tile of
-// 8 rows x kChunk columns: codes go to shared memory, then every thread assembles packed words.
-constexpr int kPackChunk = 1024;
-
-template <int G>
+// Fused W -> tensor_core_tiled packed weight + interleaved scale/zero, no shared memory.
+// A warp owns 8 rows x U columns (U = the larger of the group and the packed layout's outer tile of IKT * 16 k);
+// lane = row * 4 + c reads, for every 32-k span, the 8 values k = 8c .. 8c + 7 of its row (one 16-byte load) -
+// which is exactly the lane numbering of the packed layout.  Group min / max are quad reductions; the 8 codes of a
+// span live as nibbles of one register; a packed word takes byte c (codes 2c, 2c + 1) of the four registers of
+// its quad (shuffles), puts the low nibbles in bits 15..0 and the high nibbles in bits 31..16, and the lane's
+// IKT / 2 words of an outer tile leave as one vector store.
+template <int G, int IKT>
 __global__ void __launch_bounds__(256) int4_quantize_pack_kernel(const __nv_bfloat16* __restrict__ w, int64_t N,
-                                                                 int64_t K, int ikt, int32_t* __restrict__ packed,
+                                                                 int64_t K, int32_t* __restrict__ packed,
                                                                  __nv_bfloat16* __restrict__ scale_and_zero) {
-    constexpr int L = G / 8;
-    __shared__ uint8_t codes[8][kPackChunk + 16];
-    const int64_t nt = blockIdx.y;
-    const int64_t k0 = static_cast<int64_t>(blockIdx.x) * kPackChunk;
-    const int chunk = static_cast<int>(min(static_cast<int64_t>(kPackChunk), K - k0));  // multiple of 16*ikt and G
-    const int vec_per_row = chunk / 8;
-    const int n_vec = 8 * vec_per_row;  // multiple of 32 because chunk is a multiple of 32
-    for (int i = threadIdx.x; i < n_vec; i += blockDim.x) {
-        const int row = i / vec_per_row, col = (i % vec_per_row) * 8;
-        const int64_t n = nt * 8 + row;
-        float f[8];
-        unpack8_bf16(__ldg(reinterpret_cast<const uint4*>(w + n * K + k0 + col)), f);
-        float mn = f[0], mx = f[0];
+    constexpr int OT = IKT * 16;                 // k per outer tile
+    constexpr int U = G > OT ? G : OT;           // k per warp unit
+    constexpr int S = U / 32;                    // 32-k spans per unit
+    constexpr int SPG = G / 32;                  // spans per group
+    constexpr int HALF = IKT / 2;                // words per lane per outer tile = spans per outer tile
+    const int lane = threadIdx.x & 31, row = lane >> 2, c = lane & 3;
+    const int64_t upr = K / U;                   // units per tile row
+    const int64_t unit = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (unit >= (N / 8) * upr) return;           // whole warps leave together
+    const int64_t nt = unit / upr, k0 = (unit % upr) * U;
+    const int64_t n = nt * 8 + row;
+    const __nv_bfloat16* src = w + n * K + k0 + 8 * c;
+    float f[S][8];
 #pragma unroll
-        for (int k = 1; k < 8; ++k) {
-            mn = fminf(mn, f[k]);
-            mx = fmaxf(mx, f[k]);
-        }
-        mn = warp_min(mn, L);
-        mx = warp_max(mx, L);
+    for (int s = 0; s < S; ++s) unpack8_bf16(__ldg(reinterpret_cast<const uint4*>(src + 32 * s)), f[s]);
+    uint32_t ch[S];
+#pragma unroll
+    for (int gi = 0; gi < S / SPG; ++gi) {
+        float mn = f[gi * SPG][0], mx = mn;
+#pragma unroll
+        for (int s = gi * SPG; s < (gi + 1) * SPG; ++s)
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                mn = fminf(mn, f[s][k]);
+                mx = fmaxf(mx, f[s][k]);
+            }
+        mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, 2));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
         const Int4Params p = int4_qparams_bf16(mn, mx);
-        if ((i % L) == 0) {
-            const int64_t g = (k0 + col) / G;
+        if (c == 0) {
             __nv_bfloat162 sz;
             sz.x = __float2bfloat16_rn(p.s);
             sz.y = __float2bfloat16_rn(p.zp);
-            reinterpret_cast<__nv_bfloat162*>(scale_and_zero)[g * N + n] = sz;
+            reinterpret_cast<__nv_bfloat162*>(scale_and_zero)[(k0 / G + gi) * N + n] = sz;
         }
-        uint32_t lo = 0, hi = 0;
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            lo |= static_cast<uint32_t>(int4_code_bf16(f[k], p)) << (8 * k);
-            hi |= static_cast<uint32_t>(int4_code_bf16(f[k + 4], p)) << (8 * k);
+        for (int s = gi * SPG; s < (gi + 1) * SPG; ++s) {
+            uint32_t v = 0;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) v |= static_cast<uint32_t>(int4_code_bf16(f[s][k], p)) << (4 * k);
+            ch[s] = v;
         }
-        *reinterpret_cast<uint2*>(&codes[row][col]) = make_uint2(lo, hi);
     }
-    __syncthreads();
-    // packed words of this tile: [ko_local][lane][ikt/2]
-    const int half = ikt / 2;
-    const int outer = chunk / (ikt * 16);
-    const int n_words = outer * 32 * half;
-    const int64_t KO = K / (ikt * 16);
-    const int64_t ko0 = k0 / (ikt * 16);
-    int32_t* dst = packed + ((nt * KO + ko0) * 32) * half;
-    for (int wi = threadIdx.x; wi < n_words; wi += blockDim.x) {
-        const int j = wi % half, t = (wi / half) % 32, ko = wi / (half * 32);
-        const int row = t >> 2, c = t & 3;
-        const int kA = (ko * ikt + 2 * j) * 16 + 2 * c, kB = kA + 16;
-        const uint8_t* r = codes[row];
-        const uint32_t word = r[kA] | (r[kA + 8] << 4) | (r[kB] << 8) | (r[kB + 8] << 12) | (r[kA + 1] << 16) |
-                              (r[kA + 9] << 20) | (r[kB + 1] << 24) | (static_cast<uint32_t>(r[kB + 9]) << 28);
-        dst[wi] = static_cast<int32_t>(word);
+    // byte c of a register holds codes 2c, 2c + 1 of that 8-k chunk
+    const uint32_t sel01 = static_cast<uint32_t>(c) | (static_cast<uint32_t>(4 + c) << 4) | 0x8800u;  // upper bytes: zero
+    const int quad = lane & ~3;
+    const int64_t KO = K / OT;
+    int32_t* dst = packed + ((nt * KO + k0 / OT) * 32 + lane) * HALF;
+#pragma unroll
+    for (int o = 0; o < U / OT; ++o) {
+        uint32_t words[HALF];
+#pragma unroll
+        for (int j = 0; j < HALF; ++j) {
+            const uint32_t v = ch[o * HALF + j];
+            const uint32_t c0 = __shfl_sync(0xffffffffu, v, quad), c1 = __shfl_sync(0xffffffffu, v, quad + 1);
+            const uint32_t c2 = __shfl_sync(0xffffffffu, v, quad + 2), c3 = __shfl_sync(0xffffffffu, v, quad + 3);
+            // P = bytes (chunk 0, chunk 1, chunk 2, chunk 3) = k 2c.., 2c + 8.., 2c + 16.., 2c + 24..
+            const uint32_t p01 = __byte_perm(c0, c1, sel01), p23 = __byte_perm(c2, c3, sel01);
+            const uint32_t P = __byte_perm(p01, p23, 0x5410);
+            uint32_t lo = P & 0x0F0F0F0Fu, hi = (P >> 4) & 0x0F0F0F0Fu;
+            lo = (lo | (lo >> 4)) & 0x00FF00FFu;
+            lo = (lo | (lo >> 8)) & 0x0000FFFFu;
+            hi = (hi | (hi >> 4)) & 0x00FF00FFu;
+            hi = (hi | (hi >> 8)) & 0x0000FFFFu;
+            words[j] = lo | (hi << 16);
+        }
+        int32_t* d = dst + static_cast<int64_t>(o) * 32 * HALF;
+        if constexpr (HALF == 4)
+            *reinterpret_cast<uint4*>(d) = make_uint4(words[0], words[1], words[2], words[3]);
+        else if constexpr (HALF == 2)
+            *reinterpret_cast<uint2*>(d) = make_uint2(words[0], words[1]);
+        else
+            *reinterpret_cast<uint32_t*>(d) = words[0];
     }
 }
 
@@ -456,19 +487,29 @@ extern "C" int ao_int4_quantize_pack_tinygemm(const void* w_bf16, int64_t N, int
     if (!(inner_k_tiles == 2 || inner_k_tiles == 4 || inner_k_tiles == 8)) return AO_ERR_ARG;
     if (N < 8 || N % 8 != 0 || K < 1 || K % group != 0 || K % (inner_k_tiles * 16) != 0 || K % 32 != 0)
         return AO_ERR_SHAPE;
-    if (kPackChunk % group != 0) return AO_ERR_UNSUPPORTED;
-    if (!aligned(w_bf16, 16) || !aligned(scale_and_zero_out, 4) || !aligned(packed_out, 4)) return AO_ERR_ALIGN;
-    if (N / 8 > 65535) return AO_ERR_SHAPE;
-    dim3 grid(static_cast<unsigned>((K + kPackChunk - 1) / kPackChunk), static_cast<unsigned>(N / 8));
+    if (!aligned(w_bf16, 16) || !aligned(scale_and_zero_out, 4) || !aligned(packed_out, 16)) return AO_ERR_ALIGN;
     const auto* w = static_cast<const __nv_bfloat16*>(w_bf16);
     auto* sz = static_cast<__nv_bfloat16*>(scale_and_zero_out);
     cudaStream_t st = as_stream(stream);
+    const int ot = inner_k_tiles * 16, unit_k = group > ot ? group : ot;
+    const int64_t units = (N / 8) * (K / unit_k);
+    if ((units + 7) / 8 > 2147483647LL) return AO_ERR_SHAPE;
+    const unsigned grid = static_cast<unsigned>((units + 7) / 8);
+#define AO_LAUNCH_QP(G_, I_) int4_quantize_pack_kernel<G_, I_><<<grid, 256, 0, st>>>(w, N, K, packed_out, sz)
+#define AO_LAUNCH_QP_G(G_)                                  \
+    switch (inner_k_tiles) {                                \
+        case 8: AO_LAUNCH_QP(G_, 8); break;                 \
+        case 4: AO_LAUNCH_QP(G_, 4); break;                 \
+        default: AO_LAUNCH_QP(G_, 2); break;                \
+    }
     switch (group) {
-        case 32: int4_quantize_pack_kernel<32><<<grid, 256, 0, st>>>(w, N, K, inner_k_tiles, packed_out, sz); break;
-        case 64: int4_quantize_pack_kernel<64><<<grid, 256, 0, st>>>(w, N, K, inner_k_tiles, packed_out, sz); break;
-        case 128: int4_quantize_pack_kernel<128><<<grid, 256, 0, st>>>(w, N, K, inner_k_tiles, packed_out, sz); break;
-        case 256: int4_quantize_pack_kernel<256><<<grid, 256, 0, st>>>(w, N, K, inner_k_tiles, packed_out, sz); break;
+        case 32: AO_LAUNCH_QP_G(32); break;
+        case 64: AO_LAUNCH_QP_G(64); break;
+        case 128: AO_LAUNCH_QP_G(128); break;
+        case 256: AO_LAUNCH_QP_G(256); break;
         default: return AO_ERR_UNSUPPORTED;
     }
+#undef AO_LAUNCH_QP_G
+#undef AO_LAUNCH_QP
     return launch_status();
 }

@@ -60,3 +60,24 @@ def test_reference_error_behaviour_on_host():
         quantize_affine(x, (1, 1), torch.ones(1), torch.zeros(1), torch.int8)
     # the docstring example of the reference
     assert _get_reduction_params((3, 3, 2, 10), (3, 3, 10, 10)) == ([3, 3, 5, 2, 10], [0, 1, 3, 4])
+
+
+def test_reciprocal_multiply_matches_division_for_bf16_operands():
+    """The int4 fast path computes round_bf16(r / s) as round_bf16(r * (1 / s)) (r, s bf16 values, fp32 arithmetic).
+    Exhaustive over every pair of bf16 significands and a spread of exponents: both give the same bf16 value."""
+    import numpy as np
+
+    def rbf16(v):
+        u = np.asarray(v, np.float32).view(np.uint32)
+        r = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint32) << 16
+        return r.view(np.float32)
+
+    sig = (128 + np.arange(128, dtype=np.float32)) / 128.0          # 1.0 .. 1.9921875 in steps of 2^-7
+    r_sig, s_sig = np.meshgrid(sig, sig, indexing="ij")
+    for er in (-20, -3, 0, 5):
+        for es in (-19, -8, 0, 2):
+            r = np.ldexp(r_sig, er).astype(np.float32)
+            s = np.ldexp(s_sig, es).astype(np.float32)
+            exact = rbf16(r / s)
+            fast = rbf16(r * (np.float32(1.0) / s))
+            assert np.array_equal(exact, fast), (er, es)
