@@ -178,6 +178,56 @@ __global__ void __launch_bounds__(512) to_scaled_tc_fp6_kernel(const T* __restri
     }
 }
 
+// to_scaled_tc_fpx in two kernels: per-row absmax -> scale (one warp per row, vector loads; scale =
+// max(absmax, 1e-12) / max_normal in fp32, quant_llm.py:126-127), then encode w / scale and pack, one CTA per
+// 64 rows x 128 columns.
+template <typename T>
+__global__ void __launch_bounds__(256) row_scale_kernel(const T* __restrict__ w, int64_t M, int64_t N, float max_normal,
+                                                        float* __restrict__ scale_f32, __half* __restrict__ scale_out) {
+    const int lane = threadIdx.x & 31;
+    const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= M) return;
+    const T* r = w + row * N;
+    float amax = 0.f;
+    // N is a multiple of 64 and rows start 16-byte aligned: 8 (16-bit) or 4 (fp32) elements per load
+    constexpr int V = 16 / sizeof(T);
+    for (int64_t c = static_cast<int64_t>(lane) * V; c < N; c += 32 * V) {
+        const uint4 q = __ldg(reinterpret_cast<const uint4*>(r + c));
+        const T* e = reinterpret_cast<const T*>(&q);
+#pragma unroll
+        for (int k = 0; k < V; ++k) amax = fmaxf(amax, fabsf(to_f32<T>(e[k])));
+    }
+    amax = warp_max(amax, 32);
+    if (lane == 0) {
+        const float s = __fdiv_rn(fmaxf(amax, 1e-12f), max_normal);
+        scale_f32[row] = s;
+        scale_out[row] = __float2half_rn(s);
+    }
+}
+
+// grid (ceil(F / kFT), M / 64)
+template <typename T>
+__global__ void __launch_bounds__(256) encode_pack_tc_fp6_kernel(const T* __restrict__ w, int64_t M, int64_t N, int ebits,
+                                                                 int mbits, const float* __restrict__ scale_f32,
+                                                                 uint8_t* __restrict__ packed) {
+    __shared__ __align__(16) uint8_t codes[64][kTileCols + kTilePad];
+    const int64_t a = blockIdx.y, F = N / 16, f0 = static_cast<int64_t>(blockIdx.x) * kFT;
+    const int nf = static_cast<int>(min(static_cast<int64_t>(kFT), F - f0));
+    const int cols = nf * 16;
+    for (int i = threadIdx.x; i < 64 * (cols / 4); i += blockDim.x) {
+        const int r = i / (cols / 4), c4 = (i % (cols / 4)) * 4;
+        const float s = scale_f32[a * 64 + r];
+        const T* src = w + (a * 64 + r) * N + f0 * 16 + c4;
+        uint32_t word = 0;
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+            word |= f32_to_fpx_bits(__fdiv_rn(to_f32<T>(src[k]), s), ebits, mbits) << (8 * k);
+        *reinterpret_cast<uint32_t*>(&codes[r][c4]) = word;
+    }
+    __syncthreads();
+    emit_fp6_tile(codes, a, F, f0, nf, packed, packed + M * N / 4);
+}
+
 __device__ __forceinline__ uint32_t fp6_code_at(const uint8_t* __restrict__ plane2, const uint8_t* __restrict__ plane4,
                                                 int64_t F, int64_t row, int64_t col) {
     const int64_t a = row >> 6;
@@ -276,15 +326,39 @@ static float fpx_max_normal(int ebits, int mbits) {
 }
 
 extern "C" int ao_to_scaled_tc_fpx(const void* w, int w_dtype, int64_t M, int64_t N, int ebits, int mbits,
-                                   uint8_t* packed_out, void* scale_f16_out, ao_stream_t stream) {
+                                   uint8_t* packed_out, void* scale_f16_out, void* workspace, size_t workspace_bytes,
+                                   ao_stream_t stream) {
     if (ebits < 1 || mbits < 0 || ebits + mbits != 5) return AO_ERR_UNSUPPORTED;   // 6-bit formats only
     int rc = check_tc_shape(M, N);
     if (rc) return rc;
     if (!aligned(packed_out, 4)) return AO_ERR_ALIGN;
-    const unsigned grid = static_cast<unsigned>(M / 64);
     cudaStream_t st = as_stream(stream);
     auto* so = static_cast<__half*>(scale_f16_out);
     const float mx = fpx_max_normal(ebits, mbits);
+    if (workspace != nullptr && workspace_bytes >= static_cast<size_t>(M) * 4 && aligned(workspace, 4) && aligned(w, 16)) {
+        // two kernels: row scales (fp32 copies in the workspace), then encode + pack with one CTA per 64 x 128 tile
+        auto* sf = static_cast<float*>(workspace);
+        const unsigned g1 = static_cast<unsigned>((M + 7) / 8);
+        dim3 g2(static_cast<unsigned>((N / 16 + kFT - 1) / kFT), static_cast<unsigned>(M / 64));
+        switch (w_dtype) {
+            case AO_F32:
+                row_scale_kernel<float><<<g1, 256, 0, st>>>(static_cast<const float*>(w), M, N, mx, sf, so);
+                encode_pack_tc_fp6_kernel<float><<<g2, 256, 0, st>>>(static_cast<const float*>(w), M, N, ebits, mbits, sf, packed_out);
+                break;
+            case AO_F16:
+                row_scale_kernel<__half><<<g1, 256, 0, st>>>(static_cast<const __half*>(w), M, N, mx, sf, so);
+                encode_pack_tc_fp6_kernel<__half><<<g2, 256, 0, st>>>(static_cast<const __half*>(w), M, N, ebits, mbits, sf, packed_out);
+                break;
+            case AO_BF16:
+                row_scale_kernel<__nv_bfloat16><<<g1, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(w), M, N, mx, sf, so);
+                encode_pack_tc_fp6_kernel<__nv_bfloat16><<<g2, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(w), M, N, ebits, mbits, sf, packed_out);
+                break;
+            default: return AO_ERR_DTYPE;
+        }
+        return launch_status();
+    }
+    // no workspace: one CTA per 64 rows does both passes
+    const unsigned grid = static_cast<unsigned>(M / 64);
     switch (w_dtype) {
         case AO_F32: to_scaled_tc_fp6_kernel<float><<<grid, 512, 0, st>>>(static_cast<const float*>(w), M, N, ebits, mbits, mx, packed_out, so); break;
         case AO_F16: to_scaled_tc_fp6_kernel<__half><<<grid, 512, 0, st>>>(static_cast<const __half*>(w), M, N, ebits, mbits, mx, packed_out, so); break;
@@ -306,7 +380,7 @@ extern "C" int ao_from_scaled_tc_fpx(const uint8_t* packed, int64_t M, int64_t N
 
 extern "C" int ao_to_scaled_tc_fp6(const void* w, int w_dtype, int64_t M, int64_t N, uint8_t* packed_out,
                                    void* scale_f16_out, ao_stream_t stream) {
-    return ao_to_scaled_tc_fpx(w, w_dtype, M, N, 3, 2, packed_out, scale_f16_out, stream);
+    return ao_to_scaled_tc_fpx(w, w_dtype, M, N, 3, 2, packed_out, scale_f16_out, nullptr, 0, stream);
 }
 
 extern "C" int ao_from_scaled_tc_fp6(const uint8_t* packed, int64_t M, int64_t N, const void* scale_f16, float* out,

@@ -178,6 +178,240 @@ __global__ void __launch_bounds__(256) dequantize_kernel(const void* __restrict_
 }
 
 // ---------------------------------------------------------------------------------------------
+// Vectorised variants of the three general kernels for the common layout: blocks are contiguous runs of B elements
+// (B a multiple of 8), every thread owns 8 consecutive elements (128-bit loads for 16-bit inputs), block constants
+// are computed once per thread, group min / max by sub-warp shuffles.  Same arithmetic, same rounding steps.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void unpack8_bf16(const uint4& v, float (&f)[8]) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        f[2 * i] = __uint_as_float(w[i] << 16);
+        f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+}
+
+template <int DT>
+__device__ __forceinline__ void load8(const void* p, int64_t v8, float (&f)[8]) {
+    if constexpr (DT == AO_F32) {
+        const float4 a = __ldg(static_cast<const float4*>(p) + 2 * v8), b = __ldg(static_cast<const float4*>(p) + 2 * v8 + 1);
+        f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+    } else if constexpr (DT == AO_BF16) {
+        unpack8_bf16(__ldg(static_cast<const uint4*>(p) + v8), f);
+    } else if constexpr (DT == AO_F16) {
+        const uint4 v = __ldg(static_cast<const uint4*>(p) + v8);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const __half2 h = *reinterpret_cast<const __half2*>(&w[i]);
+            f[2 * i] = __low2float(h);
+            f[2 * i + 1] = __high2float(h);
+        }
+    } else if constexpr (DT == AO_I32) {
+        const int4 a = __ldg(static_cast<const int4*>(p) + 2 * v8), b = __ldg(static_cast<const int4*>(p) + 2 * v8 + 1);
+        f[0] = (float)a.x; f[1] = (float)a.y; f[2] = (float)a.z; f[3] = (float)a.w;
+        f[4] = (float)b.x; f[5] = (float)b.y; f[6] = (float)b.z; f[7] = (float)b.w;
+    } else {   // AO_U8 / AO_I8
+        const uint2 v = __ldg(static_cast<const uint2*>(p) + v8);
+        const uint32_t w[2] = {v.x, v.y};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t b = (w[i >> 2] >> (8 * (i & 3))) & 0xffu;
+            f[i] = DT == AO_U8 ? static_cast<float>(b) : static_cast<float>(static_cast<int8_t>(b));
+        }
+    }
+}
+
+// values are already rounded to the dtype / integral
+template <int DT>
+__device__ __forceinline__ void store8(void* p, int64_t v8, const float (&f)[8]) {
+    if constexpr (DT == AO_F32) {
+        static_cast<float4*>(p)[2 * v8] = make_float4(f[0], f[1], f[2], f[3]);
+        static_cast<float4*>(p)[2 * v8 + 1] = make_float4(f[4], f[5], f[6], f[7]);
+    } else if constexpr (DT == AO_BF16 || DT == AO_F16) {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            if constexpr (DT == AO_BF16) {
+                const __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+                w[i] = *reinterpret_cast<const uint32_t*>(&h);
+            } else {
+                const __half2 h = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+                w[i] = *reinterpret_cast<const uint32_t*>(&h);
+            }
+        }
+        static_cast<uint4*>(p)[v8] = make_uint4(w[0], w[1], w[2], w[3]);
+    } else if constexpr (DT == AO_I32) {
+        static_cast<int4*>(p)[2 * v8] = make_int4((int)f[0], (int)f[1], (int)f[2], (int)f[3]);
+        static_cast<int4*>(p)[2 * v8 + 1] = make_int4((int)f[4], (int)f[5], (int)f[6], (int)f[7]);
+    } else {   // AO_U8 / AO_I8
+        uint32_t w[2] = {0u, 0u};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) w[i >> 2] |= (static_cast<uint32_t>(static_cast<int>(f[i])) & 0xffu) << (8 * (i & 3));
+        static_cast<uint2*>(p)[v8] = make_uint2(w[0], w[1]);
+    }
+}
+
+__device__ __forceinline__ void qparams_from_minmax(const QParamsArgs& a, float mn, float mx, float* scale_out, float* zp_out) {
+    float mnn = mn, mxp = mx;
+    if (a.preserve_zero) {
+        mnn = fminf(mn, 0.f);
+        mxp = fmaxf(mx, 0.f);
+    }
+    float scale, zp;
+    if (a.mapping == AO_MAP_SYMMETRIC) {
+        mxp = fmaxf(-mnn, mxp);
+        scale = round_to(a.in_dt, __fdiv_rn(mxp, a.sym_div));
+        zp = round_to(a.in_dt, a.sym_zp);
+    } else {
+        float d = round_to(a.in_dt, __fsub_rn(mxp, mnn));
+        scale = round_to(a.in_dt, __fdiv_rn(d, a.asym_div));
+        if (a.preserve_zero) {
+            float q = rintf(round_to(a.in_dt, __fdiv_rn(mnn, scale)));
+            zp = round_to(a.in_dt, __fsub_rn(a.qmin, q));
+            zp = fminf(fmaxf(zp, a.qmin), a.qmax);
+        } else {
+            float sm = round_to(a.in_dt, __fmul_rn(scale, a.mid));
+            zp = round_to(a.in_dt, __fadd_rn(mnn, sm));
+        }
+    }
+    *scale_out = fmaxf(scale, a.eps);
+    *zp_out = zp;
+}
+
+// L = B / 8 lanes share a block (L a power of two <= 32); nvec = numel / 8
+template <int DT>
+__global__ void __launch_bounds__(256) choose_qparams_vec_kernel(const void* __restrict__ x, int64_t nvec, int L,
+                                                                 QParamsArgs a, void* __restrict__ scale_out,
+                                                                 void* __restrict__ zp_out) {
+    const int64_t step = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    const int64_t rounded = (nvec + 31) / 32 * 32;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < rounded; i += step) {
+        float f[8];
+        float mn = INFINITY, mx = -INFINITY;
+        if (i < nvec) {
+            load8<DT>(x, i, f);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                mn = fminf(mn, f[k]);
+                mx = fmaxf(mx, f[k]);
+            }
+        }
+        mn = warp_min(mn, L);
+        mx = warp_max(mx, L);
+        if (i < nvec && (i % L) == 0) {
+            float scale, zp;
+            qparams_from_minmax(a, mn, mx, &scale, &zp);
+            const int64_t b = i / L;
+            store_from_f32(scale_out, a.scale_dt, b, round_to(a.scale_dt, scale));
+            store_from_f32(zp_out, a.zp_dt, b, is_float_dtype(a.zp_dt) ? round_to(a.zp_dt, zp) : truncf(zp));
+        }
+    }
+}
+
+// one warp per block of B elements (any B that is a multiple of 8)
+template <int DT>
+__global__ void __launch_bounds__(256) choose_qparams_row_kernel(const void* __restrict__ x, int64_t nblocks, int64_t vec_per_block,
+                                                                 QParamsArgs a, void* __restrict__ scale_out,
+                                                                 void* __restrict__ zp_out) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warps = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
+    for (int64_t b = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); b < nblocks; b += warps) {
+        float mn = INFINITY, mx = -INFINITY;
+        for (int64_t e = lane; e < vec_per_block; e += 32) {
+            float f[8];
+            load8<DT>(x, b * vec_per_block + e, f);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                mn = fminf(mn, f[k]);
+                mx = fmaxf(mx, f[k]);
+            }
+        }
+        mn = warp_min(mn, 32);
+        mx = warp_max(mx, 32);
+        if (lane == 0) {
+            float scale, zp;
+            qparams_from_minmax(a, mn, mx, &scale, &zp);
+            store_from_f32(scale_out, a.scale_dt, b, round_to(a.scale_dt, scale));
+            store_from_f32(zp_out, a.zp_dt, b, is_float_dtype(a.zp_dt) ? round_to(a.zp_dt, zp) : truncf(zp));
+        }
+    }
+}
+
+template <int IN_DT, int OUT_DT>
+__global__ void __launch_bounds__(256) quantize_vec_kernel(const void* __restrict__ x, int64_t nvec, int64_t vec_per_block,
+                                                           QuantArgs a, const void* __restrict__ scale,
+                                                           const void* __restrict__ zp, void* __restrict__ out) {
+    const int64_t step = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    const int p1 = promote_dtype(a.in_dt, a.scale_dt);
+    const int p2 = is_float_dtype(a.zp_dt) ? promote_dtype(p1, a.zp_dt) : p1;
+    const int pm = promote_dtype(is_float_dtype(a.zp_dt) ? a.zp_dt : a.scale_dt, a.scale_dt);
+    const int p3 = promote_dtype(a.in_dt, pm);
+    const int p4 = promote_dtype(p3, a.scale_dt);
+    // with bf16 operands the division below equals a multiplication by the correctly rounded reciprocal
+    // (see int4_code_bf16)
+    const bool rcp_ok = IN_DT == AO_BF16 && a.scale_dt == AO_BF16 && p3 == AO_BF16 && p4 == AO_BF16;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec; i += step) {
+        const int64_t b = i / vec_per_block;
+        const float s = load_as_f32(scale, a.scale_dt, b);
+        const float z = load_as_f32(zp, a.zp_dt, b);
+        float f[8];
+        load8<IN_DT>(x, i, f);
+        if (a.zp_domain == AO_ZP_INT) {
+            const float inv = round_to(a.scale_dt, __fdiv_rn(1.0f, s));
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                float r = rintf(round_to(p1, __fmul_rn(f[k], inv)));
+                r = round_to(p2, __fadd_rn(r, z));
+                f[k] = fminf(fmaxf(r, a.qmin), a.qmax);
+            }
+        } else {
+            const float sm = round_to(a.scale_dt, __fmul_rn(s, a.mid));
+            const float minv = round_to(pm, __fsub_rn(z, sm));
+            const float rs = __frcp_rn(s);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                float r = round_to(p3, __fsub_rn(f[k], minv));
+                r = rintf(round_to(p4, rcp_ok ? __fmul_rn(r, rs) : __fdiv_rn(r, s)));
+                f[k] = fminf(fmaxf(r, a.qmin), a.qmax);
+            }
+        }
+        store8<OUT_DT>(out, i, f);
+    }
+}
+
+template <int Q_DT, int OUT_DT>
+__global__ void __launch_bounds__(256) dequantize_vec_kernel(const void* __restrict__ q, int64_t nvec, int64_t vec_per_block,
+                                                             QuantArgs a, const void* __restrict__ scale,
+                                                             const void* __restrict__ zp, void* __restrict__ out) {
+    const int64_t step = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec; i += step) {
+        const int64_t b = i / vec_per_block;
+        const float s = load_as_f32(scale, a.scale_dt, b);
+        float f[8];
+        load8<Q_DT>(q, i, f);
+        if (a.zp_domain == AO_ZP_INT) {
+            const float zi = a.has_zp ? static_cast<float>(load_as_i32(zp, a.zp_dt, b)) : 0.f;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                float r = round_to(OUT_DT, f[k] - zi);   // small integers: the difference is exact in fp32
+                f[k] = round_to(OUT_DT, __fmul_rn(r, s));
+            }
+        } else {
+            const float z = a.has_zp ? load_as_f32(zp, a.zp_dt, b) : 0.f;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                float r = round_to(OUT_DT, __fsub_rn(f[k], a.mid));
+                r = round_to(OUT_DT, __fmul_rn(r, s));
+                if (a.has_zp) r = round_to(OUT_DT, __fadd_rn(r, z));
+                f[k] = r;
+            }
+        }
+        store8<OUT_DT>(out, i, f);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
 // int4 weight-only fast path
 // ---------------------------------------------------------------------------------------------
 struct Int4Params {
@@ -205,15 +439,6 @@ __device__ __forceinline__ int int4_code_bf16(float x, const Int4Params& p) {
     float r = round_bf16(__fsub_rn(x, p.minv));
     r = rintf(round_bf16(__fmul_rn(r, p.rs)));
     return static_cast<int>(fminf(fmaxf(r, 0.f), 15.f));
-}
-
-__device__ __forceinline__ void unpack8_bf16(const uint4& v, float (&f)[8]) {
-    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        f[2 * i] = __uint_as_float(w[i] << 16);
-        f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-    }
 }
 
 // G/8 lanes share a group; each lane owns 8 consecutive elements (one 128-bit load).
@@ -400,8 +625,25 @@ extern "C" int ao_choose_qparams_affine(const void* input, int input_dtype, int 
     a.sym_div = static_cast<float>(static_cast<double>(quant_max - quant_min) / 2.0);
     a.asym_div = static_cast<float>(quant_max - quant_min);
     a.sym_zp = static_cast<float>(static_cast<int64_t>(static_cast<double>(quant_max + quant_min + 1) / 2.0));
+    cudaStream_t st = as_stream(stream);
+    if (v.rowblock && v.block_elems % 8 == 0 && aligned(input, 16)) {
+        // vectorised: B / 8 lanes per block when that is a power of two up to 32, else one warp per block
+        const int64_t vpb = v.block_elems / 8, nvec = v.numel / 8;
+        const bool sub = vpb <= 32 && (vpb & (vpb - 1)) == 0;
+        const int grid = sub ? grid_for(nvec, 256) : grid_for(v.nblocks * 32, 256);
+#define AO_CHOOSE(DT_)                                                                                               \
+    if (sub) choose_qparams_vec_kernel<DT_><<<grid, 256, 0, st>>>(input, nvec, (int)vpb, a, scale_out, zero_point_out); \
+    else choose_qparams_row_kernel<DT_><<<grid, 256, 0, st>>>(input, v.nblocks, vpb, a, scale_out, zero_point_out)
+        switch (input_dtype) {
+            case AO_BF16: AO_CHOOSE(AO_BF16); break;
+            case AO_F16: AO_CHOOSE(AO_F16); break;
+            default: AO_CHOOSE(AO_F32); break;
+        }
+#undef AO_CHOOSE
+        return launch_status();
+    }
     const int grid = grid_for(v.nblocks * 32, 256);
-    choose_qparams_kernel<<<grid, 256, 0, as_stream(stream)>>>(input, v, a, scale_out, zero_point_out);
+    choose_qparams_kernel<<<grid, 256, 0, st>>>(input, v, a, scale_out, zero_point_out);
     return launch_status();
 }
 
@@ -436,7 +678,28 @@ extern "C" int ao_quantize_affine(const void* input, int input_dtype, int ndim, 
     rc = fill_quant_args(&a, input_dtype, scale_dtype, zero_point_dtype, zero_point_domain, out_dtype, zero_point,
                          quant_min, quant_max);
     if (rc) return rc;
-    quantize_kernel<<<grid_for(v.numel, 256), 256, 0, as_stream(stream)>>>(input, v, a, scale, zero_point, out);
+    cudaStream_t st = as_stream(stream);
+    if (v.rowblock && v.block_elems % 8 == 0 && aligned(input, 16) && aligned(out, 16) &&
+        (out_dtype == AO_I32 || out_dtype == AO_U8 || out_dtype == AO_I8)) {
+        const int64_t vpb = v.block_elems / 8, nvec = v.numel / 8;
+        const int grid = grid_for(nvec, 256);
+#define AO_QUANT(IN_, OUT_) quantize_vec_kernel<IN_, OUT_><<<grid, 256, 0, st>>>(input, nvec, vpb, a, scale, zero_point, out)
+#define AO_QUANT_IN(IN_)                                  \
+    switch (out_dtype) {                                  \
+        case AO_I32: AO_QUANT(IN_, AO_I32); break;        \
+        case AO_U8: AO_QUANT(IN_, AO_U8); break;          \
+        default: AO_QUANT(IN_, AO_I8); break;             \
+    }
+        switch (input_dtype) {
+            case AO_BF16: AO_QUANT_IN(AO_BF16); break;
+            case AO_F16: AO_QUANT_IN(AO_F16); break;
+            default: AO_QUANT_IN(AO_F32); break;
+        }
+#undef AO_QUANT_IN
+#undef AO_QUANT
+        return launch_status();
+    }
+    quantize_kernel<<<grid_for(v.numel, 256), 256, 0, st>>>(input, v, a, scale, zero_point, out);
     return launch_status();
 }
 
@@ -454,8 +717,29 @@ extern "C" int ao_dequantize_affine(const void* input, int input_dtype, int ndim
     rc = fill_quant_args(&a, AO_F32, scale_dtype, zero_point_dtype, zero_point_domain, out_dtype, zero_point,
                          quant_min, quant_max);
     if (rc) return rc;
-    dequantize_kernel<<<grid_for(v.numel, 256), 256, 0, as_stream(stream)>>>(input, input_dtype, v, a, scale,
-                                                                               zero_point, out);
+    cudaStream_t st = as_stream(stream);
+    const bool small_codes = quant_min >= -(1LL << 23) && quant_max <= (1LL << 23);
+    if (v.rowblock && v.block_elems % 8 == 0 && aligned(input, 16) && aligned(out, 16) && small_codes &&
+        (input_dtype == AO_I32 || input_dtype == AO_U8 || input_dtype == AO_I8)) {
+        const int64_t vpb = v.block_elems / 8, nvec = v.numel / 8;
+        const int grid = grid_for(nvec, 256);
+#define AO_DEQ(Q_, OUT_) dequantize_vec_kernel<Q_, OUT_><<<grid, 256, 0, st>>>(input, nvec, vpb, a, scale, zero_point, out)
+#define AO_DEQ_Q(Q_)                                      \
+    switch (out_dtype) {                                  \
+        case AO_BF16: AO_DEQ(Q_, AO_BF16); break;         \
+        case AO_F16: AO_DEQ(Q_, AO_F16); break;           \
+        default: AO_DEQ(Q_, AO_F32); break;               \
+    }
+        switch (input_dtype) {
+            case AO_I32: AO_DEQ_Q(AO_I32); break;
+            case AO_U8: AO_DEQ_Q(AO_U8); break;
+            default: AO_DEQ_Q(AO_I8); break;
+        }
+#undef AO_DEQ_Q
+#undef AO_DEQ
+        return launch_status();
+    }
+    dequantize_kernel<<<grid_for(v.numel, 256), 256, 0, st>>>(input, input_dtype, v, a, scale, zero_point, out);
     return launch_status();
 }
 

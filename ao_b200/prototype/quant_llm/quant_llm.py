@@ -54,9 +54,11 @@ def to_scaled_tc_fpx(tensor: Tensor, ebits: int, mbits: int) -> Tuple[Tensor, Te
         t = t.float()
     packed = torch.empty((M, N * 6 // 8), dtype=torch.uint8, device=t.device)
     scale = torch.empty((M,), dtype=torch.float16, device=t.device)
+    scratch = torch.empty((M,), dtype=torch.float32, device=t.device)   # fp32 row scales between the two kernels
     with torch.cuda.device(t.device):
         rc = _cabi.lib().ao_to_scaled_tc_fpx(_cabi.ptr(t), _cabi.dtype_code(t.dtype), M, N, ebits, mbits, _cabi.ptr(packed),
-                                             _cabi.ptr(scale), _cabi.stream_ptr(t.device))
+                                             _cabi.ptr(scale), _cabi.ptr(scratch), scratch.numel() * 4,
+                                             _cabi.stream_ptr(t.device))
     _cabi.check(rc, "to_scaled_tc_fpx")
     return packed, scale
 

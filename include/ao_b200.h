@@ -253,9 +253,12 @@ int ao_hqq_int4_linear_transposed(const void* a, int a_dtype, int64_t a_row_stri
                                   ao_stream_t stream);
 
 /* The same two for either 6-bit format the reference's linear dispatches: (ebits, mbits) = (3, 2) or (2, 3)
- * (to_scaled_tc_fpx / from_scaled_tc_fpx, quant_llm.py:116-130, 203-208; the bit packing is format-independent). */
+ * (to_scaled_tc_fpx / from_scaled_tc_fpx, quant_llm.py:116-130, 203-208; the bit packing is format-independent).
+ * With a workspace of at least M * 4 bytes (no initialisation needed) the work runs as two well-parallel kernels;
+ * workspace may be NULL. */
 int ao_to_scaled_tc_fpx(const void* w, int w_dtype, int64_t M, int64_t N, int ebits, int mbits,
-                        uint8_t* packed_out, void* scale_f16_out, ao_stream_t stream);
+                        uint8_t* packed_out, void* scale_f16_out, void* workspace, size_t workspace_bytes,
+                        ao_stream_t stream);
 int ao_from_scaled_tc_fpx(const uint8_t* packed, int64_t M, int64_t N, int ebits, int mbits,
                           const void* scale_f16, float* out, ao_stream_t stream);
 

@@ -134,3 +134,49 @@ def test_empty_and_degenerate_inputs():
     # all-zero tensor, per-tensor: scale == eps of the dtype (test_quant_primitives.py:385-392 of the reference)
     s, z = qp.choose_qparams_affine(torch.zeros(10, 10, device="cuda"), qp.MappingType.ASYMMETRIC, (10, 10), torch.int8)
     assert float(s) == float(torch.finfo(torch.float32).eps)
+
+
+@pytest.mark.parametrize("cfg", [
+    # (dtype, mapping, block, target, qmin, qmax, domain, preserve_zero)
+    ("bf16", "asym", (1, 64), "int32", 0, 15, "float", False),      # int4 weight-only setting, general entry points
+    ("bf16", "asym", (1, 32), "uint8", 0, 255, "int", True),
+    ("f16", "asym", (1, 128), "int32", 0, 15, "float", False),
+    ("f32", "sym", (1, 256), "int8", -128, 127, "int", True),
+    ("bf16", "sym", (1, 2048), "int8", -128, 127, "int", True),     # per row: one warp per block
+    ("f32", "asym", (1, 24), "int32", 0, 15, "float", False),       # 3 vectors per block: warp-per-block kernel
+], ids=lambda c: "-".join(map(str, c)))
+def test_vectorised_primitives_vs_oracle_large(cfg):
+    """The 128-bit-load variants of choose / quantize / dequantize (contiguous blocks) on 1.5 M elements."""
+    qp = _mods()
+    dt, mapping, block, target, qmin, qmax, dom, pz = cfg
+    odt = {"bf16": orc.BF16, "f16": orc.F16, "f32": orc.F32}[dt]
+    tdt = tu.TORCH_DT[dt]
+    cols = 2048 if 2048 % block[1] == 0 else block[1] * 64
+    g = torch.Generator().manual_seed(sum(block) + qmax)
+    x = (torch.randn(768, cols, generator=g) * 0.05).to(tdt)
+    xf = x.float().numpy()
+    m = orc.SYMMETRIC if mapping == "sym" else orc.ASYMMETRIC
+    d = orc.ZP_FLOAT if dom == "float" else orc.ZP_INT
+    zdt_o = odt if dom == "float" else orc.I32
+    s_ref, z_ref = orc.choose_qparams_affine(xf, odt, m, list(block), qmin, qmax, None, odt, zdt_o, pz, d)
+    q_ref = orc.quantize_affine(xf, odt, list(block), s_ref, odt, z_ref, zdt_o, qmin, qmax, d)
+    dq_ref = orc.dequantize_affine(q_ref, list(block), s_ref, odt, z_ref, zdt_o, qmin, qmax, d, odt)
+    M = qp.MappingType.SYMMETRIC if mapping == "sym" else qp.MappingType.ASYMMETRIC
+    D = qp.ZeroPointDomain.FLOAT if dom == "float" else qp.ZeroPointDomain.INT
+    zdt_t = tdt if dom == "float" else torch.int32
+    s, z = qp.choose_qparams_affine(x.cuda(), M, block, tu.TORCH_DT[target], qmin, qmax, None, scale_dtype=tdt,
+                                    zero_point_dtype=zdt_t, preserve_zero=pz, zero_point_domain=D)
+
+    def same(t, ref, ref_dt):
+        if ref_dt == orc.BF16:
+            return np.array_equal(tu.bits(t), orc.f32_to_bf16_bits(ref).reshape(tu.bits(t).shape))
+        if ref_dt == orc.F16:
+            return np.array_equal(tu.bits(t), np.asarray(ref, np.float32).astype(np.float16).view(np.uint16).reshape(tu.bits(t).shape))
+        return np.array_equal(tu.bits(t).reshape(-1), np.asarray(ref).reshape(-1).astype(tu.bits(t).dtype))
+
+    assert same(s, s_ref, odt), "scale"
+    assert same(z, z_ref, zdt_o if dom == "float" else orc.I32), "zero point"
+    q = qp.quantize_affine(x.cuda(), block, s, z, tu.TORCH_DT[target], qmin, qmax, D)
+    assert np.array_equal(tu.bits(q).astype(np.int64), np.asarray(q_ref).astype(np.int64)), "codes"
+    dq = qp.dequantize_affine(q, block, s, z, q.dtype, qmin, qmax, D, output_dtype=tdt)
+    assert same(dq, dq_ref, odt), "dequantized"
