@@ -204,27 +204,43 @@ static __device__ __noinline__ bool exchange_rows(const Plan& P, const __nv_bflo
             for (int j = lane; j < nrows / 8; j += 32) d[j] = src[j];
         }
     }
-    // receive
+    // receive: all (source, batch row, row pair) words of this CTA form one index space; a lane issues eight loads
+    // before it looks at any of them, so the polling costs a few memory latencies, not one per word
     bool ok = true;
     const uint64_t t0 = ptx::globaltimer_ns();
-    for (int i = 1; i < P.nranks && ok; ++i) {
-        const int r = (P.rank + P.nranks - i) % P.nranks;
-        const uint2* src = P.peer_ll[P.rank] + (size_t)r * block + 8 * pbeg;
-        uint32_t* dst = reinterpret_cast<uint32_t*>(P.y_gathered + (size_t)r * P.M * P.N + 16 * pbeg);
-        for (int m = 0; m < P.M && ok; ++m) {
-            for (int j = lane; j < n2; j += 32) {
-                uint2 v = ld_volatile_u2(src + (size_t)m * half_n + j);
-                while (v.y != call) {
-                    if (ptx::globaltimer_ns() - t0 > 200000000ull) {   // 0.2 s
-                        ok = false;
-                        break;
-                    }
-                    v = ld_volatile_u2(src + (size_t)m * half_n + j);
-                }
-                dst[(size_t)m * half_n + j] = v.x;
+    const int per_src = P.M * n2, total = (P.nranks - 1) * per_src;
+    const uint2* land = P.peer_ll[P.rank] + 8 * pbeg;
+    for (int b0 = 0; b0 < total && ok; b0 += 32 * 8) {   // uniform trip count: the vote below needs every lane
+        const int base = b0 + lane;
+        uint2 v[8];
+        const uint2* src[8];
+        uint32_t* dst[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            const int i = base + 32 * q;
+            src[q] = nullptr;
+            if (i < total) {
+                const int si = i / per_src, rem = i - si * per_src;
+                const int m = rem / n2, j = rem - m * n2;
+                const int r = (P.rank + 1 + si) % P.nranks;
+                src[q] = land + (size_t)r * block + (size_t)m * half_n + j;
+                dst[q] = reinterpret_cast<uint32_t*>(P.y_gathered + (size_t)r * P.M * P.N + 16 * pbeg) + (size_t)m * half_n + j;
+                v[q] = ld_volatile_u2(src[q]);
             }
-            ok = __all_sync(0xffffffffu, ok);
         }
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            if (src[q] == nullptr) continue;
+            while (v[q].y != call) {
+                if (ptx::globaltimer_ns() - t0 > 200000000ull) {   // 0.2 s
+                    ok = false;
+                    break;
+                }
+                v[q] = ld_volatile_u2(src[q]);
+            }
+            *dst[q] = v[q].x;
+        }
+        ok = __all_sync(0xffffffffu, ok);
     }
     // the last CTA to finish advances the call number for the next launch
     if (lane == 0) {
