@@ -11,17 +11,22 @@
 //    (cp.async.bulk, up to 16 KiB each, completion counted on an mbarrier) plus the chunk's group
 //    scales/zeros (16-byte cp.async pieces that signal the same mbarrier).  Full/empty mbarriers
 //    hand the stages to the consumer warps and back.
-//  * The consumer warps take the sub-units of the CTA's stream round-robin.  A packed word already is
-//    an m16n8k16 MMA fragment (8 codes of one row): codes become bf16 (128 + q) with one logic op
-//    per pair and feed mma.sync with W as the 16-row operand (two 8-row tiles) and x^T as the
-//    8-column operand, fp32 accumulate.  Scale and zero are applied per group on the accumulator:
+//  * The consumer warps work in groups of eight that take the stages in turn; inside a group every warp
+//    takes a contiguous run of the stage's sub-units.  A packed word already is an m16n8k16 MMA fragment
+//    (8 codes of one row): codes become bf16 (128 + q) with one logic op per pair and feed mma.sync
+//    with W as the 16-row operand (two 8-row tiles) and x^T as the 8-column operand, fp32 accumulate.
+//    Scale and zero are applied per group on the accumulator:
 //    y += s * (acc - 136 * Sx) + z * Sx,  Sx = sum of x over the group.
-//  * At the end of a row pair every consumer warp leaves its partial sums in shared memory; the last
-//    one to arrive adds them in warp order (deterministic) and stores bf16.  Only when the
+//  * At the end of a row pair every consumer warp leaves its partial sums in a ring of shared-memory
+//    buffers; a reducer warp adds them in slot order (deterministic) and stores bf16.  Only when the
 //    activations of the whole K range do not fit in shared memory (large M * K) is K cut into slabs
 //    handled by different CTAs; their partial sums meet in fixed slots of the workspace and the CTA
 //    that completes the pair (atomic counter) adds the slots in slab order and leaves the counter at
 //    zero for the next call.
+//  * Programmatic dependent launch: the kernel lets its successor start early and itself touches
+//    nothing but weights before griddepcontrol.wait, so back-to-back linears overlap drain and fill.
+//  * Row-sharded multi-GPU use (nranks > 1): the reducer warp stages the CTA's rows and exchanges them
+//    with the same CTA of every peer over peer-mapped memory (exchange_rows below).
 #pragma once
 #include <cstdlib>
 
