@@ -55,6 +55,8 @@ PROTOTYPES = {
     "ao_unpack_tc_fp6": (_int, [_ptr, _i64, _i64, _ptr, _ptr]),
     "ao_to_scaled_tc_fp6": (_int, [_ptr, _int, _i64, _i64, _ptr, _ptr, _ptr]),
     "ao_from_scaled_tc_fp6": (_int, [_ptr, _i64, _i64, _ptr, _ptr, _ptr]),
+    "ao_pack_tc_fpx": (_int, [_ptr, _i64, _i64, _int, _ptr, _ptr]),
+    "ao_unpack_tc_fpx": (_int, [_ptr, _i64, _i64, _int, _ptr, _ptr]),
     "ao_to_scaled_tc_fpx": (_int, [_ptr, _int, _i64, _i64, _int, _int, _ptr, _ptr, _ptr, _size, _ptr]),
     "ao_from_scaled_tc_fpx": (_int, [_ptr, _i64, _i64, _int, _int, _ptr, _ptr, _ptr]),
     "ao_fpx_linear": (_int, [_int, _int, _ptr, _i64, _ptr, _ptr, _i64, _i64, _i64, _ptr, _ptr, _size, _ptr]),

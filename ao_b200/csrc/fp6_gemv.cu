@@ -55,7 +55,9 @@ struct Plan {
     size_t ws_counters_off, ws_slots_off, ws_bytes;
 };
 
-static int make_plan(int64_t M, int64_t N, int64_t K, bool e2m3, Plan* P) {
+static int make_plan(int64_t M, int64_t N, int64_t K, int fmt_id, Plan* P) {
+    P->fmt = make_format(fmt_id);
+    const int tile_bytes = P->fmt.nbits == 6 ? 768 : 640;   // packed bytes of 64 rows x 16 k
     if (M < 1 || M > 16) return AO_ERR_SHAPE;
     if (N < 64 || N % 64 != 0 || K < 64 || K % 64 != 0) return AO_ERR_SHAPE;
     if (N > 64 * kMaxBlocks || K > (1 << 22)) return AO_ERR_SHAPE;
@@ -73,7 +75,7 @@ static int make_plan(int64_t M, int64_t N, int64_t K, bool e2m3, Plan* P) {
         const int ks = (int)(K / ns);
         const int tl = ks / 16, TL = tl < kMaxTiles ? tl : kMaxTiles, cb = (tl + TL - 1) / TL;
         const int slots = (ngroups < cb ? ngroups : cb) * kGroupWarps;
-        const long long need = 2LL * TL * 768 + (long long)ks * P->MR * P->NB * 2 + 4 * P->NB * P->MR * 32 +
+        const long long need = 2LL * TL * tile_bytes + (long long)ks * P->MR * P->NB * 2 + 4 * P->NB * P->MR * 32 +
                                2LL * slots * 4 * P->NB * 512 + 512;
         if (need > 220 * 1024) continue;
         int g = kNumSMs / ns;
@@ -93,7 +95,7 @@ static int make_plan(int64_t M, int64_t N, int64_t K, bool e2m3, Plan* P) {
     P->tiles = P->KS / 16;
     P->TILES = P->tiles < kMaxTiles ? P->tiles : kMaxTiles;
     P->cpb = (P->tiles + P->TILES - 1) / P->TILES;
-    P->stage_bytes = P->TILES * 768;
+    P->stage_bytes = P->TILES * tile_bytes;
     int G = kNumSMs / best;
     if (G > P->NA) G = P->NA;
     P->G = G;
@@ -128,7 +130,6 @@ static int make_plan(int64_t M, int64_t N, int64_t K, bool e2m3, Plan* P) {
     P->bar_off = off;
     off += 2 * kMaxStages * 8 + 2 * kMaxBlockBufs * 8;
     P->smem_bytes = off;
-    P->fmt = e2m3 ? format_e2m3() : format_e3m2();
     P->ws_counters_off = kHeaderBytes;
     P->ws_slots_off = kHeaderBytes + (size_t)kMaxBlocks * 4;
     P->ws_bytes = P->ws_slots_off + (best > 1 ? (size_t)best * P->NA * 4 * P->NB * 512 : 0);
@@ -204,7 +205,7 @@ __device__ __noinline__ void finish_block(const Plan& P, const float (&v)[4][NB]
     if (lane == 0) *counter = 0;
 }
 
-template <int NB, int MR>
+template <int NB, int MR, int NBITS>
 __global__ void __launch_bounds__(kThreads, 1)
 fp6_gemv_kernel(const __half* __restrict__ x, long long ldx, const uint8_t* __restrict__ wq,
                 const __half* __restrict__ scale, __half* __restrict__ y, uint8_t* __restrict__ ws,
@@ -220,7 +221,8 @@ fp6_gemv_kernel(const __half* __restrict__ x, long long ldx, const uint8_t* __re
     const uint32_t full_bar = smem_base + P.bar_off, empty_bar = full_bar + kMaxStages * 8;
     const uint32_t blk_full_bar = empty_bar + kMaxStages * 8, blk_free_bar = blk_full_bar + kMaxBlockBufs * 8;
     const int tiles = P.tiles, TILES = P.TILES, cpb = P.cpb;
-    const uint32_t plane4_off = TILES * 256;
+    constexpr int HI = NBITS == 6 ? 256 : 128;   // bytes of the first plane per k16 tile
+    const uint32_t plane4_off = TILES * HI;
     int* status = reinterpret_cast<int*>(ws);
 
     const int abeg = static_cast<int>((static_cast<unsigned>(cta) * static_cast<unsigned>(P.NA)) / static_cast<unsigned>(P.G));
@@ -250,7 +252,7 @@ fp6_gemv_kernel(const __half* __restrict__ x, long long ldx, const uint8_t* __re
         // stage = [2-bit plane bytes of the chunk: 256 per k tile][4-bit plane bytes: 512 per k tile]
         if (lane == 0) {
             const uint8_t* plane2 = wq;
-            const uint8_t* plane4 = wq + (size_t)P.N * P.K / 4;
+            const uint8_t* plane4 = wq + (size_t)P.N * P.K * (NBITS - 4) / 8;
             int ai = 0, c = 0, s = 0;
             uint32_t phase = 1;
             bool ok = true;
@@ -265,8 +267,8 @@ fp6_gemv_kernel(const __half* __restrict__ x, long long ldx, const uint8_t* __re
                 const size_t tile_index = (size_t)a * (P.K / 16) + f0;
                 const uint32_t dst = smem_base + s * stage_bytes;
                 const uint32_t bar = full_bar + 8 * s;
-                ptx::mbar_arrive_expect_tx(bar, nf * 768u);
-                ptx::bulk_copy_g2s(dst, plane2 + tile_index * 256, nf * 256u, bar);
+                ptx::mbar_arrive_expect_tx(bar, nf * (HI + 512u));
+                ptx::bulk_copy_g2s(dst, plane2 + tile_index * HI, nf * HI, bar);
                 ptx::bulk_copy_g2s(dst + plane4_off, plane4 + tile_index * 512, nf * 512u, bar);
                 if (++c == cpb) {
                     c = 0;
@@ -376,23 +378,36 @@ fp6_gemv_kernel(const __half* __restrict__ x, long long ldx, const uint8_t* __re
             const int j0 = (wi * nf) / kGroupWarps, j1 = ((wi + 1) * nf) / kGroupWarps;
 #pragma unroll 2
             for (int j = j0; j < j1; ++j) {
-                const uint32_t p2 = st + j * 256 + lane * 4;
+                const uint32_t p2 = st + j * HI + lane * 4;
                 const uint32_t p4 = st + plane4_off + j * 512 + lane * 4;
                 const uint32_t xa = x_base + (c * TILES + j) * x_tile_stride;
                 uint2 xb[NB];
 #pragma unroll
                 for (int nb = 0; nb < NB; ++nb) xb[nb] = ptx::lds64(xa + nb * (MRL * 8));
+                if constexpr (NBITS == 6) {
 #pragma unroll
-                for (int b = 0; b < 2; ++b) {
-                    const uint32_t w2 = ptx::lds32(p2 + b * 128);
+                    for (int b = 0; b < 2; ++b) {
+                        const uint32_t w2 = ptx::lds32(p2 + b * 128);
 #pragma unroll
-                    for (int cc = 0; cc < 2; ++cc) {
-                        const uint32_t w4 = ptx::lds32(p4 + (b * 2 + cc) * 128);
+                        for (int cc = 0; cc < 2; ++cc) {
+                            const uint32_t w4 = ptx::lds32(p4 + (b * 2 + cc) * 128);
+                            uint32_t a[4];
+                            decode_fragment(w4, cc == 0 ? w2 : (w2 << 4), fmt, a);
+#pragma unroll
+                            for (int nb = 0; nb < NB; ++nb)
+                                ptx::mma_f16_16816(acc[b * 2 + cc][nb], a[0], a[1], a[2], a[3], xb[nb].x, xb[nb].y);
+                        }
+                    }
+                } else {
+                    const uint32_t w1 = ptx::lds32(p2);   // the signs of all 64 rows of this lane's column pair
+#pragma unroll
+                    for (int fr = 0; fr < 4; ++fr) {
+                        const uint32_t w4 = ptx::lds32(p4 + fr * 128);
                         uint32_t a[4];
-                        decode_fragment(w4, cc == 0 ? w2 : (w2 << 4), fmt, a);
+                        decode_fragment5(w4, w1, fr, fmt, a);
 #pragma unroll
                         for (int nb = 0; nb < NB; ++nb)
-                            ptx::mma_f16_16816(acc[b * 2 + cc][nb], a[0], a[1], a[2], a[3], xb[nb].x, xb[nb].y);
+                            ptx::mma_f16_16816(acc[fr][nb], a[0], a[1], a[2], a[3], xb[nb].x, xb[nb].y);
                     }
                 }
             }
@@ -420,10 +435,10 @@ fp6_gemv_kernel(const __half* __restrict__ x, long long ldx, const uint8_t* __re
     if (!ok && lane == 0) atomicExch(status, AO_ERR_TIMEOUT);
 }
 
-template <int NB, int MR>
-static int launch(const Plan& P, const void* x, long long ldx, const void* wq, const void* scale, void* y, void* ws,
+template <int NB, int MR, int NBITS>
+static int launch_bits(const Plan& P, const void* x, long long ldx, const void* wq, const void* scale, void* y, void* ws,
                   cudaStream_t st) {
-    auto kern = fp6_gemv_kernel<NB, MR>;
+    auto kern = fp6_gemv_kernel<NB, MR, NBITS>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P.smem_bytes) != cudaSuccess)
         return AO_ERR_LAUNCH;
     cudaLaunchConfig_t cfg = {};
@@ -446,13 +461,20 @@ static int launch(const Plan& P, const void* x, long long ldx, const void* wq, c
     return AO_OK;
 }
 
+template <int NB, int MR>
+static int launch(const Plan& P, const void* x, long long ldx, const void* wq, const void* scale, void* y, void* ws,
+                  cudaStream_t st) {
+    return P.fmt.nbits == 6 ? launch_bits<NB, MR, 6>(P, x, ldx, wq, scale, y, ws, st)
+                            : launch_bits<NB, MR, 5>(P, x, ldx, wq, scale, y, ws, st);
+}
+
 }  // namespace fp6
 }  // namespace ao
 
 namespace ao {
 namespace umma {
 size_t fp6_umma_workspace_bytes(int64_t M, int64_t N, int64_t K);
-int fp6_umma_linear(bool e2m3, const void* x, int64_t ldx, const uint8_t* packed, const void* scale, int64_t M, int64_t N,
+int fp6_umma_linear(int fmt, const void* x, int64_t ldx, const uint8_t* packed, const void* scale, int64_t M, int64_t N,
                     int64_t K, void* y, void* ws, size_t ws_bytes, cudaStream_t st);
 }  // namespace umma
 }  // namespace ao
@@ -464,25 +486,25 @@ namespace {
 
 // A 9..16-row call whose activations and partial sums cannot share one SM's shared memory with the stage ring
 // runs as two calls of at most 8 rows.
-size_t gemv_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+size_t gemv_workspace_bytes(int64_t M, int64_t N, int64_t K, int fmt = ao::fp6::kE3M2) {
     fp6::Plan P;
-    int rc = fp6::make_plan(M, N, K, false, &P);
+    int rc = fp6::make_plan(M, N, K, fmt, &P);
     if (rc == AO_ERR_UNSUPPORTED && M > 8) {
-        const size_t a = gemv_workspace_bytes(8, N, K), b = gemv_workspace_bytes(M - 8, N, K);
+        const size_t a = gemv_workspace_bytes(8, N, K, fmt), b = gemv_workspace_bytes(M - 8, N, K, fmt);
         return a == 0 || b == 0 ? 0 : (a > b ? a : b);
     }
     return rc == AO_OK ? P.ws_bytes : 0;
 }
 
-int gemv(bool e2m3, const void* x_f16, int64_t x_row_stride, const uint8_t* packed, const void* scale_f16, int64_t M,
+int gemv(int fmt, const void* x_f16, int64_t x_row_stride, const uint8_t* packed, const void* scale_f16, int64_t M,
          int64_t N, int64_t K, void* y_f16, void* workspace, size_t workspace_bytes, ao_stream_t stream) {
     if (M == 0 || N == 0) return AO_OK;
     fp6::Plan P;
-    int rc = fp6::make_plan(M, N, K, e2m3, &P);
+    int rc = fp6::make_plan(M, N, K, fmt, &P);
     if (rc == AO_ERR_UNSUPPORTED && M > 8) {
-        rc = gemv(e2m3, x_f16, x_row_stride, packed, scale_f16, 8, N, K, y_f16, workspace, workspace_bytes, stream);
+        rc = gemv(fmt, x_f16, x_row_stride, packed, scale_f16, 8, N, K, y_f16, workspace, workspace_bytes, stream);
         if (rc) return rc;
-        return gemv(e2m3, static_cast<const __half*>(x_f16) + 8 * x_row_stride, x_row_stride, packed, scale_f16, M - 8, N, K,
+        return gemv(fmt, static_cast<const __half*>(x_f16) + 8 * x_row_stride, x_row_stride, packed, scale_f16, M - 8, N, K,
                     static_cast<__half*>(y_f16) + 8 * N, workspace, workspace_bytes, stream);
     }
     if (rc) return rc;
@@ -514,24 +536,24 @@ size_t linear_workspace_bytes(int64_t M, int64_t N, int64_t K) {
     return need;
 }
 
-int linear(bool e2m3, const void* x_f16, int64_t x_row_stride, const uint8_t* packed, const void* scale_f16, int64_t M,
+int linear(int fmt, const void* x_f16, int64_t x_row_stride, const uint8_t* packed, const void* scale_f16, int64_t M,
            int64_t N, int64_t K, void* y_f16, void* workspace, size_t workspace_bytes, ao_stream_t stream) {
     if (M < 0 || N < 0) return AO_ERR_SHAPE;
     if (M <= 8)
-        return gemv(e2m3, x_f16, x_row_stride, packed, scale_f16, M, N, K, y_f16, workspace, workspace_bytes, stream);
+        return gemv(fmt, x_f16, x_row_stride, packed, scale_f16, M, N, K, y_f16, workspace, workspace_bytes, stream);
     if (workspace == nullptr || workspace_bytes < 256 || !aligned(workspace, 256)) return AO_ERR_WORKSPACE;
     {
-        const int rc = umma::fp6_umma_linear(e2m3, x_f16, x_row_stride, packed, scale_f16, M, N, K, y_f16, workspace,
+        const int rc = umma::fp6_umma_linear(fmt, x_f16, x_row_stride, packed, scale_f16, M, N, K, y_f16, workspace,
                                              workspace_bytes, as_stream(stream));
         if (rc != AO_ERR_UNSUPPORTED) return rc;
     }
     if (M <= 16)
-        return gemv(e2m3, x_f16, x_row_stride, packed, scale_f16, M, N, K, y_f16, workspace, workspace_bytes, stream);
+        return gemv(fmt, x_f16, x_row_stride, packed, scale_f16, M, N, K, y_f16, workspace, workspace_bytes, stream);
     const auto* x = static_cast<const __half*>(x_f16);
     auto* y = static_cast<__half*>(y_f16);
     for (int64_t m0 = 0; m0 < M; m0 += 16) {
         const int64_t mb = M - m0 < 16 ? M - m0 : 16;
-        int rc = gemv(e2m3, x + m0 * x_row_stride, x_row_stride, packed, scale_f16, mb, N, K, y + m0 * N, workspace,
+        int rc = gemv(fmt, x + m0 * x_row_stride, x_row_stride, packed, scale_f16, mb, N, K, y + m0 * N, workspace,
                       workspace_bytes, stream);
         if (rc) return rc;
     }
@@ -545,7 +567,7 @@ extern "C" size_t ao_fp6_gemv_workspace_bytes(int64_t M, int64_t N, int64_t K) {
 extern "C" int ao_fp6_gemv(const void* x_f16, int64_t x_row_stride, const uint8_t* packed, const void* scale_f16,
                            int64_t M, int64_t N, int64_t K, void* y_f16, void* workspace, size_t workspace_bytes,
                            ao_stream_t stream) {
-    return gemv(false, x_f16, x_row_stride, packed, scale_f16, M, N, K, y_f16, workspace, workspace_bytes, stream);
+    return gemv(ao::fp6::kE3M2, x_f16, x_row_stride, packed, scale_f16, M, N, K, y_f16, workspace, workspace_bytes, stream);
 }
 
 // torchao::quant_llm_linear for e3m2
@@ -554,13 +576,14 @@ extern "C" size_t ao_fp6_linear_workspace_bytes(int64_t M, int64_t N, int64_t K)
 extern "C" int ao_fp6_linear(const void* x_f16, int64_t x_row_stride, const uint8_t* packed, const void* scale_f16,
                              int64_t M, int64_t N, int64_t K, void* y_f16, void* workspace, size_t workspace_bytes,
                              ao_stream_t stream) {
-    return linear(false, x_f16, x_row_stride, packed, scale_f16, M, N, K, y_f16, workspace, workspace_bytes, stream);
+    return linear(ao::fp6::kE3M2, x_f16, x_row_stride, packed, scale_f16, M, N, K, y_f16, workspace, workspace_bytes, stream);
 }
 
-// torchao::quant_llm_linear for the 6-bit formats: (EXPONENT, MANTISSA) = (3, 2) or (2, 3)
+// torchao::quant_llm_linear: (EXPONENT, MANTISSA) = (3, 2), (2, 3), (2, 2) or (3, 1)
 extern "C" int ao_fpx_linear(int ebits, int mbits, const void* x_f16, int64_t x_row_stride, const uint8_t* packed,
                              const void* scale_f16, int64_t M, int64_t N, int64_t K, void* y_f16, void* workspace,
                              size_t workspace_bytes, ao_stream_t stream) {
-    if (!((ebits == 3 && mbits == 2) || (ebits == 2 && mbits == 3))) return AO_ERR_UNSUPPORTED;
-    return linear(ebits == 2, x_f16, x_row_stride, packed, scale_f16, M, N, K, y_f16, workspace, workspace_bytes, stream);
+    const int fmt = ao::fp6::format_id(ebits, mbits);
+    if (fmt < 0) return AO_ERR_UNSUPPORTED;
+    return linear(fmt, x_f16, x_row_stride, packed, scale_f16, M, N, K, y_f16, workspace, workspace_bytes, stream);
 }

@@ -79,10 +79,33 @@ constexpr int kFT = 8;              // 16-column groups per tile
 constexpr int kTileCols = kFT * 16; // 128 columns
 constexpr int kTilePad = 4;
 
-// Writes the packed bytes of the tile (a, f0 .. f0+nf) from the codes staged in shared memory.
+// 1-bit plane of the 5-bit formats: 128 bytes per (a, f); word t (row d = t / 4 of every 8-row group, column pair
+// cp = t % 4) holds the top bit of row b * 16 + c * 8 + d, column g * 8 + 2 cp + hb at bit
+// hb * 16 + (1 - c) * 8 + (3 - b) * 2 + (1 - g).
+__device__ __forceinline__ void emit_top_bit_plane(const uint8_t (*codes)[kTileCols + kTilePad], int64_t a, int64_t F,
+                                                   int64_t f0, int nf, uint8_t* __restrict__ plane1) {
+    uint32_t* p1 = reinterpret_cast<uint32_t*>(plane1 + (a * F + f0) * 128);
+    for (int wi = threadIdx.x; wi < nf * 32; wi += blockDim.x) {
+        const int t = wi % 32, f = wi / 32, d = t >> 2, cp = t & 3;
+        uint32_t word = 0;
+#pragma unroll
+        for (int bit = 0; bit < 32; ++bit) {
+            const int hb = bit >> 4, c = 1 - ((bit >> 3) & 1), b = 3 - ((bit >> 1) & 3), g = 1 - (bit & 1);
+            const uint32_t v = codes[b * 16 + c * 8 + d][f * 16 + g * 8 + 2 * cp + hb];
+            word |= ((v >> 4) & 1u) << bit;
+        }
+        p1[wi] = word;
+    }
+}
+
+// Writes the packed bytes of the tile (a, f0 .. f0+nf) from the codes staged in shared memory: 6-bit codes as a
+// 2-bit and a 4-bit plane, 5-bit codes as a 1-bit and a 4-bit plane (plane_hi: the first plane).
 __device__ __forceinline__ void emit_fp6_tile(const uint8_t (*codes)[kTileCols + kTilePad], int64_t a, int64_t F,
                                               int64_t f0, int nf, uint8_t* __restrict__ plane2,
-                                              uint8_t* __restrict__ plane4) {
+                                              uint8_t* __restrict__ plane4, int nbits = 6) {
+    if (nbits == 5) {
+        emit_top_bit_plane(codes, a, F, f0, nf, plane2);
+    } else {
     // 2-bit plane: 256 bytes per f, written as 32-bit words (4 consecutive bytes: d = 0,1 of h, h+1)
     uint32_t* p2 = reinterpret_cast<uint32_t*>(plane2 + (a * F + f0) * 256);
     for (int wi = threadIdx.x; wi < nf * 64; wi += blockDim.x) {
@@ -102,6 +125,7 @@ __device__ __forceinline__ void emit_fp6_tile(const uint8_t (*codes)[kTileCols +
         }
         p2[wi] = word;
     }
+    }
     uint32_t* p4 = reinterpret_cast<uint32_t*>(plane4 + (a * F + f0) * 512);
     for (int wi = threadIdx.x; wi < nf * 128; wi += blockDim.x) {
         uint32_t word = 0;
@@ -119,7 +143,7 @@ __device__ __forceinline__ void emit_fp6_tile(const uint8_t (*codes)[kTileCols +
 
 // grid (ceil(F / kFT), M / 64)
 __global__ void __launch_bounds__(256) pack_tc_fp6_kernel(const uint8_t* __restrict__ codes_in, int64_t M, int64_t N,
-                                                          uint8_t* __restrict__ out) {
+                                                          uint8_t* __restrict__ out, int nbits) {
     __shared__ __align__(16) uint8_t codes[64][kTileCols + kTilePad];
     const int64_t a = blockIdx.y, F = N / 16, f0 = static_cast<int64_t>(blockIdx.x) * kFT;
     const int nf = static_cast<int>(min(static_cast<int64_t>(kFT), F - f0));
@@ -130,7 +154,7 @@ __global__ void __launch_bounds__(256) pack_tc_fp6_kernel(const uint8_t* __restr
             *reinterpret_cast<const uint32_t*>(codes_in + (a * 64 + r) * N + f0 * 16 + c4);
     }
     __syncthreads();
-    emit_fp6_tile(codes, a, F, f0, nf, out, out + M * N / 4);
+    emit_fp6_tile(codes, a, F, f0, nf, out, out + M * N * (nbits - 4) / 8, nbits);
 }
 
 template <typename T>
@@ -173,7 +197,7 @@ __global__ void __launch_bounds__(512) to_scaled_tc_fp6_kernel(const T* __restri
             codes[r][c] = static_cast<uint8_t>(f32_to_fpx_bits(v, ebits, mbits));
         }
         __syncthreads();
-        emit_fp6_tile(codes, a, F, f0, nf, packed, packed + M * N / 4);
+        emit_fp6_tile(codes, a, F, f0, nf, packed, packed + M * N * (ebits + mbits - 3) / 8, 1 + ebits + mbits);
         __syncthreads();
     }
 }
@@ -225,11 +249,21 @@ __global__ void __launch_bounds__(256) encode_pack_tc_fp6_kernel(const T* __rest
         *reinterpret_cast<uint32_t*>(&codes[r][c4]) = word;
     }
     __syncthreads();
-    emit_fp6_tile(codes, a, F, f0, nf, packed, packed + M * N / 4);
+    emit_fp6_tile(codes, a, F, f0, nf, packed, packed + M * N * (ebits + mbits - 3) / 8, 1 + ebits + mbits);
 }
 
 __device__ __forceinline__ uint32_t fp6_code_at(const uint8_t* __restrict__ plane2, const uint8_t* __restrict__ plane4,
-                                                int64_t F, int64_t row, int64_t col) {
+                                                int64_t F, int64_t row, int64_t col, int nbits = 6) {
+    if (nbits == 5) {
+        // top bit from the 1-bit plane (see emit_top_bit_plane), low four bits from the 4-bit plane
+        const int64_t a5 = row >> 6, f5 = col >> 4;
+        const int r5 = static_cast<int>(row & 63), b5 = r5 >> 4, c5 = (r5 >> 3) & 1, d5 = r5 & 7;
+        const int g5 = static_cast<int>((col >> 3) & 1), cp5 = static_cast<int>((col & 7) >> 1), hb5 = static_cast<int>(col & 1);
+        const int bit = hb5 * 16 + (1 - c5) * 8 + (3 - b5) * 2 + (1 - g5);
+        const int64_t byte = ((a5 * F + f5) * 32 + d5 * 4 + cp5) * 4 + (bit >> 3);
+        const uint32_t top = (plane2[byte] >> (bit & 7)) & 1u;
+        return (top << 4) | (fp6_code_at(plane2, plane4, F, row, col, 6) & 15u);
+    }
     const int64_t a = row >> 6;
     const int r = static_cast<int>(row & 63);
     const int b = r >> 5, c = (r >> 4) & 1, d = 1 - ((r >> 3) & 1), e = r & 7;
@@ -243,11 +277,11 @@ __device__ __forceinline__ uint32_t fp6_code_at(const uint8_t* __restrict__ plan
 }
 
 __global__ void __launch_bounds__(256) unpack_tc_fp6_kernel(const uint8_t* __restrict__ packed, int64_t M, int64_t N,
-                                                            uint8_t* __restrict__ codes_out) {
+                                                            uint8_t* __restrict__ codes_out, int nbits) {
     const int64_t total = M * N, F = N / 16;
     const int64_t step = static_cast<int64_t>(gridDim.x) * blockDim.x;
     for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += step)
-        codes_out[i] = static_cast<uint8_t>(fp6_code_at(packed, packed + total / 4, F, i / N, i % N));
+        codes_out[i] = static_cast<uint8_t>(fp6_code_at(packed, packed + total * (nbits - 4) / 8, F, i / N, i % N, nbits));
 }
 
 __global__ void __launch_bounds__(256) from_scaled_tc_fp6_kernel(const uint8_t* __restrict__ packed, int64_t M, int64_t N,
@@ -257,7 +291,7 @@ __global__ void __launch_bounds__(256) from_scaled_tc_fp6_kernel(const uint8_t* 
     const int64_t step = static_cast<int64_t>(gridDim.x) * blockDim.x;
     for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += step) {
         const int64_t row = i / N;
-        float v = fpx_bits_to_f32(fp6_code_at(packed, packed + total / 4, F, row, i % N), ebits, mbits);
+        float v = fpx_bits_to_f32(fp6_code_at(packed, packed + total * (ebits + mbits - 3) / 8, F, row, i % N, 1 + ebits + mbits), ebits, mbits);
         if (scale) v = __fmul_rn(v, __half2float(scale[row]));
         out[i] = v;
     }
@@ -303,20 +337,32 @@ static int check_tc_shape(int64_t M, int64_t N) {
     return AO_OK;
 }
 
-extern "C" int ao_pack_tc_fp6(const uint8_t* codes, int64_t M, int64_t N, uint8_t* packed_out, ao_stream_t stream) {
+extern "C" int ao_pack_tc_fpx(const uint8_t* codes, int64_t M, int64_t N, int nbits, uint8_t* packed_out,
+                              ao_stream_t stream) {
+    if (nbits != 5 && nbits != 6) return AO_ERR_UNSUPPORTED;
     int rc = check_tc_shape(M, N);
     if (rc) return rc;
     if (!aligned(codes, 4) || !aligned(packed_out, 4)) return AO_ERR_ALIGN;
     dim3 grid(static_cast<unsigned>((N / 16 + kFT - 1) / kFT), static_cast<unsigned>(M / 64));
-    pack_tc_fp6_kernel<<<grid, 256, 0, as_stream(stream)>>>(codes, M, N, packed_out);
+    pack_tc_fp6_kernel<<<grid, 256, 0, as_stream(stream)>>>(codes, M, N, packed_out, nbits);
     return launch_status();
 }
 
-extern "C" int ao_unpack_tc_fp6(const uint8_t* packed, int64_t M, int64_t N, uint8_t* codes_out, ao_stream_t stream) {
+extern "C" int ao_unpack_tc_fpx(const uint8_t* packed, int64_t M, int64_t N, int nbits, uint8_t* codes_out,
+                                ao_stream_t stream) {
+    if (nbits != 5 && nbits != 6) return AO_ERR_UNSUPPORTED;
     int rc = check_tc_shape(M, N);
     if (rc) return rc;
-    unpack_tc_fp6_kernel<<<grid_1d(M * N), 256, 0, as_stream(stream)>>>(packed, M, N, codes_out);
+    unpack_tc_fp6_kernel<<<grid_1d(M * N), 256, 0, as_stream(stream)>>>(packed, M, N, codes_out, nbits);
     return launch_status();
+}
+
+extern "C" int ao_pack_tc_fp6(const uint8_t* codes, int64_t M, int64_t N, uint8_t* packed_out, ao_stream_t stream) {
+    return ao_pack_tc_fpx(codes, M, N, 6, packed_out, stream);
+}
+
+extern "C" int ao_unpack_tc_fp6(const uint8_t* packed, int64_t M, int64_t N, uint8_t* codes_out, ao_stream_t stream) {
+    return ao_unpack_tc_fpx(packed, M, N, 6, codes_out, stream);
 }
 
 // largest finite value of a sign-magnitude ExMy format without inf / nan (custom_fp_utils.py:62-66)
@@ -328,7 +374,7 @@ static float fpx_max_normal(int ebits, int mbits) {
 extern "C" int ao_to_scaled_tc_fpx(const void* w, int w_dtype, int64_t M, int64_t N, int ebits, int mbits,
                                    uint8_t* packed_out, void* scale_f16_out, void* workspace, size_t workspace_bytes,
                                    ao_stream_t stream) {
-    if (ebits < 1 || mbits < 0 || ebits + mbits != 5) return AO_ERR_UNSUPPORTED;   // 6-bit formats only
+    if (ebits < 1 || mbits < 0 || (ebits + mbits != 5 && ebits + mbits != 4)) return AO_ERR_UNSUPPORTED;   // 5 or 6 bits
     int rc = check_tc_shape(M, N);
     if (rc) return rc;
     if (!aligned(packed_out, 4)) return AO_ERR_ALIGN;
@@ -370,7 +416,7 @@ extern "C" int ao_to_scaled_tc_fpx(const void* w, int w_dtype, int64_t M, int64_
 
 extern "C" int ao_from_scaled_tc_fpx(const uint8_t* packed, int64_t M, int64_t N, int ebits, int mbits,
                                      const void* scale_f16, float* out, ao_stream_t stream) {
-    if (ebits < 1 || mbits < 0 || ebits + mbits != 5) return AO_ERR_UNSUPPORTED;
+    if (ebits < 1 || mbits < 0 || (ebits + mbits != 5 && ebits + mbits != 4)) return AO_ERR_UNSUPPORTED;
     int rc = check_tc_shape(M, N);
     if (rc) return rc;
     from_scaled_tc_fp6_kernel<<<grid_1d(M * N), 256, 0, as_stream(stream)>>>(packed, M, N, ebits, mbits,

@@ -1,4 +1,4 @@
-// Prefill-shaped FP6 (e3m2 / e2m3) weight-only linear (M > 8) on the tensor-core pre-packed weight of
+// Prefill-shaped FPx (e3m2 / e2m3 / e2m2 / e3m1) weight-only linear (M > 8) on the tensor-core pre-packed weight of
 // torchao/prototype/quant_llm/quant_llm.py:90-106, replacing torchao::quant_llm_linear
 // (torchao/csrc/cuda/fp6_llm/fp6_linear.cu:139-196) for large batches.  The pipeline is umma_linear.cuh.
 //
@@ -12,24 +12,26 @@
 namespace ao {
 namespace umma {
 
-template <bool E2M3>
+template <int FMT>
 struct Fp6Policy {
+    static constexpr int kNBits = (FMT == fp6::kE3M2 || FMT == fp6::kE2M3) ? 6 : 5;
+    static constexpr int kHi = kNBits == 6 ? 256 : 128;    // bytes of the first plane per k16 tile and 64-row block
     static constexpr int kTiles = kRawK / 16;              // k16 tiles per raw stage
-    static constexpr int kP2 = kTiles * 256, kP4 = kTiles * 512, kBlk = kP2 + kP4;   // per 64-row block
-    static constexpr int kRawBytes = 2 * kBlk;             // 12 KiB
+    static constexpr int kP2 = kTiles * kHi, kP4 = kTiles * 512, kBlk = kP2 + kP4;   // per 64-row block
+    static constexpr int kRawBytes = 2 * kBlk;             // 12 KiB (6 bits) / 10 KiB (5 bits)
     static constexpr bool kBF16 = false;
     static constexpr bool kAMajorMN = false;
 
     static __device__ __forceinline__ void issue_raw(const Params& p, uint32_t dst, uint32_t bar, int k0, int n0) {
         const int nblk = (p.N - n0) >= kRows ? 2 : 1;       // N is a multiple of 64
-        // the 2-bit plane of every 64-row block comes first (N * K / 4 bytes), then the 4-bit plane; inside a plane
-        // the k16 tiles of one block are contiguous
+        // the first plane (2 bits or 1 bit per code) of every 64-row block comes first, then the 4-bit plane; inside a
+        // plane the k16 tiles of one block are contiguous
         const uint8_t* plane2 = static_cast<const uint8_t*>(p.w);
-        const uint8_t* plane4 = plane2 + (size_t)p.N * p.K / 4;
+        const uint8_t* plane4 = plane2 + (size_t)p.N * p.K * (kNBits - 4) / 8;
         ptx::mbar_arrive_expect_tx(bar, nblk * kBlk);
         for (int b = 0; b < nblk; ++b) {
             const size_t tile_index = (size_t)(n0 / 64 + b) * (p.K / 16) + k0 / 16;
-            ptx::bulk_copy_g2s(dst + b * kBlk, plane2 + tile_index * 256, kP2, bar);
+            ptx::bulk_copy_g2s(dst + b * kBlk, plane2 + tile_index * kHi, kP2, bar);
             ptx::bulk_copy_g2s(dst + b * kBlk + kP2, plane4 + tile_index * 512, kP4, bar);
         }
     }
@@ -37,7 +39,7 @@ struct Fp6Policy {
     // 16 units = (k16 tile, 64-row block) of 4 fragments of 16 rows each, dealt to the GW warps of a group
     template <int GW>
     static __device__ __forceinline__ void dequant(uint32_t raw, uint32_t a_tiles, int wi, int lane) {
-        const fp6::Format fmt = E2M3 ? fp6::format_e2m3() : fp6::format_e3m2();
+        const fp6::Format fmt = fp6::make_format(FMT);
         // stmatrix: lane 8i + rr gives row rr of matrix i; matrix i = rows (i & 1) * 8.., k chunk (i >> 1)
         const int i = lane >> 3, rr = lane & 7;
 #pragma unroll
@@ -46,18 +48,29 @@ struct Fp6Policy {
             const int chunk = (j & 3) * 2 + (i >> 1);
             const uint32_t st_lane = ((i & 1) * 8 + rr) * 128 + ((chunk ^ rr) << 4);
             const uint32_t tile = a_tiles + (j >> 2) * kABytes;
-            const uint32_t p2 = raw + blk * kBlk + j * 256 + lane * 4;
+            const uint32_t p2 = raw + blk * kBlk + j * kHi + lane * 4;
             const uint32_t p4 = raw + blk * kBlk + kP2 + j * 512 + lane * 4;
+            if constexpr (kNBits == 6) {
 #pragma unroll
-            for (int b = 0; b < 2; ++b) {
-                const uint32_t w2 = ptx::lds32(p2 + b * 128);
+                for (int b = 0; b < 2; ++b) {
+                    const uint32_t w2 = ptx::lds32(p2 + b * 128);
 #pragma unroll
-                for (int cc = 0; cc < 2; ++cc) {
-                    const uint32_t w4 = ptx::lds32(p4 + (b * 2 + cc) * 128);
+                    for (int cc = 0; cc < 2; ++cc) {
+                        const uint32_t w4 = ptx::lds32(p4 + (b * 2 + cc) * 128);
+                        uint32_t a[4];
+                        fp6::decode_fragment(w4, cc == 0 ? w2 : (w2 << 4), fmt, a);
+                        // fragment registers: a0 (rows e, k 0..7), a1 (rows e + 8, k 0..7), a2 (rows e, k 8..15), a3
+                        ptx::stmatrix_x4(tile + (blk * 64 + (b * 2 + cc) * 16) * 128 + st_lane, a[0], a[1], a[2], a[3]);
+                    }
+                }
+            } else {
+                const uint32_t w1 = ptx::lds32(p2);
+#pragma unroll
+                for (int fr = 0; fr < 4; ++fr) {
+                    const uint32_t w4 = ptx::lds32(p4 + fr * 128);
                     uint32_t a[4];
-                    fp6::decode_fragment(w4, cc == 0 ? w2 : (w2 << 4), fmt, a);
-                    // fragment registers: a0 (rows e, k 0..7), a1 (rows e + 8, k 0..7), a2 (rows e, k 8..15), a3
-                    ptx::stmatrix_x4(tile + (blk * 64 + (b * 2 + cc) * 16) * 128 + st_lane, a[0], a[1], a[2], a[3]);
+                    fp6::decode_fragment5(w4, w1, fr, fmt, a);
+                    ptx::stmatrix_x4(tile + (blk * 64 + fr * 16) * 128 + st_lane, a[0], a[1], a[2], a[3]);
                 }
             }
         }
@@ -65,7 +78,7 @@ struct Fp6Policy {
 
     static __device__ __forceinline__ int out_row(int row) { return row; }
     static __device__ __forceinline__ float row_scale(const Params& p, int n) {
-        return (E2M3 ? 16384.f : 4096.f) * __half2float(static_cast<const __half*>(p.scale)[n]);
+        return fp6::make_format(FMT).post_scale * __half2float(static_cast<const __half*>(p.scale)[n]);
     }
 };
 
@@ -82,7 +95,7 @@ size_t fp6_umma_workspace_bytes(int64_t M, int64_t N, int64_t K) {
 }
 
 // AO_ERR_UNSUPPORTED: the caller falls back to row blocks through the decode kernel.
-int fp6_umma_linear(bool e2m3, const void* x, int64_t ldx, const uint8_t* packed, const void* scale, int64_t M, int64_t N,
+int fp6_umma_linear(int fmt, const void* x, int64_t ldx, const uint8_t* packed, const void* scale, int64_t M, int64_t N,
                     int64_t K, void* y, void* ws, size_t ws_bytes, cudaStream_t st) {
     Plan P;
     if (!fp6_shape_ok(M, N, K) || !make_plan(M, N, K, &P)) return AO_ERR_UNSUPPORTED;
@@ -100,7 +113,13 @@ int fp6_umma_linear(bool e2m3, const void* x, int64_t ldx, const uint8_t* packed
     prm.M = (int)M;
     prm.N = (int)N;
     prm.K = (int)K;
-    return e2m3 ? launch_mt<Fp6Policy<true>>(P, prm, st) : launch_mt<Fp6Policy<false>>(P, prm, st);
+    switch (fmt) {
+        case fp6::kE3M2: return launch_mt<Fp6Policy<fp6::kE3M2>>(P, prm, st);
+        case fp6::kE2M3: return launch_mt<Fp6Policy<fp6::kE2M3>>(P, prm, st);
+        case fp6::kE2M2: return launch_mt<Fp6Policy<fp6::kE2M2>>(P, prm, st);
+        case fp6::kE3M1: return launch_mt<Fp6Policy<fp6::kE3M1>>(P, prm, st);
+    }
+    return AO_ERR_UNSUPPORTED;
 }
 
 }  // namespace umma

@@ -195,7 +195,7 @@ def prepack_fp6_weight(codes: Tensor) -> Tensor:
 def quant_llm_linear(EXPONENT: int, MANTISSA: int, _in_feats: Tensor, _weights: Tensor, _scales: Tensor,
                      splitK: int = 1) -> Tensor:
     """Quant-LLM linear layer A @ W.T (torchao/ops.py:15-55).  _in_feats fp16 [BS][IC], _weights packed FPx uint8
-    [OC][IC/8*nbits], _scales fp16 [OC] -> fp16 [BS][OC].  Built for e3m2 and e2m3; `splitK` is accepted and ignored (the
+    [OC][IC/8*nbits], _scales fp16 [OC] -> fp16 [BS][OC].  Formats: e3m2, e2m3 (fp6), e2m2, e3m1 (fp5); `splitK` is accepted and ignored (the
     kernel chooses its own K split)."""
     torch._check(_in_feats.dim() == 2, lambda: f"input should be a 2d tensor, got {_in_feats.dim()}D")
     torch._check(_in_feats.dtype is torch.float16, lambda: f"weight must be FP16, got {_in_feats.dtype}")
@@ -208,9 +208,8 @@ def quant_llm_linear(EXPONENT: int, MANTISSA: int, _in_feats: Tensor, _weights: 
     N_BITS = 1 + EXPONENT + MANTISSA
     torch._check(IC // 8 * N_BITS == _weights.shape[1], lambda: "Dimensions mismatched")
     torch._check(OC == _scales.shape[0], lambda: "Dimensions mismatched")
-    if (EXPONENT, MANTISSA) not in ((3, 2), (2, 3)):
-        raise NotImplementedError("quant_llm_linear is built for the 6-bit formats (e3m2, e2m3); "
-                                  f"FP{1 + EXPONENT + MANTISSA} E{EXPONENT}M{MANTISSA} is not supported")
+    torch._check((EXPONENT, MANTISSA) in ((3, 2), (2, 3), (2, 2), (3, 1)),
+                 lambda: f"FP{1 + EXPONENT + MANTISSA} E{EXPONENT}M{MANTISSA} is not supported.")   # fp6_linear.cu:193
     torch._check(IC % 64 == 0, lambda: f"Expect IC to be a multiple of 64, got {IC}")
     torch._check(OC % 64 == 0, lambda: f"Expect OC to be a multiple of 64, got {OC}")
     _cabi.require_cuda(_in_feats, _weights, _scales)

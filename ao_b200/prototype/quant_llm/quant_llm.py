@@ -12,39 +12,50 @@ from torch import Tensor
 from ... import _cabi
 
 
-def _check_fp6(nbits: int):
-    if nbits != 6:
-        raise NotImplementedError(f"only 6-bit (e3m2 / e2m3) tensor-core packing is built, got {nbits} bits")
+_FORMATS = ((3, 2), (2, 3), (2, 2), (3, 1))   # the (ebits, mbits) the reference's linear dispatches
+
+
+def _check_nbits(nbits: int):
+    if nbits not in (5, 6):
+        raise NotImplementedError(f"tensor-core packing is built for 5- and 6-bit codes, got {nbits} bits")
 
 
 def pack_tc_fpx(tensor: Tensor, nbits: int) -> Tensor:
     """uint8 codes [M][N] -> tensor-core pre-packed uint8 [M][N*nbits/8] (quant_llm.py:60-113)."""
-    _check_fp6(nbits)
-    from ...ops import prepack_fp6_weight
-    return prepack_fp6_weight(tensor)
+    _check_nbits(nbits)
+    _cabi.require_cuda(tensor)
+    assert tensor.ndim == 2 and tensor.dtype == torch.uint8
+    M, N = tensor.shape
+    assert (M % 64 == 0) and (N % 64 == 0)
+    t = tensor.contiguous()
+    out = torch.empty((M, N * nbits // 8), dtype=torch.uint8, device=t.device)
+    with torch.cuda.device(t.device):
+        rc = _cabi.lib().ao_pack_tc_fpx(_cabi.ptr(t), M, N, nbits, _cabi.ptr(out), _cabi.stream_ptr(t.device))
+    _cabi.check(rc, "pack_tc_fpx")
+    return out
 
 
 def unpack_tc_fpx(tensor: Tensor, nbits: int) -> Tensor:
     """Inverse of pack_tc_fpx (quant_llm.py:134-200)."""
-    _check_fp6(nbits)
+    _check_nbits(nbits)
     assert tensor.ndim == 2 and tensor.dtype == torch.uint8
     _cabi.require_cuda(tensor)
     M = tensor.shape[0]
-    N = tensor.shape[1] // 3 * 4
+    N = tensor.shape[1] // nbits * 8
     assert (M % 64 == 0) and (N % 64 == 0)
     t = tensor.contiguous()
     out = torch.empty((M, N), dtype=torch.uint8, device=t.device)
     with torch.cuda.device(t.device):
-        rc = _cabi.lib().ao_unpack_tc_fp6(_cabi.ptr(t), M, N, _cabi.ptr(out), _cabi.stream_ptr(t.device))
+        rc = _cabi.lib().ao_unpack_tc_fpx(_cabi.ptr(t), M, N, nbits, _cabi.ptr(out), _cabi.stream_ptr(t.device))
     _cabi.check(rc, "unpack_tc_fpx")
     return out
 
 
 def to_scaled_tc_fpx(tensor: Tensor, ebits: int, mbits: int) -> Tuple[Tensor, Tensor]:
     """Per-row absmax/max_normal scale (fp32 math, fp16 result), ExMy encode, pre-pack
-    (quant_llm.py:116-130).  Built for the 6-bit formats e3m2 and e2m3."""
-    if (ebits, mbits) not in ((3, 2), (2, 3)):
-        raise NotImplementedError("to_scaled_tc_fpx is built for the 6-bit formats (e3m2, e2m3) only")
+    (quant_llm.py:116-130).  Built for e3m2, e2m3, e2m2 and e3m1."""
+    if (ebits, mbits) not in _FORMATS:
+        raise NotImplementedError(f"to_scaled_tc_fpx: e{ebits}m{mbits} is not built")
     _cabi.require_cuda(tensor)
     assert tensor.ndim == 2
     M, N = tensor.shape
@@ -52,7 +63,7 @@ def to_scaled_tc_fpx(tensor: Tensor, ebits: int, mbits: int) -> Tuple[Tensor, Te
     t = tensor.contiguous()
     if t.dtype not in (torch.float32, torch.float16, torch.bfloat16):
         t = t.float()
-    packed = torch.empty((M, N * 6 // 8), dtype=torch.uint8, device=t.device)
+    packed = torch.empty((M, N * (1 + ebits + mbits) // 8), dtype=torch.uint8, device=t.device)
     scale = torch.empty((M,), dtype=torch.float16, device=t.device)
     scratch = torch.empty((M,), dtype=torch.float32, device=t.device)   # fp32 row scales between the two kernels
     with torch.cuda.device(t.device):
@@ -64,13 +75,13 @@ def to_scaled_tc_fpx(tensor: Tensor, ebits: int, mbits: int) -> Tuple[Tensor, Te
 
 
 def from_scaled_tc_fpx(tensor: Tensor, ebits: int, mbits: int, scale=None) -> Tensor:
-    """Unpack, decode to fp32 and apply the per-row scale (quant_llm.py:203-208).  Built for e3m2 and e2m3."""
-    if (ebits, mbits) not in ((3, 2), (2, 3)):
-        raise NotImplementedError("from_scaled_tc_fpx is built for the 6-bit formats (e3m2, e2m3) only")
+    """Unpack, decode to fp32 and apply the per-row scale (quant_llm.py:203-208)."""
+    if (ebits, mbits) not in _FORMATS:
+        raise NotImplementedError(f"from_scaled_tc_fpx: e{ebits}m{mbits} is not built")
     assert tensor.ndim == 2 and tensor.dtype == torch.uint8
     _cabi.require_cuda(tensor, scale)
     M = tensor.shape[0]
-    N = tensor.shape[1] // 3 * 4
+    N = tensor.shape[1] // (1 + ebits + mbits) * 8
     assert (M % 64 == 0) and (N % 64 == 0)
     t = tensor.contiguous()
     s = None if scale is None else scale.to(torch.float16).contiguous()

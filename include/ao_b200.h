@@ -252,7 +252,12 @@ int ao_hqq_int4_linear_transposed(const void* a, int a_dtype, int64_t a_row_stri
                                   int group, void* c, void* workspace, size_t workspace_bytes,
                                   ao_stream_t stream);
 
-/* The same two for either 6-bit format the reference's linear dispatches: (ebits, mbits) = (3, 2) or (2, 3)
+/* pack_tc_fpx / unpack_tc_fpx for 5- and 6-bit codes (quant_llm.py:60-113, 134-200): a 5-bit code is split into a
+ * 1-bit and a 4-bit plane, a 6-bit code into a 2-bit and a 4-bit plane.  packed: uint8 [M][N * nbits / 8]. */
+int ao_pack_tc_fpx(const uint8_t* codes, int64_t M, int64_t N, int nbits, uint8_t* packed_out, ao_stream_t stream);
+int ao_unpack_tc_fpx(const uint8_t* packed, int64_t M, int64_t N, int nbits, uint8_t* codes_out, ao_stream_t stream);
+
+/* The same two for the formats the reference's linear dispatches: (ebits, mbits) = (3, 2), (2, 3), (2, 2), (3, 1)
  * (to_scaled_tc_fpx / from_scaled_tc_fpx, quant_llm.py:116-130, 203-208; the bit packing is format-independent).
  * With a workspace of at least M * 4 bytes (no initialisation needed) the work runs as two well-parallel kernels;
  * workspace may be NULL. */
@@ -273,9 +278,10 @@ int ao_fp6_linear(const void* x_f16, int64_t x_row_stride, const uint8_t* packed
                   int64_t M, int64_t N, int64_t K, void* y_f16, void* workspace,
                   size_t workspace_bytes, ao_stream_t stream);
 
-/* torchao::quant_llm_linear(EXPONENT, MANTISSA, ...) for (3, 2) and (2, 3) — the dispatch of
- * torchao/csrc/cuda/fp6_llm/fp6_linear.cu:175-182 restricted to the 6-bit formats (the 5-bit ones, e2m2 and e3m1,
- * return AO_ERR_UNSUPPORTED).  Same arguments and workspace (ao_fp6_linear_workspace_bytes) as ao_fp6_linear. */
+/* torchao::quant_llm_linear(EXPONENT, MANTISSA, ...) — the dispatch of
+ * torchao/csrc/cuda/fp6_llm/fp6_linear.cu:175-193: (3, 2), (2, 3) (6 bits), (2, 2), (3, 1) (5 bits); anything else
+ * returns AO_ERR_UNSUPPORTED.  packed: uint8 [N][K * nbits / 8].  Same arguments and workspace
+ * (ao_fp6_linear_workspace_bytes) as ao_fp6_linear. */
 int ao_fpx_linear(int ebits, int mbits, const void* x_f16, int64_t x_row_stride, const uint8_t* packed,
                   const void* scale_f16, int64_t M, int64_t N, int64_t K, void* y_f16, void* workspace,
                   size_t workspace_bytes, ao_stream_t stream);

@@ -259,6 +259,103 @@ def from_scaled_tc_fp6(packed, scale_bits=None, ebits=3, mbits=2):
     return out
 
 
+# ----------------------------------------------------------------------------
+# generic tensor-core pre-packing for any bit width (numpy restatement of
+# torchao/prototype/quant_llm/quant_llm.py:15-86): the code's bits are split into 1-, 2- and 4-bit planes
+# (highest bits first); every plane is laid out so that word t of each 128-byte piece is warp lane t's data
+# ----------------------------------------------------------------------------
+_BIT_ORDER = {
+    1: [1, 5, 9, 13, 17, 21, 25, 29, 3, 7, 11, 15, 19, 23, 27, 31, 0, 4, 8, 12, 16, 20, 24, 28, 2, 6, 10, 14, 18, 22, 26, 30],
+    2: [1, 5, 9, 13, 3, 7, 11, 15, 0, 4, 8, 12, 2, 6, 10, 14],
+    4: [1, 5, 3, 7, 0, 4, 2, 6],
+}
+
+
+def _pack_bits(x, n_bits):
+    """8 // n_bits consecutive elements of the last axis -> one byte, first element in the highest bits."""
+    per = 8 // n_bits
+    out = np.zeros(x.shape[:-1] + (x.shape[-1] // per,), np.uint8)
+    for i in range(per):
+        out |= (x[..., i::per].astype(np.uint8) << (8 - (i + 1) * n_bits)).astype(np.uint8)
+    return out
+
+
+def _unpack_bits(x, n_bits):
+    per = 8 // n_bits
+    parts = [(x >> (8 - (i + 1) * n_bits)) & ((1 << n_bits) - 1) for i in range(per)]
+    return np.stack(parts, axis=-1).reshape(x.shape[:-1] + (x.shape[-1] * per,))
+
+
+def _bit_interleave(x, n_bits, undo=False):
+    x = x.reshape(-1, 4)[:, ::-1]                       # bytes of a 32-bit word, most significant first
+    x = _unpack_bits(x, n_bits).reshape(-1, 4 * (8 // n_bits))
+    order = _BIT_ORDER[n_bits]
+    if undo:
+        order = [order.index(i) for i in range(len(order))]
+    x = _pack_bits(x[:, order], n_bits)
+    return x.reshape(-1, 4)[:, ::-1].reshape(-1)
+
+
+def pack_tc_fpx(codes, nbits):
+    """codes uint8 [M][N] (one nbits-wide code per byte) -> uint8 [M][N * nbits / 8]."""
+    t = np.ascontiguousarray(codes, np.uint8)
+    M, N = t.shape
+    assert M % 64 == 0 and N % 64 == 0
+    t = t.reshape(M // 64, 4, 2, 8, N // 16, 2, 8).transpose(0, 4, 1, 5, 2, 3, 6).reshape(-1, 32, 2)
+    t = t.transpose(1, 0, 2).reshape(-1)
+    used, planes = 0, []
+    for y in (1, 2, 4):
+        if nbits & y:
+            plane = (t >> (nbits - used - y)) & ((1 << y) - 1)
+            plane = _pack_bits(plane, y)
+            plane = plane.reshape(32, -1, 4).transpose(1, 0, 2)[:, :, ::-1].reshape(-1)
+            planes.append(_bit_interleave(np.ascontiguousarray(plane), y))
+            used += y
+    return np.concatenate(planes).reshape(M, -1)
+
+
+def unpack_tc_fpx(packed, nbits):
+    """Inverse of pack_tc_fpx."""
+    p = np.ascontiguousarray(packed, np.uint8)
+    M = p.shape[0]
+    size = p.size
+    N = p.shape[1] // nbits * 8
+    flat = p.reshape(-1)
+    offset, used = 0, 0
+    total = None
+    for y in (1, 2, 4):
+        if nbits & y:
+            n = size * y // nbits
+            plane = _bit_interleave(flat[offset:offset + n], y, undo=True)
+            plane = plane.reshape(-1, 32, 4)[:, :, ::-1].transpose(1, 0, 2).reshape(-1)
+            vals = _unpack_bits(np.ascontiguousarray(plane), y).astype(np.uint8) << (nbits - used - y)
+            total = vals if total is None else (total | vals)
+            offset += n
+            used += y
+    t = total.reshape(32, -1, 2).transpose(1, 0, 2).reshape(M // 64, N // 16, 4, 2, 2, 8, 8)
+    return np.ascontiguousarray(t.transpose(0, 2, 4, 5, 1, 3, 6)).reshape(M, N)
+
+
+def to_scaled_tc_fpx(w_f32, ebits, mbits):
+    """to_scaled_tc_fpx for any ExMy the generic packer takes (quant_llm.py:116-130): per-row scale =
+    max(absmax, 1e-12) / max_normal in fp32, codes of w / scale, pre-packed.  -> (packed, fp16 scale bits)."""
+    w = np.ascontiguousarray(w_f32, np.float32)
+    bias = (1 << (ebits - 1)) - 1
+    max_normal = np.float32(2.0 ** (((1 << ebits) - 1) - bias) * (((1 << (mbits + 1)) - 1) / (1 << mbits)))
+    amax = np.maximum(np.abs(w).max(axis=1), np.float32(1e-12)).astype(np.float32)
+    scale = (amax / max_normal).astype(np.float32)
+    codes = f32_to_fpx_unpacked((w / scale[:, None]).astype(np.float32), ebits, mbits)
+    return pack_tc_fpx(codes, 1 + ebits + mbits), scale.astype(np.float16).view(np.uint16)
+
+
+def from_scaled_tc_fpx(packed, scale_bits, ebits, mbits):
+    codes = unpack_tc_fpx(packed, 1 + ebits + mbits)
+    v = fpx_unpacked_to_f32(codes, ebits, mbits)
+    if scale_bits is not None:
+        v = v * f16_bits_to_f32(np.asarray(scale_bits, np.uint16))[:, None]
+    return v.astype(np.float32)
+
+
 def hqq_quants_to_torch_quants(wq, scale_bits, zero_bits, dt):
     """torchao/prototype/hqq/hqq_tinygemm_linear.py:173-208 for 4 bits: wq uint8 [groups][g], scale / zero bit
     patterns [groups] of dtype dt (BF16 or F16) -> (int32 codes [groups][g], new_zero bit patterns [groups]);

@@ -98,8 +98,8 @@ def test_bad_arguments_raise():
         ops.quant_llm_linear(3, 2, x.float(), w, s, 1)
     with pytest.raises(RuntimeError, match="Dimensions mismatched"):
         ops.quant_llm_linear(3, 2, x, w[:, :100], s, 1)
-    with pytest.raises(NotImplementedError):
-        ops.quant_llm_linear(2, 2, x, torch.zeros(256, 320, dtype=torch.uint8, device="cuda"), s, 1)
+    with pytest.raises(RuntimeError, match="is not supported"):
+        ops.quant_llm_linear(2, 1, x, torch.zeros(256, 256, dtype=torch.uint8, device="cuda"), s, 1)
 
 
 @pytest.mark.parametrize("N,K", [(256, 512), (1024, 4096), (4096, 1024)])
@@ -160,6 +160,54 @@ def test_e2m3_linear_vs_reference_fixture_and_oracle():
         y = lin(x.cuda()).detach()
         assert rel_err(tu.f32(y), orc.linear_f32(x.float().numpy(), wd)) <= TOL, f"M={M}"
     assert _cabi.workspace_status("cuda") == 0
-    with pytest.raises(NotImplementedError):
-        ops.quant_llm_linear(2, 2, x.cuda(), torch.zeros(N, K // 8 * 5, dtype=torch.uint8, device="cuda"),
+    with pytest.raises(RuntimeError, match="is not supported"):
+        ops.quant_llm_linear(2, 1, x.cuda(), torch.zeros(N, K // 8 * 4, dtype=torch.uint8, device="cuda"),
                              torch.ones(N, dtype=torch.float16, device="cuda"), 1)
+
+
+def test_generic_packer_5_and_6_bits_bit_exact():
+    from ao_b200.prototype.quant_llm.quant_llm import pack_tc_fpx, unpack_tc_fpx
+    A = gu.load("fp5.npz")
+    for key, nbits in (("pack5", 5), ("pack6", 6)):
+        codes = torch.from_numpy(A[f"{key}/codes"]).cuda()
+        packed = pack_tc_fpx(codes, nbits)
+        assert np.array_equal(packed.cpu().numpy(), A[f"{key}/packed"])
+        assert torch.equal(unpack_tc_fpx(packed, nbits), codes)
+
+
+@pytest.mark.parametrize("fmt", [(2, 2), (3, 1)], ids=["e2m2", "e3m1"])
+def test_fp5_formats_codec_and_linear(fmt):
+    from ao_b200 import _cabi, ops
+    from ao_b200.prototype.quant_llm import quant_llm_fpx_weight_only
+    from ao_b200.prototype.quant_llm.quant_llm import from_scaled_tc_fpx, to_scaled_tc_fpx
+    from ao_b200.quantization import quantize
+    e, m = fmt
+    name = f"e{e}m{m}"
+    A = gu.load("fp5.npz")
+    w = tu.to_torch(A[f"{name}/w"], "f16")
+    packed, scale = to_scaled_tc_fpx(w, e, m)
+    assert np.array_equal(tu.bits(packed), A[f"{name}/packed"])
+    assert np.array_equal(tu.bits(scale), A[f"{name}/scale"])
+    assert np.array_equal(tu.f32(from_scaled_tc_fpx(packed, e, m, scale)), A[f"{name}/dequant_f32"])
+    packed = tu.to_torch(A[f"{name}_lin/packed"], "u8")
+    scale = tu.to_torch(A[f"{name}_lin/scale"], "f16")
+    for M in (1, 16, 64):
+        x = tu.to_torch(A[f"{name}_lin/x_m{M}"], "f16")
+        y = ops.quant_llm_linear(e, m, x, packed, scale, 1)
+        assert rel_err(tu.f32(y), A[f"{name}_lin/y_m{M}"]) <= TOL, f"M={M}"
+    # larger shapes against the oracle, decode and prefill kernels, through the weight subclass
+    N, K = 1024, 4096
+    w = tu.make_weight((N, K), seed=91 + e, dtype=torch.float16, outliers=False)
+    packed_ref, scale_ref = orc.to_scaled_tc_fpx(w.float().numpy(), e, m)
+    wd = orc.from_scaled_tc_fpx(packed_ref, scale_ref, e, m)
+    lin = torch.nn.Linear(K, N, bias=False, device="cuda", dtype=torch.float16)
+    with torch.no_grad():
+        lin.weight.copy_(w)
+    quantize(lin, quant_llm_fpx_weight_only(e, m))
+    assert np.array_equal(tu.bits(lin.weight.fpx_data), packed_ref)
+    g = torch.Generator().manual_seed(6)
+    for M in (1, 4, 8, 17, 100, 256):
+        x = torch.randn(M, K, generator=g).half()
+        y = lin(x.cuda()).detach()
+        assert rel_err(tu.f32(y), orc.linear_f32(x.float().numpy(), wd)) <= TOL, f"M={M}"
+    assert _cabi.workspace_status("cuda") == 0

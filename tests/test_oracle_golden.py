@@ -188,3 +188,23 @@ def test_e2m3_to_scaled_and_from_scaled_match_reference(name):
     assert np.array_equal(packed, A[f"{name}/packed"])
     assert np.array_equal(scale, A[f"{name}/scale"])
     assert np.array_equal(orc.from_scaled_tc_fp6(packed, scale, 2, 3), A[f"{name}/dequant_f32"])
+
+
+def test_generic_tc_packer_matches_reference_for_5_and_6_bits():
+    A = gu.load("fp5.npz")
+    for key, nbits in (("pack5", 5), ("pack6", 6)):
+        packed = orc.pack_tc_fpx(A[f"{key}/codes"], nbits)
+        assert np.array_equal(packed, A[f"{key}/packed"])
+        assert np.array_equal(orc.unpack_tc_fpx(packed, nbits), A[f"{key}/codes"])
+    assert np.array_equal(orc.pack_tc_fpx(A["pack6/codes"], 6), orc.pack_tc_fp6(A["pack6/codes"]))
+
+
+@pytest.mark.parametrize("fmt", [(2, 2), (3, 1)], ids=["e2m2", "e3m1"])
+def test_fp5_to_scaled_and_from_scaled_match_reference(fmt):
+    A = gu.load("fp5.npz")
+    e, m = fmt
+    name = f"e{e}m{m}"
+    packed, scale = orc.to_scaled_tc_fpx(orc.f16_bits_to_f32(A[f"{name}/w"]), e, m)
+    assert np.array_equal(packed, A[f"{name}/packed"])
+    assert np.array_equal(scale, A[f"{name}/scale"])
+    assert np.array_equal(orc.from_scaled_tc_fpx(packed, scale, e, m), A[f"{name}/dequant_f32"])
