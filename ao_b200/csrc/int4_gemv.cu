@@ -38,6 +38,7 @@ int make_plan(int64_t M, int64_t N, int64_t K, int g, int ikt, Plan* P) {
     // a stage holds one row pair x up to kMaxSubs sub-units of K
     P->subs = P->KS / P->UK;
     P->SUBS = P->subs < kMaxSubs ? P->subs : kMaxSubs;
+    { const char* e = getenv("AO_GEMV_SUBS"); if (e && atoi(e) < P->SUBS) P->SUBS = atoi(e); }
     P->cpp = (P->subs + P->SUBS - 1) / P->SUBS;
     if ((long long)P->NP * P->cpp > (1LL << 30)) return AO_ERR_SHAPE;
     const int stage_raw = 2 * P->SUBS * P->UB + P->SUBS * P->GPU * 64;
@@ -47,6 +48,8 @@ int make_plan(int64_t M, int64_t N, int64_t K, int g, int ikt, Plan* P) {
     const int xs_bytes = 2 * P->KS * P->MR * P->NB, zero_bytes = (P->UK / 32) * P->NB * P->MR * 64;
     const int sx_bytes = (P->KS / g) * P->NB * 32, p32_bytes = (P->KS / 32) * P->NB * 32;
     int nwarps = kMaxConsumerWarps, stages = kMaxStages;
+    { const char* e = getenv("AO_GEMV_NWARPS"); if (e) nwarps = atoi(e); }
+    { const char* e = getenv("AO_GEMV_STAGES"); if (e) stages = atoi(e); }
     for (;;) {
         const int total = xs_bytes + zero_bytes + sx_bytes + p32_bytes + 2 * nwarps * P->NB * 512 + 512 +
                           stages * P->stage_bytes;
@@ -67,6 +70,7 @@ int make_plan(int64_t M, int64_t N, int64_t K, int g, int ikt, Plan* P) {
     P->p32_off = off;
     off += p32_bytes;
     int G = kNumSMs / nslabs;
+    { const char* e = getenv("AO_GEMV_GRIDMUL"); if (e) G *= atoi(e); }
     if (G < 1) G = 1;
     if (G > P->NP) G = P->NP;
     P->G = G;

@@ -395,13 +395,20 @@ int4_gemv_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int Kx, con
         }
         ptx::fence_mbar_init();
     }
-    __syncthreads();
+    // the producer warp only announces that the barriers exist and goes straight to its first copies
+    if (warp == nwarps) {
+        __syncwarp();
+        ptx::named_barrier_arrive(2, blockDim.x);
+    } else {
+        ptx::named_barrier_sync(2, blockDim.x);
+    }
 
     if (warp == nwarps) {
         // =============================== producer warp =================================================
         // stage = [tile A bytes][tile B bytes][scales/zeros: one 64-byte row per group]
         int pi = 0, c = 0, s = 0;
         uint32_t phase = 1;  // a fresh barrier counts as "previous phase complete"
+        const uint64_t stream_once = ptx::l2_policy_evict_first();   // every weight byte is read exactly once
         bool ok = true;
         for (int t = 0; t < nstage_total; ++t) {
             if (!ptx::mbar_wait_bounded(empty_bar + 8 * s, phase, kWaitPolls)) {
@@ -419,8 +426,8 @@ int4_gemv_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int Kx, con
                 const uint32_t wbytes = static_cast<uint32_t>(nsub * UB);
                 const uint8_t* src = wq + ((size_t)(2 * p) * P.K + k0) * 4;
                 ptx::mbar_arrive_expect_tx(bar, has_b ? 2u * wbytes : wbytes);
-                ptx::bulk_copy_g2s(dst, src, wbytes, bar);
-                if (has_b) ptx::bulk_copy_g2s(dst + tile_b, src + (size_t)P.K * 4, wbytes, bar);
+                ptx::bulk_copy_g2s_hint(dst, src, wbytes, bar, stream_once);
+                if (has_b) ptx::bulk_copy_g2s_hint(dst + tile_b, src + (size_t)P.K * 4, wbytes, bar, stream_once);
             }
             {
                 // 64 bytes ((scale, zero) of the pair's 16 rows) per group; a lone last tile has only 32
@@ -516,35 +523,48 @@ int4_gemv_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int Kx, con
         float* p32 = reinterpret_cast<float*>(smem + P.p32_off);
         // lanes without a batch column read zeros: one sub-unit's worth of fragment bytes
         for (int i = tid; i < S::SPU * S::XSTEP / 4; i += nconsumers) reinterpret_cast<uint32_t*>(smem + P.zero_off)[i] = 0u;
-        for (int it = tid; it < items_round; it += nconsumers) {
-            uint4 wv = make_uint4(0u, 0u, 0u, 0u);
-            float psum = 0.f;
-            int l = 0, blk = 0;
-            if (it < items) {
-                l = it % MRL;
-                blk = it / MRL;  // step * NB + nb
-                const int nb = blk % NB, step = blk / NB;
-                const int m = nb * 8 + (l >> 2), c = l & 3;
-                if (m < P.M) {
-                    const int k = slab * P.KS + step * 32 + 2 * c;
-                    const uint32_t* row = reinterpret_cast<const uint32_t*>(x + (long long)m * ldx);
-                    uint32_t w[4];
+        // every CTA re-reads x: keep it in L2 while the weights stream through.  The loads of four rounds of items
+        // are issued before any is used, so the prologue costs one memory latency, not one per round.
+        const uint64_t keep = ptx::l2_policy_evict_last();
+        constexpr int kRounds = 4;
+        for (int it0 = tid; it0 < items_round; it0 += kRounds * nconsumers) {
+            uint32_t w[kRounds][4];
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        const int kk = k + 8 * q;
-                        w[q] = (kk < Kx) ? __ldg(row + (kk >> 1)) : 0u;
+            for (int u = 0; u < kRounds; ++u) {
+                const int it = it0 + u * nconsumers;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) w[u][q] = 0u;
+                if (it < items) {
+                    const int l = it % MRL, blk = it / MRL;  // blk = step * NB + nb
+                    const int nb = blk % NB, step = blk / NB;
+                    const int m = nb * 8 + (l >> 2), c = l & 3;
+                    if (m < P.M) {
+                        const int k = slab * P.KS + step * 32 + 2 * c;
+                        const uint32_t* row = reinterpret_cast<const uint32_t*>(x + (long long)m * ldx);
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const int kk = k + 8 * q;
+                            if (kk < Kx) w[u][q] = ptx::ldg_u32_hint(row + (kk >> 1), keep);
+                        }
                     }
-                    wv = make_uint4(w[0], w[1], w[2], w[3]);
-#pragma unroll
-                    for (int q = 0; q < 4; ++q)
-                        psum += bf16_bits_to_f32(w[q] & 0xffffu) + __uint_as_float(w[q] & 0xffff0000u);
                 }
-                *reinterpret_cast<uint4*>(smem + P.xs_off + (size_t)it * 16) = wv;
             }
-            // the four lanes (c = 0..3) of a batch column are adjacent
-            psum += __shfl_xor_sync(0xffffffffu, psum, 1);
-            psum += __shfl_xor_sync(0xffffffffu, psum, 2);
-            if (it < items && (l & 3) == 0) p32[blk * 8 + (l >> 2)] = psum;
+#pragma unroll
+            for (int u = 0; u < kRounds; ++u) {
+                const int it = it0 + u * nconsumers;
+                if (it >= items_round) break;   // uniform over the warp: items_round is a multiple of 32
+                float psum = 0.f;
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+                    psum += bf16_bits_to_f32(w[u][q] & 0xffffu) + __uint_as_float(w[u][q] & 0xffff0000u);
+                if (it < items)
+                    *reinterpret_cast<uint4*>(smem + P.xs_off + (size_t)it * 16) = make_uint4(w[u][0], w[u][1], w[u][2], w[u][3]);
+                // the four lanes (c = 0..3) of a batch column are adjacent
+                psum += __shfl_xor_sync(0xffffffffu, psum, 1);
+                psum += __shfl_xor_sync(0xffffffffu, psum, 2);
+                const int l = it % MRL, blk = it / MRL;
+                if (it < items && (l & 3) == 0) p32[blk * 8 + (l >> 2)] = psum;
+            }
         }
         ptx::named_barrier_sync(1, nconsumers);
         float* sx = reinterpret_cast<float*>(smem + P.sx_off);

@@ -77,6 +77,32 @@ __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst_smem, const void* src
                  : "memory");
 }
 
+// L2 eviction policies: streamed-once data (weights) leaves the cache first, data every CTA re-reads (activations) last
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ void bulk_copy_g2s_hint(uint32_t dst_smem, const void* src_gmem, uint32_t bytes, uint32_t bar,
+                                                   uint64_t policy) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(dst_smem),
+                 "l"(src_gmem), "r"(bytes), "r"(bar), "l"(policy)
+                 : "memory");
+}
+__device__ __forceinline__ uint32_t ldg_u32_hint(const uint32_t* p, uint64_t policy) {
+    uint32_t v;
+    asm volatile("ld.global.L2::cache_hint.u32 %0, [%1], %2;" : "=r"(v) : "l"(p), "l"(policy));
+    return v;
+}
+__device__ __forceinline__ void named_barrier_arrive(int id, int nthreads) {
+    asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
 // 2-D tiled TMA load (no multicast): box at element coordinates (x, y) of the tensor map -> shared memory.
 // x * element size must be a multiple of 16 bytes.
 __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const void* tensor_map, int x, int y, uint32_t bar) {
