@@ -30,7 +30,7 @@ int make_plan(int64_t M, int64_t N, int64_t K, int g, int ikt, Plan* P) {
         const int subs_ = ks / P->UK, SUBS_ = subs_ < kMaxSubs ? subs_ : kMaxSubs;
         const int stage_ = ((2 * SUBS_ * P->UB + SUBS_ * P->GPU * 64 + 127) / 128) * 128;
         const long long need = 2LL * ks * P->MR * P->NB + (P->UK / 32) * P->NB * P->MR * 64 + (ks / g) * P->NB * 32 +
-                               (ks / 32) * P->NB * 32 + 2 * 8 * P->NB * 512 + 512 + 2 * stage_;
+                               2 * 8 * P->NB * 512 + 512 + 2 * stage_;
         if (need <= 220 * 1024) break;
     }
     P->nslabs = nslabs;
@@ -43,15 +43,15 @@ int make_plan(int64_t M, int64_t N, int64_t K, int g, int ikt, Plan* P) {
     if ((long long)P->NP * P->cpp > (1LL << 30)) return AO_ERR_SHAPE;
     const int stage_raw = 2 * P->SUBS * P->UB + P->SUBS * P->GPU * 64;
     P->stage_bytes = ((stage_raw + 127) / 128) * 128;
-    // shared memory: stage ring, x fragments, zero block, group sums, partial sums (two pair parities),
+    // shared memory: stage ring, x fragments, zero block, group sums of x, partial sums (two pair parities),
     // control block, barriers.  As many consumer warps (24, 16, 8) and as deep a ring (4 .. 2) as fit.
     const int xs_bytes = 2 * P->KS * P->MR * P->NB, zero_bytes = (P->UK / 32) * P->NB * P->MR * 64;
-    const int sx_bytes = (P->KS / g) * P->NB * 32, p32_bytes = (P->KS / 32) * P->NB * 32;
+    const int sx_bytes = (P->KS / g) * P->NB * 32;
     int nwarps = kMaxConsumerWarps, stages = kMaxStages;
     { const char* e = getenv("AO_GEMV_NWARPS"); if (e) nwarps = atoi(e); }
     { const char* e = getenv("AO_GEMV_STAGES"); if (e) stages = atoi(e); }
     for (;;) {
-        const int total = xs_bytes + zero_bytes + sx_bytes + p32_bytes + 2 * nwarps * P->NB * 512 + 512 +
+        const int total = xs_bytes + zero_bytes + sx_bytes + 2 * nwarps * P->NB * 512 + 512 +
                           stages * P->stage_bytes;
         if (total <= 220 * 1024) break;
         if (stages > 2) stages = 2;   // the ring depth stays a power of two
@@ -67,8 +67,6 @@ int make_plan(int64_t M, int64_t N, int64_t K, int g, int ikt, Plan* P) {
     off += zero_bytes;
     P->sx_off = off;
     off += sx_bytes;
-    P->p32_off = off;
-    off += p32_bytes;
     int G = kNumSMs / nslabs;
     { const char* e = getenv("AO_GEMV_GRIDMUL"); if (e) G *= atoi(e); }
     if (G < 1) G = 1;

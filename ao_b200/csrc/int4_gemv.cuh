@@ -60,7 +60,7 @@ struct Plan {
     int nbuf;          // ring of per-pair partial-sum buffers (a power of two)
     int stages, stage_bytes;  // ring depth (a power of two), bytes per stage
     int gw_shift, stage_shift, nbuf_shift;  // log2 of GW, stages, nbuf: the per-stage bookkeeping has no divisions
-    int xs_off, zero_off, sx_off, p32_off, part_off, bar_off, smem_bytes;
+    int xs_off, zero_off, sx_off, part_off, bar_off, smem_bytes;
     uint32_t nib_mask, magic;  // 0x000F000F, bf16x2 (128, 128): runtime values so they stay in registers
     size_t ws_counters_off, ws_slots_off, ws_bytes;
     // output exchange over peer memory (nranks > 1): every CTA sends its rows to every peer as 8-byte
@@ -517,34 +517,48 @@ int4_gemv_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int Kx, con
     ptx::grid_dependency_wait();       // x may be the output of the previous kernel
     // ---- activation prologue: x slab -> MMA fragment order, plus per-group sums of x -------------------
     {
-        const int steps = P.KS / 32;
-        const int items = steps * NB * MRL;  // one item = 4 words (two k16 tiles) of one lane
+        // One item = 8 consecutive k of one batch row (16 bytes, one vector load: every CTA reads all of x, so the
+        // number of L2 requests per CTA is what this prologue costs).  Its four bf16 pairs go to the four lanes
+        // c = 0..3 of the row's fragment column; the g / 8 items of a quantization group sit in adjacent lanes and
+        // add up their x with shuffles.
+        constexpr int G8 = G32 * 4;                 // items per quantization group
+        const int octs = P.KS / 8;                  // items per batch row (a multiple of G8)
+        const int items = octs * (NB * MR);         // rows at and beyond M are zeros
         const int items_round = (items + 31) / 32 * 32;
-        float* p32 = reinterpret_cast<float*>(smem + P.p32_off);
+        float* sx = reinterpret_cast<float*>(smem + P.sx_off);
         // lanes without a batch column read zeros: one sub-unit's worth of fragment bytes
         for (int i = tid; i < S::SPU * S::XSTEP / 4; i += nconsumers) reinterpret_cast<uint32_t*>(smem + P.zero_off)[i] = 0u;
-        // every CTA re-reads x: keep it in L2 while the weights stream through.  The loads of four rounds of items
-        // are issued before any is used, so the prologue costs one memory latency, not one per round.
+        if constexpr (MR < 8) {
+            // group sums of the fragment columns that carry no batch row
+            const int groups = P.KS / (32 * G32);
+            for (int i = tid; i < groups * NB * 8; i += nconsumers)
+                if ((i & 7) >= MR) sx[i] = 0.f;
+        }
+        // x stays in L2 while the weights stream through.  The loads of four rounds of items are issued before any
+        // is used, so the prologue costs one memory latency, not one per round.
         const uint64_t keep = ptx::l2_policy_evict_last();
+        const bool vec_ok = ((reinterpret_cast<uintptr_t>(x) & 15) == 0) && ((ldx & 7) == 0);
         constexpr int kRounds = 4;
         for (int it0 = tid; it0 < items_round; it0 += kRounds * nconsumers) {
-            uint32_t w[kRounds][4];
+            uint4 w[kRounds];
 #pragma unroll
             for (int u = 0; u < kRounds; ++u) {
                 const int it = it0 + u * nconsumers;
-#pragma unroll
-                for (int q = 0; q < 4; ++q) w[u][q] = 0u;
+                w[u] = make_uint4(0u, 0u, 0u, 0u);
                 if (it < items) {
-                    const int l = it % MRL, blk = it / MRL;  // blk = step * NB + nb
-                    const int nb = blk % NB, step = blk / NB;
-                    const int m = nb * 8 + (l >> 2), c = l & 3;
+                    const int rr = it / octs, j = it - rr * octs;
+                    const int m = (rr / MR) * 8 + (rr % MR);
                     if (m < P.M) {
-                        const int k = slab * P.KS + step * 32 + 2 * c;
-                        const uint32_t* row = reinterpret_cast<const uint32_t*>(x + (long long)m * ldx);
-#pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            const int kk = k + 8 * q;
-                            if (kk < Kx) w[u][q] = ptx::ldg_u32_hint(row + (kk >> 1), keep);
+                        const int k = slab * P.KS + 8 * j;
+                        const __nv_bfloat16* row = x + (long long)m * ldx;
+                        if (vec_ok && k + 8 <= Kx) {
+                            w[u] = ptx::ldg_u32x4_hint(row + k, keep);
+                        } else {
+                            const uint32_t* row32 = reinterpret_cast<const uint32_t*>(row);
+                            if (k < Kx) w[u].x = ptx::ldg_u32_hint(row32 + (k >> 1), keep);
+                            if (k + 2 < Kx) w[u].y = ptx::ldg_u32_hint(row32 + (k >> 1) + 1, keep);
+                            if (k + 4 < Kx) w[u].z = ptx::ldg_u32_hint(row32 + (k >> 1) + 2, keep);
+                            if (k + 6 < Kx) w[u].w = ptx::ldg_u32_hint(row32 + (k >> 1) + 3, keep);
                         }
                     }
                 }
@@ -553,30 +567,22 @@ int4_gemv_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int Kx, con
             for (int u = 0; u < kRounds; ++u) {
                 const int it = it0 + u * nconsumers;
                 if (it >= items_round) break;   // uniform over the warp: items_round is a multiple of 32
+                const uint32_t wv[4] = {w[u].x, w[u].y, w[u].z, w[u].w};
                 float psum = 0.f;
 #pragma unroll
-                for (int q = 0; q < 4; ++q)
-                    psum += bf16_bits_to_f32(w[u][q] & 0xffffu) + __uint_as_float(w[u][q] & 0xffff0000u);
-                if (it < items)
-                    *reinterpret_cast<uint4*>(smem + P.xs_off + (size_t)it * 16) = make_uint4(w[u][0], w[u][1], w[u][2], w[u][3]);
-                // the four lanes (c = 0..3) of a batch column are adjacent
-                psum += __shfl_xor_sync(0xffffffffu, psum, 1);
-                psum += __shfl_xor_sync(0xffffffffu, psum, 2);
-                const int l = it % MRL, blk = it / MRL;
-                if (it < items && (l & 3) == 0) p32[blk * 8 + (l >> 2)] = psum;
-            }
-        }
-        ptx::named_barrier_sync(1, nconsumers);
-        float* sx = reinterpret_cast<float*>(smem + P.sx_off);
-        const int groups = P.KS / (32 * G32);
-        for (int it = tid; it < groups * NB * 8; it += nconsumers) {
-            const int mm = it & 7, nb = (it >> 3) % NB, kg = it / (8 * NB);
-            float s = 0.f;
-            if (mm < MR) {
+                for (int c = 0; c < 4; ++c) psum += bf16_bits_to_f32(wv[c] & 0xffffu) + __uint_as_float(wv[c] & 0xffff0000u);
 #pragma unroll
-                for (int q = 0; q < G32; ++q) s += p32[((kg * G32 + q) * NB + nb) * 8 + mm];
+                for (int o = 1; o < G8; o <<= 1) psum += __shfl_xor_sync(0xffffffffu, psum, o);
+                if (it < items) {
+                    const int rr = it / octs, j = it - rr * octs;
+                    const int nb = rr / MR, mm = rr % MR;
+                    // pair c of octet j is word (j & 3) of lane (mm, c) at k32 step j / 4
+                    uint32_t* dst = reinterpret_cast<uint32_t*>(smem + P.xs_off) + (((j >> 2) * NB + nb) * MRL + mm * 4) * 4 + (j & 3);
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) dst[c * 4] = wv[c];
+                    if ((j & (G8 - 1)) == 0) sx[((j / G8) * NB + nb) * 8 + mm] = psum;
+                }
             }
-            sx[it] = s;
         }
         ptx::named_barrier_sync(1, nconsumers);
     }

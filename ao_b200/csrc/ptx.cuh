@@ -99,6 +99,11 @@ __device__ __forceinline__ uint32_t ldg_u32_hint(const uint32_t* p, uint64_t pol
     asm volatile("ld.global.L2::cache_hint.u32 %0, [%1], %2;" : "=r"(v) : "l"(p), "l"(policy));
     return v;
 }
+__device__ __forceinline__ uint4 ldg_u32x4_hint(const void* p, uint64_t policy) {
+    uint4 v;
+    asm volatile("ld.global.L2::cache_hint.v4.u32 {%0,%1,%2,%3}, [%4], %5;" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p), "l"(policy));
+    return v;
+}
 __device__ __forceinline__ void named_barrier_arrive(int id, int nthreads) {
     asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
