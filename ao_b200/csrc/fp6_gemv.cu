@@ -132,19 +132,35 @@ static int make_plan(int64_t M, int64_t N, int64_t K, int fmt_id, Plan* P) {
     P->smem_bytes = off;
     P->ws_counters_off = kHeaderBytes;
     P->ws_slots_off = kHeaderBytes + (size_t)kMaxBlocks * 4;
-    P->ws_bytes = P->ws_slots_off + (best > 1 ? (size_t)best * P->NA * 4 * P->NB * 512 : 0);
+    P->ws_bytes = P->ws_slots_off + (best > 1 ? (size_t)best * P->NA * 4 * P->NB * 1024 : 0);   // {value, tag} words
     return AO_OK;
+}
+
+// post_scale * scale[row] of the eight rows this lane stores of row block a (fragment fr: rows e and e + 8)
+struct RowScales {
+    float s0[4], s1[4];
+};
+__device__ __forceinline__ RowScales load_row_scales(const Plan& P, int a, int lane, const __half* __restrict__ scale) {
+    RowScales r;
+    const int row = lane >> 2;
+#pragma unroll
+    for (int fr = 0; fr < 4; ++fr) {
+        const int n0 = a * 64 + fr * 16 + row;
+        r.s0[fr] = P.fmt.post_scale * __half2float(scale[n0]);
+        r.s1[fr] = P.fmt.post_scale * __half2float(scale[n0 + 8]);
+    }
+    return r;
 }
 
 // rows of fragment fr (16 rows) of row block a: store y = acc * 2^12 * scale[row]
 template <int NB>
-__device__ __forceinline__ void store_block(const Plan& P, const float (&v)[4][NB][4], int a, int lane,
-                                            const __half* __restrict__ scale, __half* __restrict__ y) {
+__device__ __forceinline__ void store_block(const Plan& P, const float (&v)[4][NB][4], int a, int lane, const RowScales& rs,
+                                            __half* __restrict__ y) {
     const int row = lane >> 2, c = lane & 3;
 #pragma unroll
     for (int fr = 0; fr < 4; ++fr) {
         const int n0 = a * 64 + fr * 16 + row, n1 = n0 + 8;
-        const float s0 = P.fmt.post_scale * __half2float(scale[n0]), s1 = P.fmt.post_scale * __half2float(scale[n1]);
+        const float s0 = rs.s0[fr], s1 = rs.s1[fr];
 #pragma unroll
         for (int nb = 0; nb < NB; ++nb) {
             const int m0 = nb * 8 + 2 * c;
@@ -160,30 +176,47 @@ __device__ __forceinline__ void store_block(const Plan& P, const float (&v)[4][N
     }
 }
 
+// Header words of the workspace used by the K-slab hand-off: {CTAs of this launch that have finished, number of
+// slab launches completed so far}.  The second is the tag the partial sums of the next launch carry.
+constexpr int kCallStateOff = 16;
+
+__device__ __forceinline__ uint2 ld_volatile_u2(const uint2* p) {
+    uint2 v;
+    asm volatile("ld.volatile.global.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_volatile_u2(uint2* p, uint32_t a, uint32_t b) {
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(a), "r"(b) : "memory");
+}
+
+// K slabs.  The CTAs that share row block a draw a ticket from the block's counter when they start on it (the
+// round trip is over by the time their sums are ready); the one that drew the last ticket adds the slabs up and
+// stores y, the others leave their partial sums in their workspace slot as 8-byte {value, tag} words (tag = number of
+// this launch; an 8-byte store is written as a unit, so a word that carries the tag carries the value: no fence is
+// needed) and move on.  The finisher polls those words (bounded); it only ever waits for CTAs that hold a ticket,
+// i.e. are running and have no reason to wait for it, and every CTA walks the blocks in the same order.
 template <int NB>
-__device__ __noinline__ void finish_block(const Plan& P, const float (&v)[4][NB][4], int a, int slab, int lane,
-                                          const __half* __restrict__ scale, __half* __restrict__ y,
-                                          uint8_t* __restrict__ ws) {
+__device__ __noinline__ bool finish_block(const Plan& P, const float (&v)[4][NB][4], int a, int slab, int lane,
+                                          const RowScales& rs, __half* __restrict__ y, uint8_t* __restrict__ ws,
+                                          unsigned call, int ticket) {
     if (P.nslabs == 1) {
-        store_block<NB>(P, v, a, lane, scale, y);
-        return;
+        store_block<NB>(P, v, a, lane, rs, y);
+        return true;
     }
-    float4* slots = reinterpret_cast<float4*>(ws + P.ws_slots_off);
-    const size_t slot_stride = (size_t)4 * NB * 32;  // float4 per slot
-    float4* mine = slots + ((size_t)slab * P.NA + a) * slot_stride;
+    uint2* slots = reinterpret_cast<uint2*>(ws + P.ws_slots_off);
+    const size_t slot_stride = (size_t)4 * NB * 4 * 32;  // words per slot: [fragment][batch block][value][lane]
+    if (ticket + 1 != P.nslabs) {
+        uint2* mine = slots + ((size_t)slab * P.NA + a) * slot_stride + lane;
 #pragma unroll
-    for (int fr = 0; fr < 4; ++fr)
+        for (int fr = 0; fr < 4; ++fr)
 #pragma unroll
-        for (int nb = 0; nb < NB; ++nb)
-            mine[(fr * NB + nb) * 32 + lane] = make_float4(v[fr][nb][0], v[fr][nb][1], v[fr][nb][2], v[fr][nb][3]);
-    __threadfence();
-    __syncwarp();
-    int* counter = reinterpret_cast<int*>(ws + P.ws_counters_off) + a;
-    int old = 0;
-    if (lane == 0) old = atomicAdd(counter, 1);
-    old = __shfl_sync(0xffffffffu, old, 0);
-    if (old + 1 != P.nslabs) return;
-    __threadfence();
+            for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    st_volatile_u2(mine + ((fr * NB + nb) * 4 + i) * 32, __float_as_uint(v[fr][nb][i]), call);
+        return true;
+    }
+    if (lane == 0) *(reinterpret_cast<int*>(ws + P.ws_counters_off) + a) = 0;   // ready for the next call
     float sum[4][NB][4];
 #pragma unroll
     for (int fr = 0; fr < 4; ++fr)
@@ -191,18 +224,44 @@ __device__ __noinline__ void finish_block(const Plan& P, const float (&v)[4][NB]
         for (int nb = 0; nb < NB; ++nb)
 #pragma unroll
             for (int i = 0; i < 4; ++i) sum[fr][nb][i] = 0.f;
+    bool ok = true;
+    const uint64_t t0 = ptx::globaltimer_ns();
     for (int sl = 0; sl < P.nslabs; ++sl) {
-        const float4* src = slots + ((size_t)sl * P.NA + a) * slot_stride + lane;
+        if (sl == slab) {
 #pragma unroll
-        for (int fr = 0; fr < 4; ++fr)
+            for (int fr = 0; fr < 4; ++fr)
 #pragma unroll
-            for (int nb = 0; nb < NB; ++nb) {
-                const float4 q = ptx::ldcg_f32x4(src + (fr * NB + nb) * 32);
-                sum[fr][nb][0] += q.x; sum[fr][nb][1] += q.y; sum[fr][nb][2] += q.z; sum[fr][nb][3] += q.w;
-            }
+                for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) sum[fr][nb][i] += v[fr][nb][i];
+            continue;
+        }
+        const uint2* src = slots + ((size_t)sl * P.NA + a) * slot_stride + lane;
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) {
+            uint2 q[4][4];
+            // the sixteen loads of a batch block are issued before any is looked at: one round trip, not sixteen
+#pragma unroll
+            for (int fr = 0; fr < 4; ++fr)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) q[fr][i] = ld_volatile_u2(src + ((fr * NB + nb) * 4 + i) * 32);
+#pragma unroll
+            for (int fr = 0; fr < 4; ++fr)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    while (q[fr][i].y != call) {
+                        if (ptx::globaltimer_ns() - t0 > 200000000ull) {   // 0.2 s
+                            ok = false;
+                            break;
+                        }
+                        q[fr][i] = ld_volatile_u2(src + ((fr * NB + nb) * 4 + i) * 32);
+                    }
+                    sum[fr][nb][i] += __uint_as_float(q[fr][i].x);
+                }
+        }
     }
-    store_block<NB>(P, sum, a, lane, scale, y);
-    if (lane == 0) *counter = 0;
+    store_block<NB>(P, sum, a, lane, rs, y);
+    return __all_sync(0xffffffffu, ok);
 }
 
 template <int NB, int MR, int NBITS>
@@ -245,7 +304,13 @@ fp6_gemv_kernel(const __half* __restrict__ x, long long ldx, const uint8_t* __re
         }
         ptx::fence_mbar_init();
     }
-    __syncthreads();
+    // the producer warp only announces that the barriers exist and goes straight to its first copies
+    if (warp == nwarps) {
+        __syncwarp();
+        ptx::named_barrier_arrive(2, blockDim.x);
+    } else {
+        ptx::named_barrier_sync(2, blockDim.x);
+    }
 
     if (warp == nwarps) {
         // =============================== producer warp =================================================
@@ -256,6 +321,7 @@ fp6_gemv_kernel(const __half* __restrict__ x, long long ldx, const uint8_t* __re
             int ai = 0, c = 0, s = 0;
             uint32_t phase = 1;
             bool ok = true;
+            const uint64_t stream_once = ptx::l2_policy_evict_first();   // every weight byte is read exactly once
             for (int t = 0; t < nstage_total; ++t) {
                 if (!ptx::mbar_wait_bounded(empty_bar + 8 * s, phase, kWaitPolls)) {
                     ok = false;
@@ -268,8 +334,8 @@ fp6_gemv_kernel(const __half* __restrict__ x, long long ldx, const uint8_t* __re
                 const uint32_t dst = smem_base + s * stage_bytes;
                 const uint32_t bar = full_bar + 8 * s;
                 ptx::mbar_arrive_expect_tx(bar, nf * (HI + 512u));
-                ptx::bulk_copy_g2s(dst, plane2 + tile_index * HI, nf * HI, bar);
-                ptx::bulk_copy_g2s(dst + plane4_off, plane4 + tile_index * 512, nf * 512u, bar);
+                ptx::bulk_copy_g2s_hint(dst, plane2 + tile_index * HI, nf * HI, bar, stream_once);
+                ptx::bulk_copy_g2s_hint(dst + plane4_off, plane4 + tile_index * 512, nf * 512u, bar, stream_once);
                 if (++c == cpb) {
                     c = 0;
                     ++ai;
@@ -292,8 +358,15 @@ fp6_gemv_kernel(const __half* __restrict__ x, long long ldx, const uint8_t* __re
         // =============================== reducer warp ==================================================
         ptx::grid_dependency_wait();   // y and the workspace may be in use by earlier kernels
         bool ok = true;
+        // tag of this launch's partial sums (all CTAs read the same value: it changes when the last one finishes)
+        unsigned* call_state = reinterpret_cast<unsigned*>(ws + kCallStateOff);
+        const unsigned call = P.nslabs > 1 ? *reinterpret_cast<volatile unsigned*>(call_state + 1) + 1u : 0u;
         for (int ai = 0; ai < aend - abeg; ++ai) {
             const int buf = ai & (P.nbuf - 1);
+            // issued before the wait: the ticket that decides who finishes the block, and the rows' scales
+            int ticket = 0;
+            if (P.nslabs > 1 && lane == 0) ticket = atomicAdd(reinterpret_cast<int*>(ws + P.ws_counters_off) + abeg + ai, 1);
+            const RowScales rs = load_row_scales(P, abeg + ai, lane, scale);
             if (!ptx::mbar_wait_bounded(blk_full_bar + 8 * buf, static_cast<uint32_t>(ai >> P.nbuf_shift) & 1u, kWaitPolls)) {
                 ok = false;
                 break;
@@ -306,18 +379,36 @@ fp6_gemv_kernel(const __half* __restrict__ x, long long ldx, const uint8_t* __re
 #pragma unroll
                     for (int i = 0; i < 4; ++i) sum[fr][nb][i] = 0.f;
             const float4* src = parts_ro + (size_t)(buf * nslots) * (4 * NB * 32) + lane;
-            for (int w = 0; w < nslots; ++w) {
+            // nslots is a multiple of 8; the loads of two slots are issued before either is used
+            for (int w = 0; w < nslots; w += 2) {
+                float4 q[2][4][NB];
 #pragma unroll
-                for (int fr = 0; fr < 4; ++fr)
+                for (int h = 0; h < 2; ++h)
 #pragma unroll
-                    for (int nb = 0; nb < NB; ++nb) {
-                        const float4 q = src[(size_t)(w * 4 * NB + fr * NB + nb) * 32];
-                        sum[fr][nb][0] += q.x; sum[fr][nb][1] += q.y; sum[fr][nb][2] += q.z; sum[fr][nb][3] += q.w;
-                    }
+                    for (int fr = 0; fr < 4; ++fr)
+#pragma unroll
+                        for (int nb = 0; nb < NB; ++nb) q[h][fr][nb] = src[(size_t)((w + h) * 4 * NB + fr * NB + nb) * 32];
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+#pragma unroll
+                    for (int fr = 0; fr < 4; ++fr)
+#pragma unroll
+                        for (int nb = 0; nb < NB; ++nb) {
+                            sum[fr][nb][0] += q[h][fr][nb].x; sum[fr][nb][1] += q[h][fr][nb].y;
+                            sum[fr][nb][2] += q[h][fr][nb].z; sum[fr][nb][3] += q[h][fr][nb].w;
+                        }
             }
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(blk_free_bar + 8 * buf);
-            finish_block<NB>(P, sum, abeg + ai, slab, lane, scale, y, ws);
+            if (!finish_block<NB>(P, sum, abeg + ai, slab, lane, rs, y, ws, call, __shfl_sync(0xffffffffu, ticket, 0))) ok = false;
+        }
+        if (P.nslabs > 1 && lane == 0) {
+            // the last CTA of the launch to finish advances the launch number
+            const unsigned done = atomicAdd(call_state, 1u);
+            if (done + 1 == gridDim.x * gridDim.y) {
+                call_state[0] = 0u;
+                call_state[1] = call;
+            }
         }
         if (!ok && lane == 0) atomicExch(status, AO_ERR_TIMEOUT);
         return;
@@ -328,20 +419,50 @@ fp6_gemv_kernel(const __half* __restrict__ x, long long ldx, const uint8_t* __re
     // x slab -> MMA B-fragment order: per k16 tile and lane (batch column m = lane/4, c = lane%4) the words
     // x[m][k0+2c .. +1] and x[m][k0+2c+8 .. +9]
     {
-        const int items = tiles * NB * MRL;
+        // One item = 8 consecutive k of one batch row (a 16-byte vector load: every CTA reads all of x, so the number
+        // of L2 requests is what this prologue costs); its four pairs go to lanes c = 0..3 of the row's column.
+        // The loads of four rounds of items are issued before any is used.
+        const int octs = P.KS / 8;
+        const int items = octs * (NB * MR);         // rows at and beyond M are zeros
         for (int i = tid; i < 4 * XT / 4; i += nconsumers) reinterpret_cast<uint32_t*>(smem + P.zero_off)[i] = 0u;
-        for (int it = tid; it < items; it += nconsumers) {
-            const int l = it % MRL, blk = it / MRL;
-            const int nb = blk % NB, tile = blk / NB;
-            const int m = nb * 8 + (l >> 2), c = l & 3;
-            uint2 wv = make_uint2(0u, 0u);
-            if (m < P.M) {
-                const int k = slab * P.KS + tile * 16 + 2 * c;
-                const uint32_t* row = reinterpret_cast<const uint32_t*>(x + (long long)m * ldx);
-                wv.x = __ldg(row + (k >> 1));
-                wv.y = __ldg(row + ((k + 8) >> 1));
+        const uint64_t keep = ptx::l2_policy_evict_last();   // x stays in L2 while the weights stream through
+        const bool vec_ok = ((reinterpret_cast<uintptr_t>(x) & 15) == 0) && ((ldx & 7) == 0);
+        constexpr int kRounds = 4;
+        for (int it0 = tid; it0 < items; it0 += kRounds * nconsumers) {
+            uint4 w[kRounds];
+#pragma unroll
+            for (int u = 0; u < kRounds; ++u) {
+                const int it = it0 + u * nconsumers;
+                w[u] = make_uint4(0u, 0u, 0u, 0u);
+                if (it < items) {
+                    const int rr = it / octs, j = it - rr * octs;
+                    const int m = (rr / MR) * 8 + (rr % MR);
+                    if (m < P.M) {
+                        const int k = slab * P.KS + 8 * j;
+                        const __half* row = x + (long long)m * ldx;
+                        if (vec_ok) {
+                            w[u] = ptx::ldg_u32x4_hint(row + k, keep);
+                        } else {
+                            const uint32_t* row32 = reinterpret_cast<const uint32_t*>(row) + (k >> 1);
+                            w[u].x = ptx::ldg_u32_hint(row32, keep);
+                            w[u].y = ptx::ldg_u32_hint(row32 + 1, keep);
+                            w[u].z = ptx::ldg_u32_hint(row32 + 2, keep);
+                            w[u].w = ptx::ldg_u32_hint(row32 + 3, keep);
+                        }
+                    }
+                }
             }
-            *reinterpret_cast<uint2*>(smem + P.xs_off + (size_t)it * 8) = wv;
+#pragma unroll
+            for (int u = 0; u < kRounds; ++u) {
+                const int it = it0 + u * nconsumers;
+                if (it < items) {
+                    const int rr = it / octs, j = it - rr * octs;
+                    const int nb = rr / MR, mm = rr % MR;
+                    // pair c of octet j is word (j & 1) of lane (mm, c) at k16 tile j / 2
+                    uint32_t* dst = reinterpret_cast<uint32_t*>(smem + P.xs_off) + (((j >> 1) * NB + nb) * MRL + mm * 4) * 2 + (j & 1);
+                    dst[0] = w[u].x; dst[2] = w[u].y; dst[4] = w[u].z; dst[6] = w[u].w;
+                }
+            }
         }
         ptx::named_barrier_sync(1, nconsumers);
     }
