@@ -240,24 +240,28 @@ __device__ __noinline__ bool finish_block(const Plan& P, const float (&v)[4][NB]
 #pragma unroll
         for (int nb = 0; nb < NB; ++nb) {
             uint2 q[4][4];
-            // the sixteen loads of a batch block are issued before any is looked at: one round trip, not sixteen
+            // the sixteen loads of a batch block are issued before any is looked at, and all of them again while any
+            // word of the warp still lacks the tag: a retry costs one round trip, not one per word
+            for (;;) {
+                bool all = true;
 #pragma unroll
-            for (int fr = 0; fr < 4; ++fr)
+                for (int fr = 0; fr < 4; ++fr)
 #pragma unroll
-                for (int i = 0; i < 4; ++i) q[fr][i] = ld_volatile_u2(src + ((fr * NB + nb) * 4 + i) * 32);
+                    for (int i = 0; i < 4; ++i) q[fr][i] = ld_volatile_u2(src + ((fr * NB + nb) * 4 + i) * 32);
 #pragma unroll
-            for (int fr = 0; fr < 4; ++fr)
+                for (int fr = 0; fr < 4; ++fr)
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    while (q[fr][i].y != call) {
-                        if (ptx::globaltimer_ns() - t0 > 200000000ull) {   // 0.2 s
-                            ok = false;
-                            break;
-                        }
-                        q[fr][i] = ld_volatile_u2(src + ((fr * NB + nb) * 4 + i) * 32);
-                    }
-                    sum[fr][nb][i] += __uint_as_float(q[fr][i].x);
+                    for (int i = 0; i < 4; ++i) all = all && (q[fr][i].y == call);
+                if (__all_sync(0xffffffffu, all)) break;
+                if (ptx::globaltimer_ns() - t0 > 200000000ull) {   // 0.2 s
+                    ok = false;
+                    break;
                 }
+            }
+#pragma unroll
+            for (int fr = 0; fr < 4; ++fr)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) sum[fr][nb][i] += __uint_as_float(q[fr][i].x);
         }
     }
     store_block<NB>(P, sum, a, lane, rs, y);
