@@ -103,7 +103,7 @@ int make_plan(int64_t M, int64_t N, int64_t K, int g, int ikt, Plan* P) {
     P->magic = 0x43004300u;
     P->ws_counters_off = kHeaderBytes;
     P->ws_slots_off = kHeaderBytes + (size_t)kMaxPairs * 4;
-    P->ws_bytes = P->ws_slots_off + (nslabs > 1 ? (size_t)nslabs * P->NP * P->NB * 512 : 0);
+    P->ws_bytes = P->ws_slots_off + (nslabs > 1 ? (size_t)nslabs * P->NP * P->NB * 1024 : 0);   // {value, tag} words
     return AO_OK;
 }
 

@@ -20,9 +20,9 @@
 //  * At the end of a row pair every consumer warp leaves its partial sums in a ring of shared-memory
 //    buffers; a reducer warp adds them in slot order (deterministic) and stores bf16.  Only when the
 //    activations of the whole K range do not fit in shared memory (large M * K) is K cut into slabs
-//    handled by different CTAs; their partial sums meet in fixed slots of the workspace and the CTA
-//    that completes the pair (atomic counter) adds the slots in slab order and leaves the counter at
-//    zero for the next call.
+//    handled by different CTAs; the CTA that draws the last ticket of a pair (atomic counter, left at
+//    zero for the next call) collects the others' partial sums from fixed slots of the workspace and
+//    adds them in slab order (finish_pair below).
 //  * Programmatic dependent launch: the kernel lets its successor start early and itself touches
 //    nothing but weights before griddepcontrol.wait, so back-to-back linears overlap drain and fill.
 //  * Row-sharded multi-GPU use (nranks > 1): the reducer warp stages the CTA's rows and exchanges them
@@ -97,61 +97,10 @@ __device__ __forceinline__ void store_rows(const Plan& P, const float (&v)[NB][4
     }
 }
 
-// One warp finishes row pair p for its CTA (which has seen the pair's whole K range inside its slab):
-// a direct bf16 store, or with K slabs a partial slot plus the completion protocol.
-template <int NB>
-__device__ __noinline__ void finish_pair(const Plan& P, const float (&v)[NB][4], int p, int slab, int lane,
-                                         __nv_bfloat16* __restrict__ y, uint8_t* __restrict__ ws) {
-    if (P.nslabs == 1) {
-        store_rows<NB>(P, v, p, lane, y);
-        return;
-    }
-    float4* slots = reinterpret_cast<float4*>(ws + P.ws_slots_off);
-    const size_t slot_stride = (size_t)NB * 32;  // float4 per slot
-    {
-        float4* mine = slots + ((size_t)slab * P.NP + p) * slot_stride;
-#pragma unroll
-        for (int nb = 0; nb < NB; ++nb) mine[nb * 32 + lane] = make_float4(v[nb][0], v[nb][1], v[nb][2], v[nb][3]);
-    }
-    __threadfence();
-    __syncwarp();
-    int* counter = reinterpret_cast<int*>(ws + P.ws_counters_off) + p;
-    int old = 0;
-    if (lane == 0) old = atomicAdd(counter, 1);
-    old = __shfl_sync(0xffffffffu, old, 0);
-    if (old + 1 != P.nslabs) return;
-    // this CTA completed the pair: add the slabs' partial sums in slab order
-    __threadfence();
-    float sum[NB][4];
-#pragma unroll
-    for (int nb = 0; nb < NB; ++nb)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) sum[nb][i] = 0.f;
-    for (int sl0 = 0; sl0 < P.nslabs; sl0 += 4) {
-        float4 v4[4][NB];
-        // issue the loads of up to four slots before using any of them
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            const bool live = sl0 + q < P.nslabs;
-#pragma unroll
-            for (int nb = 0; nb < NB; ++nb)
-                v4[q][nb] = live ? ptx::ldcg_f32x4(slots + ((size_t)(sl0 + q) * P.NP + p) * slot_stride + nb * 32 + lane)
-                                 : make_float4(0.f, 0.f, 0.f, 0.f);
-        }
-#pragma unroll
-        for (int q = 0; q < 4; ++q)
-#pragma unroll
-            for (int nb = 0; nb < NB; ++nb) {
-                sum[nb][0] += v4[q][nb].x; sum[nb][1] += v4[q][nb].y;
-                sum[nb][2] += v4[q][nb].z; sum[nb][3] += v4[q][nb].w;
-            }
-    }
-    store_rows<NB>(P, sum, p, lane, y);
-    if (lane == 0) *counter = 0;  // ready for the next call
-}
+// Header words of the workspace used by the K-slab hand-off: {CTAs of this launch that have finished, number of
+// slab launches completed so far}.  The second is the tag the partial sums of the next launch carry.
+constexpr int kCallStateOff = 16;
 
-
-// ---- output exchange over peer memory -------------------------------------------------------------------------
 __device__ __forceinline__ uint2 ld_volatile_u2(const uint2* p) {
     uint2 v;
     asm volatile("ld.volatile.global.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
@@ -160,6 +109,89 @@ __device__ __forceinline__ uint2 ld_volatile_u2(const uint2* p) {
 __device__ __forceinline__ void st_volatile_u2(uint2* p, uint32_t a, uint32_t b) {
     asm volatile("st.volatile.global.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(a), "r"(b) : "memory");
 }
+
+// One warp finishes row pair p for its CTA (which has seen the pair's whole K range inside its slab): a direct bf16
+// store, or with K slabs the hand-off.  The CTAs that share a pair draw a ticket from the pair's counter when they
+// start on it (the round trip is over by the time their sums are ready); the one that drew the last ticket adds the
+// slabs up in slab order and stores y, the others leave their partial sums in their workspace slot as 8-byte
+// {value, tag} words (tag = number of this launch; an 8-byte store is written as a unit, so a word that carries the
+// tag carries the value: no fence is needed) and move on.  The finisher polls those words (bounded); it only ever
+// waits for CTAs that hold a ticket, i.e. are running and have no reason to wait for it, and every CTA walks its
+// pairs in the same order.
+template <int NB>
+__device__ __noinline__ bool finish_pair(const Plan& P, const float (&v)[NB][4], int p, int slab, int lane,
+                                         __nv_bfloat16* __restrict__ y, uint8_t* __restrict__ ws, unsigned call, int ticket) {
+    if (P.nslabs == 1) {
+        store_rows<NB>(P, v, p, lane, y);
+        return true;
+    }
+    uint2* slots = reinterpret_cast<uint2*>(ws + P.ws_slots_off);
+    const size_t slot_stride = (size_t)NB * 4 * 32;  // words per slot: [batch block][value][lane]
+    if (ticket + 1 != P.nslabs) {
+        uint2* mine = slots + ((size_t)slab * P.NP + p) * slot_stride + lane;
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) st_volatile_u2(mine + (nb * 4 + i) * 32, __float_as_uint(v[nb][i]), call);
+        return true;
+    }
+    if (lane == 0) *(reinterpret_cast<int*>(ws + P.ws_counters_off) + p) = 0;   // ready for the next call
+    float sum[NB][4];
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) sum[nb][i] = 0.f;
+    bool ok = true;
+    const uint64_t t0 = ptx::globaltimer_ns();
+    for (int sl0 = 0; sl0 < P.nslabs; sl0 += 4) {
+        // the loads of up to four slabs are issued before any is looked at, and all of them again while any word of
+        // the warp still lacks the tag: a retry costs one round trip, not one per word
+        uint2 q[4][NB][4];
+        for (;;) {
+            bool all = true;
+#pragma unroll
+            for (int h = 0; h < 4; ++h) {
+                const int sl = sl0 + h;
+                if (sl >= P.nslabs || sl == slab) continue;
+                const uint2* src = slots + ((size_t)sl * P.NP + p) * slot_stride + lane;
+#pragma unroll
+                for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        q[h][nb][i] = ld_volatile_u2(src + (nb * 4 + i) * 32);
+                    }
+            }
+#pragma unroll
+            for (int h = 0; h < 4; ++h) {
+                const int sl = sl0 + h;
+                if (sl >= P.nslabs || sl == slab) continue;
+#pragma unroll
+                for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) all = all && (q[h][nb][i].y == call);
+            }
+            if (__all_sync(0xffffffffu, all)) break;
+            if (ptx::globaltimer_ns() - t0 > 200000000ull) {   // 0.2 s
+                ok = false;
+                break;
+            }
+        }
+#pragma unroll
+        for (int h = 0; h < 4; ++h) {
+            const int sl = sl0 + h;
+            if (sl >= P.nslabs) continue;
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) sum[nb][i] += (sl == slab) ? v[nb][i] : __uint_as_float(q[h][nb][i].x);
+        }
+    }
+    store_rows<NB>(P, sum, p, lane, y);
+    return ok;
+}
+
+
+// ---- output exchange over peer memory -------------------------------------------------------------------------
 
 // The reducer warp keeps the CTA's finished rows in shared memory ([M][rows_cta_max] bf16) instead of storing them.
 template <int NB>
@@ -470,8 +502,14 @@ int4_gemv_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int Kx, con
         // number of this call of the exchange (all CTAs of a launch read the same value: it changes when the last
         // CTA of the launch finishes)
         const unsigned call = P.nranks > 1 ? *reinterpret_cast<volatile unsigned*>(P.local_state + 1) + 1u : 0u;
+        // tag of this launch's slab partial sums (all CTAs read the same value: it changes when the last one finishes)
+        unsigned* call_state = reinterpret_cast<unsigned*>(ws + kCallStateOff);
+        const unsigned slab_call = P.nslabs > 1 ? *reinterpret_cast<volatile unsigned*>(call_state + 1) + 1u : 0u;
         for (int pi = 0; pi < pend - pbeg; ++pi) {
             const int buf = pi & nbuf_mask;
+            // issued before the wait: the ticket that decides who finishes the pair
+            int ticket = 0;
+            if (P.nslabs > 1 && lane == 0) ticket = atomicAdd(reinterpret_cast<int*>(ws + P.ws_counters_off) + pbeg + pi, 1);
             if (!ptx::mbar_wait_bounded(pair_full_bar + 8 * buf, static_cast<uint32_t>(pi >> nbuf_shift) & 1u, kWaitPolls)) {
                 ok = false;
                 break;
@@ -501,8 +539,16 @@ int4_gemv_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int Kx, con
             if (lane == 0) ptx::mbar_arrive(pair_free_bar + 8 * buf);
             if (P.nranks > 1)
                 stage_rows<NB>(P, reinterpret_cast<__nv_bfloat16*>(smem + P.ystage_off), sum, pi, lane);
-            else
-                finish_pair<NB>(P, sum, pbeg + pi, slab, lane, y, ws);
+            else if (!finish_pair<NB>(P, sum, pbeg + pi, slab, lane, y, ws, slab_call, __shfl_sync(0xffffffffu, ticket, 0)))
+                ok = false;
+        }
+        if (P.nslabs > 1 && lane == 0) {
+            // the last CTA of the launch to finish advances the launch number
+            const unsigned done = atomicAdd(call_state, 1u);
+            if (done + 1 == gridDim.x * gridDim.y) {
+                call_state[0] = 0u;
+                call_state[1] = slab_call;
+            }
         }
         if (P.nranks > 1) {
             // even after a failed wait the exchange runs, so that the other ranks are not left waiting for this one

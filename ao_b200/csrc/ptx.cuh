@@ -283,11 +283,6 @@ __device__ __forceinline__ float ldcg_f32(const float* p) {
     asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(v) : "l"(p));
     return v;
 }
-__device__ __forceinline__ float4 ldcg_f32x4(const float4* p) {
-    float4 v;
-    asm volatile("ld.global.cg.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
-    return v;
-}
 
 }  // namespace ptx
 }  // namespace ao
