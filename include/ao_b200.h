@@ -167,9 +167,11 @@ int ao_from_scaled_tc_fp6(const uint8_t* packed, int64_t M, int64_t N, const voi
  *
  * Workspace: ao_int4_tinygemm_linear_workspace_bytes(...) bytes, 256-byte aligned.  It holds a
  * status word (int at offset 0: AO_OK, or the code of a device-side failure such as a copy
- * that never completed), split-K completion counters and partial-sum slots.  It must be
- * zero-filled once before its first use; every call that completes leaves it ready for the
- * next one.  Calls that may overlap on the GPU need workspaces of their own. */
+ * that never completed), the number of K-slab launches so far (bytes 16..23; it tags the partial
+ * sums that CTAs hand to one another), split-K completion counters and partial-sum slots.  It must
+ * be zero-filled once before its first use; every call that completes leaves it ready for the
+ * next one; after a non-zero status word it must be zero-filled again.  Calls that may overlap on
+ * the GPU need workspaces of their own. */
 size_t ao_int4_tinygemm_linear_workspace_bytes(int64_t M, int64_t N, int64_t K, int group,
                                                int inner_k_tiles);
 int ao_int4_tinygemm_linear(const void* x_bf16, int64_t x_row_stride, int64_t x_cols,

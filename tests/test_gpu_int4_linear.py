@@ -151,3 +151,36 @@ def test_bad_arguments_raise():
         ops.weight_int4pack_mm(x, packed, 64, sz[:8])
     with pytest.raises(RuntimeError, match="no CPU fallback"):
         ops.weight_int4pack_mm(x.cpu(), packed, 64, sz)
+
+
+def test_k_slab_kernels_share_one_workspace_over_many_launches():
+    """The decode kernels with K slabs (int4 at M = 8 on K = 14336, fp6 on a small N) and the split-K tcgen05 kernel
+    use the same workspace one after the other; the launch number that tags the slab partial sums advances with
+    every launch.  Results must keep the bits of the first launch and the status word must stay clean."""
+    from ao_b200 import _cabi, ops
+    from ao_b200.prototype.quant_llm.quant_llm import to_scaled_tc_fpx
+    g = torch.Generator(device="cuda").manual_seed(11)
+    w = (torch.randn(1024, 14336, generator=g, device="cuda") * 0.02).bfloat16()
+    packed, sz = ops.int4_quantize_pack(w, 64, 8)
+    x8 = torch.randn(8, 14336, generator=g, device="cuda").bfloat16()
+    x64 = torch.randn(64, 14336, generator=g, device="cuda").bfloat16()
+    assert _cabi.lib().ao_int4_gemv_workspace_bytes(8, 1024, 14336, 64, 8) > 256 + 4 * 16384, "expected a K-slab plan"
+    w6 = (torch.randn(1024, 4096, generator=g, device="cuda") * 0.02).half()
+    p6, s6 = to_scaled_tc_fpx(w6, 3, 2)
+    x6 = torch.randn(1, 4096, generator=g, device="cuda").half()
+    first = None
+    for it in range(40):
+        ys = (ops.weight_int4pack_mm(x8, packed, 64, sz), ops.quant_llm_linear(3, 2, x6, p6, s6, 1),
+              ops.weight_int4pack_mm(x64, packed, 64, sz), ops.weight_int4pack_mm(x8[:4].contiguous(), packed, 64, sz))
+        if first is None:
+            first = [y.clone() for y in ys]
+            wd = ops.int4_groupwise_quantize(w, 64, torch.int32)
+            from ao_b200.quantization import quant_primitives as qp
+            wdq = qp.dequantize_affine(wd[2], (1, 64), wd[0], wd[1], torch.int32, 0, 15, qp.ZeroPointDomain.FLOAT,
+                                       output_dtype=torch.float32)
+            ref = x8.float() @ wdq.T
+            assert float((ys[0].float() - ref).abs().max() / ref.abs().max()) <= TOL
+        else:
+            for y, f in zip(ys, first):
+                assert torch.equal(y, f), f"launch {it}"
+    assert _cabi.workspace_status("cuda") == 0
