@@ -65,11 +65,11 @@ static int make_plan(int64_t M, int64_t N, int64_t K, int fmt_id, Plan* P) {
     P->NB = M > 8 ? 2 : 1;
     P->MR = M > 4 ? 8 : (M > 2 ? 4 : (M > 1 ? 2 : 1));
     P->NA = (int)(N / 64);
-    // K slabs: the x fragments of a slab (KS * MR * NB * 2 bytes) must fit next to a ring of two stages, and
-    // row blocks x slabs should fill the SMs evenly
+    // K slabs: the x fragments of a slab (KS * MR * NB * 2 bytes) must fit next to a ring of two stages; among
+    // those the split with the shortest estimated time of the busiest CTA
     const int ngroups = kConsumerWarps / kGroupWarps;
     int best = 0;
-    double best_eff = -1.0;
+    double best_cost = 0.0;
     for (int ns = 1; ns <= 32; ++ns) {
         if (K % (64 * ns) != 0) continue;
         const int ks = (int)(K / ns);
@@ -82,10 +82,13 @@ static int make_plan(int64_t M, int64_t N, int64_t K, int fmt_id, Plan* P) {
         if (g < 1) continue;
         if (g > P->NA) g = P->NA;
         const int per = (P->NA + g - 1) / g;
-        double eff = (double)P->NA / ((double)per * g) * ((double)g * ns / kNumSMs);
-        eff -= 0.02 * (ns - 1);  // every extra slab costs a trip through the workspace
-        if (eff > best_eff) {
-            best_eff = eff;
+        // time of the busiest CTA in units of one full stage: its (block, slab) units, each the unit's stages plus
+        // about one and a half stages of fixed cost (pipeline hand-over, partial sums, hand-off), plus the
+        // finisher's collection of the other slabs.  Measured on 4096 x 4096 / 11008 x 4096 (1, 2, 4, 8 slabs):
+        // 9.7 / 16.9, 8.2 / 15.1, 10.7 / 21.9, 22.3 / 51.1 us.
+        const double cost = per * (tl / (double)kMaxTiles + 1.5) + 0.5 * (ns - 1);
+        if (best == 0 || cost < best_cost) {
+            best_cost = cost;
             best = ns;
         }
     }
