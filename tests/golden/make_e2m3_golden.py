@@ -1,7 +1,7 @@
 """Golden vectors for the second 6-bit format the reference's linear dispatches, fp6 e2m3
 (torchao/csrc/cuda/fp6_llm/fp6_linear.cu:181-182): to_scaled_tc_fpx / from_scaled_tc_fpx of the reference
 (torchao/prototype/quant_llm/quant_llm.py:116-130, 203-208) and the fp32 dequant-matmul.
-Run once:  python make_e2m3_golden.py [/path/to/reference]
+Run once:  python make_e2m3_golden.py /path/to/reference
 """
 import os
 import sys
@@ -15,7 +15,9 @@ from make_golden import load_reference, make_weight, store  # noqa: E402
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: python " + sys.argv[0] + " <path of a torchao 0.3.1 source tree>")
+    ref = sys.argv[1]
     ql = load_reference(ref)["quant_llm"]
     arrays = {}
     for name, shape, dt, seed in [("scaled_e2m3_f16", (128, 192), torch.float16, 62), ("scaled_e2m3_f32", (64, 128), torch.float32, 63)]:

@@ -1,6 +1,6 @@
 """Golden vectors for the 5-bit formats of the reference's linear (e2m2, e3m1): generic pre-packing
 _pack_tc_fpx / _unpack_tc_fpx on random codes, to_scaled_tc_fpx / from_scaled_tc_fpx, and the fp32 dequant-matmul
-(torchao/prototype/quant_llm/quant_llm.py:60-86, 116-130, 134-208).  Run once:  python make_fp5_golden.py [reference]"""
+(torchao/prototype/quant_llm/quant_llm.py:60-86, 116-130, 134-208).  Run once:  python make_fp5_golden.py /path/to/reference"""
 import os
 import sys
 
@@ -13,7 +13,9 @@ from make_golden import load_reference, make_weight, store  # noqa: E402
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: python " + sys.argv[0] + " <path of a torchao 0.3.1 source tree>")
+    ref = sys.argv[1]
     ql = load_reference(ref)["quant_llm"]
     arrays = {}
     g = torch.Generator().manual_seed(5)

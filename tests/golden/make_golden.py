@@ -285,7 +285,9 @@ def linear(mods, arrays, manifest):
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: python " + sys.argv[0] + " <path of a torchao 0.3.1 source tree>")
+    ref = sys.argv[1]
     mods = load_reference(ref)
     manifest = {"reference": "torchao 0.3.1", "torch": torch.__version__, "primitives": [], "fp6": [],
                 "linear": [], "fp6_linear": []}
