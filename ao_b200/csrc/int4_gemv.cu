@@ -6,6 +6,16 @@
 namespace ao {
 namespace gemv {
 
+#ifdef AO_B200_DEV_KNOBS
+// Tuning sweeps only (a build with -DAO_B200_DEV_KNOBS): an integer from the environment, clamped to [lo, hi].
+static int dev_knob(const char* name, int dflt, int lo, int hi) {
+    const char* e = getenv(name);
+    if (!e) return dflt;
+    const int v = atoi(e);
+    return v < lo ? lo : (v > hi ? hi : v);
+}
+#endif
+
 int make_plan(int64_t M, int64_t N, int64_t K, int g, int ikt, Plan* P) {
     if (M < 1 || M > 16) return AO_ERR_SHAPE;
     if (!(ikt == 2 || ikt == 4 || ikt == 8)) return AO_ERR_ARG;
@@ -38,7 +48,9 @@ int make_plan(int64_t M, int64_t N, int64_t K, int g, int ikt, Plan* P) {
     // a stage holds one row pair x up to kMaxSubs sub-units of K
     P->subs = P->KS / P->UK;
     P->SUBS = P->subs < kMaxSubs ? P->subs : kMaxSubs;
-    { const char* e = getenv("AO_GEMV_SUBS"); if (e && atoi(e) < P->SUBS) P->SUBS = atoi(e); }
+#ifdef AO_B200_DEV_KNOBS
+    P->SUBS = dev_knob("AO_GEMV_SUBS", P->SUBS, 1, P->SUBS);
+#endif
     P->cpp = (P->subs + P->SUBS - 1) / P->SUBS;
     if ((long long)P->NP * P->cpp > (1LL << 30)) return AO_ERR_SHAPE;
     const int stage_raw = 2 * P->SUBS * P->UB + P->SUBS * P->GPU * 64;
@@ -48,8 +60,10 @@ int make_plan(int64_t M, int64_t N, int64_t K, int g, int ikt, Plan* P) {
     const int xs_bytes = 2 * P->KS * P->MR * P->NB, zero_bytes = (P->UK / 32) * P->NB * P->MR * 64;
     const int sx_bytes = (P->KS / g) * P->NB * 32;
     int nwarps = kMaxConsumerWarps, stages = kMaxStages;
-    { const char* e = getenv("AO_GEMV_NWARPS"); if (e) nwarps = atoi(e); }
-    { const char* e = getenv("AO_GEMV_STAGES"); if (e) stages = atoi(e); }
+#ifdef AO_B200_DEV_KNOBS
+    nwarps = dev_knob("AO_GEMV_NWARPS", nwarps, 8, kMaxConsumerWarps) / 8 * 8;
+    stages = dev_knob("AO_GEMV_STAGES", stages, 2, kMaxStages) >= 4 ? 4 : 2;
+#endif
     for (;;) {
         const int total = xs_bytes + zero_bytes + sx_bytes + 2 * nwarps * P->NB * 512 + 512 +
                           stages * P->stage_bytes;
@@ -68,7 +82,6 @@ int make_plan(int64_t M, int64_t N, int64_t K, int g, int ikt, Plan* P) {
     P->sx_off = off;
     off += sx_bytes;
     int G = kNumSMs / nslabs;
-    { const char* e = getenv("AO_GEMV_GRIDMUL"); if (e) G *= atoi(e); }
     if (G < 1) G = 1;
     if (G > P->NP) G = P->NP;
     P->G = G;

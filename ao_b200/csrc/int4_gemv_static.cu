@@ -13,8 +13,13 @@
 //     (ao_int4_gemv_static_scratch_max_bytes() reports the limit, ao_int4_gemv_workspace_bytes() the need);
 //   * every call on a device uses the same array, which still holds what the previous call left there.  The
 //     part that has to start at zero (status word and completion counters) is cleared on the stream at the
-//     start of each call; two calls that overlap on the GPU (different streams) race on the array and must
-//     be serialised by the caller, or use ao_int4_gemv with workspaces of their own.
+//     start of each call.  The launch counter next to the status word is deliberately NOT cleared: the K-slab
+//     hand-off tags its partial sums with the launch number, so the number must keep growing from call to call or
+//     a finisher could mistake the previous call's partial sums (still in the array) for this call's.  Two calls
+//     that overlap on the GPU (different streams) race on the array and must be serialised by the caller, or use
+//     ao_int4_gemv with workspaces of their own;
+//   * the array that is used belongs to the device that is current when the entry point is called; the stream
+//     must be a stream of that device.
 #include <mutex>
 
 #include "int4_gemv.cuh"
@@ -40,7 +45,8 @@ static void* g_scratch_ptr[kMaxDevices] = {};
 // Device address of the scratch array on the current device; looked up once per device.
 static int scratch_for_current_device(void** out) {
     int dev = -1;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return AO_ERR_LAUNCH;
+    if (cudaGetDevice(&dev) != cudaSuccess) return AO_ERR_LAUNCH;
+    if (dev < 0 || dev >= kMaxDevices) return AO_ERR_UNSUPPORTED;   // more devices than the address table holds
     std::lock_guard<std::mutex> lock(g_setup_mutex);
     if (g_scratch_ptr[dev] == nullptr) {
         void* ptr = nullptr;
@@ -76,9 +82,14 @@ extern "C" int ao_int4_gemv_static_scratch(const void* x_bf16, int64_t x_row_str
     rc = gemv::scratch_for_current_device(&scratch);
     if (rc) return rc;
     cudaStream_t st = as_stream(stream);
-    // what must start at zero: the status word and the completion counters of this call's row pairs
-    const size_t clear_bytes = P.nslabs > 1 ? P.ws_counters_off + (size_t)P.NP * 4 : (size_t)gemv::kHeaderBytes;
-    if (cudaMemsetAsync(scratch, 0, clear_bytes, st) != cudaSuccess) {
+    // what must start at zero: the status word and, with K slabs, the completion counters of this call's row
+    // pairs.  Bytes [kCallStateOff, kCallStateOff + 8) -- the finished-CTA counter, which every launch leaves at
+    // zero itself, and the launch number that tags the slab partial sums -- persist from call to call.
+    static_assert(gemv::kCallStateOff >= 4, "the status word is cleared on its own");
+    unsigned char* base = static_cast<unsigned char*>(scratch);
+    bool ok = cudaMemsetAsync(base, 0, 4, st) == cudaSuccess;
+    if (ok && P.nslabs > 1) ok = cudaMemsetAsync(base + P.ws_counters_off, 0, (size_t)P.NP * 4, st) == cudaSuccess;
+    if (!ok) {
         (void)cudaGetLastError();
         return AO_ERR_LAUNCH;
     }

@@ -220,7 +220,9 @@ int ao_comm_close(void* base);
  *    during start-up, before any stream capture.
  *  - A shape whose ao_int4_gemv_workspace_bytes() exceeds the maximum returns AO_ERR_WORKSPACE.
  *  - All calls on a device share the array; the call clears the part that has to start at zero on
- *    `stream` itself, but calls that overlap on the GPU race on it: serialise them, or use ao_int4_gemv. */
+ *    `stream` itself (and keeps the launch counter that tags split-K partial sums growing across calls), but
+ *    calls that overlap on the GPU race on it: serialise them, or use ao_int4_gemv.
+ *  - The array of the device that is current at the call is used: `stream` must belong to that device. */
 size_t ao_int4_gemv_static_scratch_max_bytes(void);
 int ao_int4_gemv_static_scratch(const void* x_bf16, int64_t x_row_stride, int64_t x_cols,
                                 const int32_t* packed, const void* scale_and_zero, int64_t M, int64_t N,
