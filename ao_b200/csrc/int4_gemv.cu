@@ -40,8 +40,8 @@ int make_plan(int64_t M, int64_t N, int64_t K, int g, int ikt, Plan* P) {
         const int subs_ = ks / P->UK, SUBS_ = subs_ < kMaxSubs ? subs_ : kMaxSubs;
         const int stage_ = ((2 * SUBS_ * P->UB + SUBS_ * P->GPU * 64 + 127) / 128) * 128;
         const long long need = 2LL * ks * P->MR * P->NB + (P->UK / 32) * P->NB * P->MR * 64 + (ks / g) * P->NB * 32 +
-                               2 * 8 * P->NB * 512 + 512 + 2 * stage_;
-        if (need <= 220 * 1024) break;
+                               2 * 8 * P->NB * 512 + 1024 + 2 * stage_;
+        if (need <= kSmemBudget) break;
     }
     P->nslabs = nslabs;
     P->KS = (int)(K / nslabs);
@@ -65,9 +65,9 @@ int make_plan(int64_t M, int64_t N, int64_t K, int g, int ikt, Plan* P) {
     stages = dev_knob("AO_GEMV_STAGES", stages, 2, kMaxStages) >= 4 ? 4 : 2;
 #endif
     for (;;) {
-        const int total = xs_bytes + zero_bytes + sx_bytes + 2 * nwarps * P->NB * 512 + 512 +
+        const int total = xs_bytes + zero_bytes + sx_bytes + 2 * nwarps * P->NB * 512 + 1024 +
                           stages * P->stage_bytes;
-        if (total <= 220 * 1024) break;
+        if (total <= kSmemBudget) break;
         if (stages > 2) stages = 2;   // the ring depth stays a power of two
         else if (nwarps > 8) nwarps -= 8;
         else return AO_ERR_UNSUPPORTED;
@@ -78,6 +78,7 @@ int make_plan(int64_t M, int64_t N, int64_t K, int g, int ikt, Plan* P) {
     P->xs_off = off;
     off += xs_bytes;
     P->zero_off = off;
+    P->trace_id = 0;
     off += zero_bytes;
     P->sx_off = off;
     off += sx_bytes;
@@ -85,10 +86,12 @@ int make_plan(int64_t M, int64_t N, int64_t K, int g, int ikt, Plan* P) {
     if (G < 1) G = 1;
     if (G > P->NP) G = P->NP;
     P->G = G;
+    P->pair_q = P->NP / G;
+    P->pair_r = P->NP % G;
     // groups of 8 warps (four sub-units per warp and stage, unrolled) when the CTA has enough stages to keep
     // every group busy; otherwise all warps share each stage
     const int stages_per_cta = ((P->NP + G - 1) / G) * P->cpp;
-    P->GW = (stages_per_cta >= 2 * (nwarps / 8) && P->SUBS >= 32) ? 8 : nwarps;
+    P->GW = (stages_per_cta >= 2 * (nwarps / 8) && P->SUBS >= kMaxSubs) ? 8 : nwarps;
     // ring of pair buffers: within the budget of two buffers of all warps, at most kMaxPairBufs
     const int NG = nwarps / P->GW;
     const int nslots = (NG < P->cpp ? NG : P->cpp) * P->GW;
@@ -101,7 +104,7 @@ int make_plan(int64_t M, int64_t N, int64_t K, int g, int ikt, Plan* P) {
     P->part_off = off;
     off += nbuf * nslots * P->NB * 512;
     P->bar_off = off;
-    off += 2 * kMaxStages * 8 + 2 * kMaxPairBufs * 8;
+    off += 2 * kMaxStages * 8 + 2 * kMaxPairBufs * 8 + 2 * kMaxXChunks * 8;
     // staging of the CTA's output rows for the peer exchange (used only when nranks > 1; small)
     P->rows_cta_max = 16 * ((P->NP + G - 1) / G);
     P->ystage_off = (off + 15) / 16 * 16;
@@ -138,9 +141,9 @@ extern "C" size_t ao_int4_gemv_workspace_bytes(int64_t M, int64_t N, int64_t K, 
     return P.ws_bytes;
 }
 
-extern "C" int ao_int4_gemv(const void* x_bf16, int64_t x_row_stride, int64_t x_cols, const int32_t* packed,
-                            const void* scale_and_zero, int64_t M, int64_t N, int64_t K, int group, int inner_k_tiles,
-                            void* y_bf16, void* workspace, size_t workspace_bytes, ao_stream_t stream) {
+static int int4_gemv_impl(const void* x_bf16, int64_t x_row_stride, int64_t x_cols, const int32_t* packed,
+                         const void* scale_and_zero, int64_t M, int64_t N, int64_t K, int group, int inner_k_tiles,
+                         void* y_bf16, void* workspace, size_t workspace_bytes, ao_stream_t stream) {
     if (M == 0 || N == 0) return AO_OK;
     gemv::Plan P;
     int rc = gemv::make_plan(M, N, K, group, inner_k_tiles, &P);
@@ -150,6 +153,9 @@ extern "C" int ao_int4_gemv(const void* x_bf16, int64_t x_row_stride, int64_t x_
         !aligned(workspace, 256))
         return AO_ERR_ALIGN;
     if (workspace == nullptr || workspace_bytes < P.ws_bytes) return AO_ERR_WORKSPACE;
+#if defined(AO_GEMV_TRACE) && AO_GEMV_TRACE
+    P.trace_id = N == 6144 ? 0 : (N == 28672 ? 2 : (K == 14336 ? 3 : 1));   // the four layers of the decode set
+#endif
     cudaStream_t st = as_stream(stream);
     switch (inner_k_tiles) {
         case 8: return gemv::launch_ikt<8>(P, x_bf16, x_row_stride, (int)x_cols, packed, scale_and_zero, y_bf16, workspace, st);
@@ -157,6 +163,13 @@ extern "C" int ao_int4_gemv(const void* x_bf16, int64_t x_row_stride, int64_t x_
         case 2: return gemv::launch_ikt<2>(P, x_bf16, x_row_stride, (int)x_cols, packed, scale_and_zero, y_bf16, workspace, st);
     }
     return AO_ERR_ARG;
+}
+
+extern "C" int ao_int4_gemv(const void* x_bf16, int64_t x_row_stride, int64_t x_cols, const int32_t* packed,
+                            const void* scale_and_zero, int64_t M, int64_t N, int64_t K, int group, int inner_k_tiles,
+                            void* y_bf16, void* workspace, size_t workspace_bytes, ao_stream_t stream) {
+    return int4_gemv_impl(x_bf16, x_row_stride, x_cols, packed, scale_and_zero, M, N, K, group, inner_k_tiles, y_bf16,
+                          workspace, workspace_bytes, stream);
 }
 
 // The same kernel with the output exchange in its epilogue: every CTA sends its rows to the same CTA of every peer

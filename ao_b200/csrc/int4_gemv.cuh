@@ -25,6 +25,11 @@
 //    adds them in slab order (finish_pair below).
 //  * Programmatic dependent launch: the kernel lets its successor start early and itself touches
 //    nothing but weights before griddepcontrol.wait, so back-to-back linears overlap drain and fill.
+//  * A single activation row (M = 1) whose K range spans several stages does not wait for all of x before the main
+//    loop: the consumer warps fetch only the first K chunk themselves; for the later chunks the reducer warp, idle
+//    at that time, issues one bulk async copy each, straight into the place the fragments live in, and the
+//    consumer group that meets a chunk first turns it into fragment order in place (a 4 x 4 word transpose per
+//    32 k) and publishes it on a "chunk ready" mbarrier.  The rest of x arrives behind the weight stream.
 //  * Row-sharded multi-GPU use (nranks > 1): the reducer warp stages the CTA's rows and exchanges them
 //    with the same CTA of every peer over peer-mapped memory (exchange_rows below).
 #pragma once
@@ -33,16 +38,34 @@
 #include "common.cuh"
 #include "ptx.cuh"
 
+// Build-time switch for A/B measurements (the shipped library uses the default):
+//   AO_GEMV_BULKX   0: activations always fetched by the consumer warps before the main loop; 1: single-row kernels
+//                   fetch the first K chunk that way and the later chunks by bulk copies behind the weight stream
+#ifndef AO_GEMV_BULKX
+#define AO_GEMV_BULKX 1
+#endif
+
 namespace ao {
 namespace gemv {
+
+// Device-side timeline (a build with -DAO_GEMV_TRACE=1 only): globaltimer stamps per CTA in a device array that a
+// debug entry point of that build copies out.  The macros expand to nothing in the shipped library.
+#if defined(AO_GEMV_TRACE) && AO_GEMV_TRACE
+static __device__ unsigned long long g_trace[8 * 512 * 32];   // one per translation unit
+#define AO_TR(slot) do { g_trace[((P.trace_id & 7) * 512 + blockIdx.y * gridDim.x + blockIdx.x) * 32 + (slot)] = ptx::globaltimer_ns(); } while (0)
+#else
+#define AO_TR(slot) do { } while (0)
+#endif
 
 constexpr int kMaxConsumerWarps = 16;
 constexpr int kMaxThreads = (kMaxConsumerWarps + 2) * 32;  // + the producer warp and the reducer warp
 constexpr int kMaxStages = 4;
 constexpr int kMaxSubs = 32;             // sub-units per stage
+constexpr int kSmemBudget = 220 * 1024;
 constexpr int kWaitPolls = 2000;          // suspending polls (<= 0.1 ms each) of one mbarrier phase
 constexpr int kHeaderBytes = 256;
 constexpr int kMaxRanks = 8;
+constexpr int kMaxXChunks = 32;          // K chunks of x with a barrier pair of their own (single-row bulk prologue)
 constexpr int kMaxPairs = 16384;          // completion counters live in a fixed region so that calls of
                                           // different shapes can share one workspace
 
@@ -55,12 +78,14 @@ struct Plan {
     int subs;          // sub-units per pair per slab
     int SUBS, cpp;     // sub-units per full stage, stages (K chunks) per pair
     int G;             // CTAs per slab
+    int pair_q, pair_r;  // row pairs per CTA: NP / G, and the number of CTAs that have one more (NP % G)
     int nwarps;        // consumer warps per CTA (the CTA has one more warp, the producer)
     int GW;            // consumer warps that share one stage (nwarps / GW groups take the stages in turn)
     int nbuf;          // ring of per-pair partial-sum buffers (a power of two)
     int stages, stage_bytes;  // ring depth (a power of two), bytes per stage
     int gw_shift, stage_shift, nbuf_shift;  // log2 of GW, stages, nbuf: the per-stage bookkeeping has no divisions
     int xs_off, zero_off, sx_off, part_off, bar_off, smem_bytes;
+    int trace_id;      // timeline slot of this launch (trace builds only)
     uint32_t nib_mask, magic;  // 0x000F000F, bf16x2 (128, 128): runtime values so they stay in registers
     size_t ws_counters_off, ws_slots_off, ws_bytes;
     // output exchange over peer memory (nranks > 1): every CTA sends its rows to every peer as 8-byte
@@ -385,6 +410,43 @@ __device__ __forceinline__ void process_units(float (&acc)[NB][4], uint32_t st, 
     }
 }
 
+// Single-row bulk prologue: the warps of one consumer group turn a chunk of x that a bulk copy has just landed
+// (raw bf16, 64 bytes per 32 k) into MMA fragment order in place -- lane c of a fragment column reads the bf16
+// pairs at k = 2c + {0, 8, 16, 24}, i.e. a 4 x 4 word transpose inside every 64-byte block, one thread per block --
+// and write the per-group sums of x of the chunk's groups.  blk0: first 32-k block of the chunk inside the slab;
+// k_abs0: its first k inside the activation row; elements at k >= Kx do not exist and count as zero (Kx % 8 == 0).
+template <int G32>
+__device__ __noinline__ void prepare_x_chunk(uint8_t* xs, float* sx, int blk0, int nblk, int k_abs0, int Kx,
+                                             int wi, int GW, int lane) {
+    for (int b0 = wi * 32; b0 < nblk; b0 += GW * 32) {   // uniform per warp: the shuffles need every lane
+        const int b = b0 + lane;
+        const bool valid = b < nblk;
+        float psum = 0.f;
+        if (valid) {
+            uint4* blk = reinterpret_cast<uint4*>(xs + (size_t)(blk0 + b) * 64);
+            const int kb = k_abs0 + 32 * b;
+            uint4 q[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) q[u] = (kb + 8 * u + 8 <= Kx) ? blk[u] : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const uint32_t wv[4] = {q[u].x, q[u].y, q[u].z, q[u].w};
+                float part = 0.f;
+#pragma unroll
+                for (int cc = 0; cc < 4; ++cc) part += bf16_bits_to_f32(wv[cc] & 0xffffu) + __uint_as_float(wv[cc] & 0xffff0000u);
+                psum += part;
+            }
+            blk[0] = make_uint4(q[0].x, q[1].x, q[2].x, q[3].x);
+            blk[1] = make_uint4(q[0].y, q[1].y, q[2].y, q[3].y);
+            blk[2] = make_uint4(q[0].z, q[1].z, q[2].z, q[3].z);
+            blk[3] = make_uint4(q[0].w, q[1].w, q[2].w, q[3].w);
+        }
+#pragma unroll
+        for (int o = 1; o < G32; o <<= 1) psum += __shfl_xor_sync(0xffffffffu, psum, o);
+        if (valid && (b & (G32 - 1)) == 0) sx[((blk0 + b) / G32) * 8] = psum;
+    }
+}
+
 // shared-memory control block of one CTA
 constexpr int kMaxPairBufs = 8;
 
@@ -400,16 +462,24 @@ int4_gemv_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int Kx, con
     const int nwarps = P.nwarps, nconsumers = nwarps * 32;
     const int slab = blockIdx.y, cta = blockIdx.x;
     const uint32_t smem_base = ptx::smem_addr(smem);
+    if (tid == 0) AO_TR(0);                      // CTA start
+    if (tid == P.nwarps * 32) AO_TR(1);          // producer lane start
     const int nstages = P.stages, stage_bytes = P.stage_bytes;
     const uint32_t full_bar = smem_base + P.bar_off, empty_bar = full_bar + kMaxStages * 8;
     const uint32_t pair_full_bar = empty_bar + kMaxStages * 8, pair_free_bar = pair_full_bar + kMaxPairBufs * 8;
+    const uint32_t x_full_bar = pair_free_bar + kMaxPairBufs * 8, x_ready_bar = x_full_bar + kMaxXChunks * 8;
     const int subs = P.subs, SUBS = P.SUBS, cpp = P.cpp;
+    // single activation row, several K chunks: chunks 1.. of x by bulk copy when its address and width allow
+    constexpr bool kM1 = (NB == 1 && MR == 1);
+    const bool bulk_x = kM1 && (AO_GEMV_BULKX != 0) && cpp > 1 && cpp <= kMaxXChunks &&
+                        (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (Kx & 7) == 0;
     const uint32_t tile_b = SUBS * UB, sc_off = 2 * SUBS * UB;
     int* status = reinterpret_cast<int*>(ws);
 
-    // whole row pairs per CTA; its stream of stages is (pair, K chunk), pair-major
-    const int pbeg = static_cast<int>((static_cast<unsigned>(cta) * static_cast<unsigned>(P.NP)) / static_cast<unsigned>(P.G));
-    const int pend = static_cast<int>((static_cast<unsigned>(cta + 1) * static_cast<unsigned>(P.NP)) / static_cast<unsigned>(P.G));
+    // whole row pairs per CTA, contiguous, the first pair_r CTAs one more than the others; the CTA's stream of stages
+    // is (pair, K chunk), pair-major
+    const int pbeg = cta * P.pair_q + min(cta, P.pair_r);
+    const int pend = pbeg + P.pair_q + (cta < P.pair_r ? 1 : 0);
     const int nstage_total = (pend - pbeg) * cpp;
 
     // the next kernel of the stream may start its own weight prefetch as soon as SMs free up; whatever it reads or
@@ -425,6 +495,12 @@ int4_gemv_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int Kx, con
             ptx::mbar_init(pair_full_bar + 8 * i, nslots_init);  // one arrival per warp that worked on the pair
             ptx::mbar_init(pair_free_bar + 8 * i, 1);            // the reducer hands the buffer back
         }
+        if (bulk_x) {
+            for (int c = 1; c < cpp; ++c) {
+                ptx::mbar_init(x_full_bar + 8 * c, 1);           // the bulk copy of chunk c of x (expect_tx arrival)
+                ptx::mbar_init(x_ready_bar + 8 * c, 1 << P.gw_shift);   // the warps that put it into fragment order
+            }
+        }
         ptx::fence_mbar_init();
     }
     // the producer warp only announces that the barriers exist and goes straight to its first copies
@@ -434,6 +510,7 @@ int4_gemv_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int Kx, con
     } else {
         ptx::named_barrier_sync(2, blockDim.x);
     }
+    if (tid == 0) AO_TR(5);                      // consumers past the barrier-ready barrier
 
     if (warp == nwarps) {
         // =============================== producer warp =================================================
@@ -460,6 +537,7 @@ int4_gemv_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int Kx, con
                 ptx::mbar_arrive_expect_tx(bar, has_b ? 2u * wbytes : wbytes);
                 ptx::bulk_copy_g2s_hint(dst, src, wbytes, bar, stream_once);
                 if (has_b) ptx::bulk_copy_g2s_hint(dst + tile_b, src + (size_t)P.K * 4, wbytes, bar, stream_once);
+                if (t == 0) AO_TR(8);            // first stage's bulk copies issued
             }
             {
                 // 64 bytes ((scale, zero) of the pair's 16 rows) per group; a lone last tile has only 32
@@ -483,6 +561,7 @@ int4_gemv_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int Kx, con
                 phase ^= 1u;
             }
         }
+        if (lane == 0) AO_TR(9);                 // last stage issued
         if (!ok && lane == 0) {
             ptx::grid_dependency_wait();
             atomicExch(status, AO_ERR_TIMEOUT);
@@ -492,7 +571,26 @@ int4_gemv_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int Kx, con
 
     if (warp == nwarps + 1) {
         // =============================== reducer warp ==================================================
+        if (lane == 0) AO_TR(10);      // reducer at the dependency wait
         ptx::grid_dependency_wait();   // y, the workspace and the exchange state may be in use by earlier kernels
+        if (lane == 0) AO_TR(11);      // dependency wait passed
+        if (bulk_x && lane == 0) {
+            // x may be the previous kernel's output, hence after the wait: one bulk copy per K chunk, straight
+            // into the place where the fragments live (the consumers reorder each chunk in place)
+            const uint64_t keep = ptx::l2_policy_evict_last();   // every CTA reads the same activations
+            const int CK = SUBS * UK;
+            for (int c = 1; c < cpp; ++c) {
+                const int k0 = slab * P.KS + c * CK;                         // first k of the chunk in the row
+                const int nk = max(0, min(min(CK, P.KS - c * CK), Kx - k0));  // elements that exist
+                const uint32_t bar = x_full_bar + 8 * c;
+                if (nk > 0) {
+                    ptx::mbar_arrive_expect_tx(bar, static_cast<uint32_t>(nk) * 2u);
+                    ptx::bulk_copy_g2s_hint(smem_base + P.xs_off + c * CK * 2, x + k0, static_cast<uint32_t>(nk) * 2u, bar, keep);
+                } else {
+                    ptx::mbar_arrive(bar);
+                }
+            }
+        }
         // adds the consumer warps' partial sums of each finished pair in slot order and stores the rows
         const int NGr = nwarps >> P.gw_shift;
         const int nslots = min(NGr, cpp) << P.gw_shift;
@@ -555,25 +653,27 @@ int4_gemv_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int Kx, con
             if (!exchange_rows(P, reinterpret_cast<const __nv_bfloat16*>(smem + P.ystage_off), pbeg, pend - pbeg, lane, call))
                 ok = false;
         }
+        if (lane == 0) AO_TR(12);      // reducer done: last rows stored
         if (!ok && lane == 0) atomicExch(status, AO_ERR_TIMEOUT);
         return;
     }
 
     // ================================= consumer warps ==================================================
     ptx::grid_dependency_wait();       // x may be the output of the previous kernel
-    // ---- activation prologue: x slab -> MMA fragment order, plus per-group sums of x -------------------
+    // ---- activation prologue: x slab (with later chunks by bulk copy: its first chunk) -> MMA fragment order,
+    // ---- plus per-group sums of x ----------------------------------------------------------------------
     {
+        // lanes without a batch column read zeros: one sub-unit's worth of fragment bytes
+        for (int i = tid; i < S::SPU * S::XSTEP / 4; i += nconsumers) reinterpret_cast<uint32_t*>(smem + P.zero_off)[i] = 0u;
         // One item = 8 consecutive k of one batch row (16 bytes, one vector load: every CTA reads all of x, so the
         // number of L2 requests per CTA is what this prologue costs).  Its four bf16 pairs go to the four lanes
         // c = 0..3 of the row's fragment column; the g / 8 items of a quantization group sit in adjacent lanes and
         // add up their x with shuffles.
         constexpr int G8 = G32 * 4;                 // items per quantization group
-        const int octs = P.KS / 8;                  // items per batch row (a multiple of G8)
+        const int octs = (bulk_x ? min(SUBS * UK, P.KS) : P.KS) / 8;   // items per batch row (a multiple of G8)
         const int items = octs * (NB * MR);         // rows at and beyond M are zeros
         const int items_round = (items + 31) / 32 * 32;
         float* sx = reinterpret_cast<float*>(smem + P.sx_off);
-        // lanes without a batch column read zeros: one sub-unit's worth of fragment bytes
-        for (int i = tid; i < S::SPU * S::XSTEP / 4; i += nconsumers) reinterpret_cast<uint32_t*>(smem + P.zero_off)[i] = 0u;
         if constexpr (MR < 8) {
             // group sums of the fragment columns that carry no batch row
             const int groups = P.KS / (32 * G32);
@@ -632,6 +732,7 @@ int4_gemv_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int Kx, con
         }
         ptx::named_barrier_sync(1, nconsumers);
     }
+    if (tid == 0) AO_TR(13);                     // activations staged
 
     // ---- main loop: sub-units of the CTA's stream are dealt round-robin to the consumer warps ---------
     const bool x_lane = lane < MRL;
@@ -658,6 +759,7 @@ int4_gemv_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int Kx, con
     const int nslots = ncontrib << gw_shift;     // warps whose partial sums make up one pair
     const int stage_mask = nstages - 1, stage_shift = P.stage_shift;
     const int nbuf_mask = P.nbuf - 1, nbuf_shift = P.nbuf_shift;
+    uint32_t x_seen = 1u;                        // chunks of x this warp knows to be in fragment order
     for (int pi = 0, t0 = 0; pi < npairs && ok; ++pi, t0 += cpp) {
         // the pair's stages t0 .. t0 + cpp - 1 go to groups t0 % NG, t0 % NG + 1, ...
         const int ordinal = (grp - t0) & ng_mask;
@@ -671,6 +773,26 @@ int4_gemv_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int Kx, con
             if (!ptx::mbar_wait_bounded(full_bar + 8 * s, phase, kWaitPolls)) {
                 ok = false;
                 break;
+            }
+            if (tid == 0 && t == 0) AO_TR(14);   // warp 0 sees its first stage full
+            if (bulk_x && !((x_seen >> c) & 1u)) {
+                // chunk c of x: whoever meets it first (the group that has stage c of the CTA's first pair) puts
+                // it into fragment order; everybody else waits until that has happened
+                if (pi == 0) {
+                    if (!ptx::mbar_wait_bounded(x_full_bar + 8 * c, 0u, kWaitPolls)) {
+                        ok = false;
+                        break;
+                    }
+                    prepare_x_chunk<G32>(smem + P.xs_off, reinterpret_cast<float*>(smem + P.sx_off), sub0 * (UK / 32),
+                                         nsub * (UK / 32), slab * P.KS + sub0 * UK, Kx, wi, GW, lane);
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(x_ready_bar + 8 * c);
+                }
+                if (!ptx::mbar_wait_bounded(x_ready_bar + 8 * c, 0u, kWaitPolls)) {
+                    ok = false;
+                    break;
+                }
+                x_seen |= 1u << c;
             }
             const uint32_t st = smem_base + s * stage_bytes;
             int j = (wi * nsub) >> gw_shift;
@@ -702,6 +824,7 @@ int4_gemv_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int Kx, con
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(pair_full_bar + 8 * buf);
     }
+    if (tid == 0) AO_TR(15);                     // warp 0 leaves the main loop
     if (!ok && lane == 0) atomicExch(status, AO_ERR_TIMEOUT);
 }
 

@@ -8,3 +8,10 @@ template int launch_ikt<8>(const Plan&, const void*, long long, int, const void*
 }
 }  // namespace ao
 
+
+#if defined(AO_GEMV_TRACE) && AO_GEMV_TRACE
+// trace builds: copy the timeline of the kernels of this translation unit out (8 launches x 512 CTAs x 32 slots)
+extern "C" int ao_debug_read_trace(unsigned long long* host_out, int n) {
+    return (int)cudaMemcpyFromSymbol(host_out, ao::gemv::g_trace, sizeof(unsigned long long) * n);
+}
+#endif

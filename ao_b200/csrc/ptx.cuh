@@ -54,17 +54,36 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
     return t;
 }
 
-// Bounded wait: returns false if the phase did not complete within about limit * 0.1 ms.  mbarrier.try_wait blocks
-// inside the hardware for a short, implementation-defined time and returns as soon as the phase completes, so the
-// loop issues few instructions and wakes up without the latency of a sleep.
+// try_wait with a suspend-time hint (ns): the thread may sleep inside the hardware for up to that long, and is
+// woken as soon as the phase completes.  Without the hint a failed try_wait comes back after a few tens of cycles,
+// and a warp that waits a long time (a producer on a full ring, a reducer between row pairs) spends issue slots of
+// its scheduler on the polling loop.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(hint_ns)
+        : "memory");
+    return ok != 0;
+}
+
+// Bounded wait: returns false if the phase did not complete within about limit * 0.1 ms.  The wait itself happens
+// inside mbarrier.try_wait (see above); the loop only re-arms it and checks the time budget.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, int limit) {
     if (mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = globaltimer_ns();
     const uint64_t budget = static_cast<uint64_t>(limit) * 100000ull;
     for (;;) {
+#if defined(AO_B200_WAIT_NO_HINT)
 #pragma unroll 1
         for (int i = 0; i < 16; ++i)
             if (mbar_try_wait(bar, parity)) return true;
+#else
+        if (mbar_try_wait_hint(bar, parity, 20000u)) return true;
+#endif
         if (globaltimer_ns() - t0 > budget) return false;
     }
 }
