@@ -68,6 +68,10 @@ PROTOTYPES = {
     "ao_int4_gemv_static_scratch": (_int, [_ptr, _i64, _i64, _ptr, _ptr, _i64, _i64, _i64, _int, _int, _ptr, _ptr]),
     "ao_int4_gemv_gather": (_int, [_ptr, _i64, _i64, _ptr, _ptr, _i64, _i64, _i64, _int, _int, _int, _int,
                                    _c.POINTER(_ptr), _ptr, _ptr, _ptr, _size, _ptr]),
+    "ao_int4_gemv_push": (_int, [_ptr, _i64, _i64, _ptr, _ptr, _i64, _i64, _i64, _int, _int, _int, _int,
+                                 _c.POINTER(_ptr), _ptr, _ptr, _ptr, _size, _ptr]),
+    "ao_gather_exchange": (_int, [_int, _c.POINTER(_ptr), _c.POINTER(_ptr), _c.POINTER(_ptr), _i64p, _i64p, _int, _int,
+                                  _int, _ptr, _ptr]),
     "ao_comm_export": (_int, [_ptr, _ptr, _i64p]),
     "ao_comm_import": (_int, [_ptr, _c.POINTER(_ptr)]),
     "ao_comm_close": (_int, [_ptr]),

@@ -172,16 +172,16 @@ extern "C" int ao_int4_gemv(const void* x_bf16, int64_t x_row_stride, int64_t x_
                           workspace, workspace_bytes, stream);
 }
 
-// The same kernel with the output exchange in its epilogue: every CTA sends its rows to the same CTA of every peer
-// through peer-mapped memory (NVLink) and collects the peers' rows; the kernel returns once this GPU's gathered
-// output [nranks][M][N] is complete.
-extern "C" int ao_int4_gemv_gather(const void* x_bf16, int64_t x_row_stride, int64_t x_cols, const int32_t* packed,
+// The same kernel with the output exchange of a row-sharded layer in its epilogue: every CTA sends its rows to every
+// peer's landing area through peer-mapped memory (NVLink) and returns without waiting; ao_gather_wait (comm.cu)
+// collects the peers' rows.  ao_int4_gemv_gather enqueues both for one call site.
+extern "C" int ao_int4_gemv_push(const void* x_bf16, int64_t x_row_stride, int64_t x_cols, const int32_t* packed,
                                    const void* scale_and_zero, int64_t M, int64_t N, int64_t K, int group,
-                                   int inner_k_tiles, int nranks, int rank, void* const* peer_landing,
-                                   void* y_gathered, void* local_state, void* workspace, size_t workspace_bytes,
-                                   ao_stream_t stream) {
+                                 int inner_k_tiles, int nranks, int rank, void* const* peer_landing,
+                                 void* y_gathered, void* site_state, void* workspace, size_t workspace_bytes,
+                                 ao_stream_t stream) {
     if (M == 0 || N == 0) return AO_OK;
-    if (nranks < 1 || nranks > gemv::kMaxRanks || rank < 0 || rank >= nranks || !peer_landing || !y_gathered || !local_state)
+    if (nranks < 1 || nranks > gemv::kMaxRanks || rank < 0 || rank >= nranks || !peer_landing || !y_gathered || !site_state)
         return AO_ERR_ARG;
     gemv::Plan P;
     int rc = gemv::make_plan(M, N, K, group, inner_k_tiles, &P);
@@ -190,12 +190,12 @@ extern "C" int ao_int4_gemv_gather(const void* x_bf16, int64_t x_row_stride, int
     if (P.smem_bytes > 227 * 1024) return AO_ERR_UNSUPPORTED;
     if (x_cols < 2 || x_cols > K || x_cols % 2 != 0 || x_row_stride < x_cols || x_row_stride % 2 != 0) return AO_ERR_SHAPE;
     if (!aligned(x_bf16, 4) || !aligned(packed, 16) || !aligned(scale_and_zero, 16) || !aligned(workspace, 256) ||
-        !aligned(local_state, 8) || !aligned(y_gathered, 16))
+        !aligned(site_state, 16) || !aligned(y_gathered, 16))
         return AO_ERR_ALIGN;
     if (workspace == nullptr || workspace_bytes < P.ws_bytes) return AO_ERR_WORKSPACE;
     P.nranks = nranks;
     P.rank = rank;
-    P.local_state = static_cast<unsigned*>(local_state);
+    P.local_state = static_cast<unsigned*>(site_state);
     P.y_gathered = static_cast<__nv_bfloat16*>(y_gathered);
     for (int r = 0; r < nranks; ++r) {
         if (!peer_landing[r] || !aligned(peer_landing[r], 16)) return AO_ERR_ALIGN;
@@ -208,4 +208,20 @@ extern "C" int ao_int4_gemv_gather(const void* x_bf16, int64_t x_row_stride, int
         case 2: return gemv::launch_ikt<2>(P, x_bf16, x_row_stride, (int)x_cols, packed, scale_and_zero, y_gathered, workspace, st);
     }
     return AO_ERR_ARG;
+}
+
+extern "C" int ao_gather_exchange(int nsites, void* const* peer_landing, void* const* y_gathered, void* const* state,
+                                  const int64_t* M, const int64_t* N, int nranks, int rank, int push, void* workspace,
+                                  ao_stream_t stream);
+
+extern "C" int ao_int4_gemv_gather(const void* x_bf16, int64_t x_row_stride, int64_t x_cols, const int32_t* packed,
+                                   const void* scale_and_zero, int64_t M, int64_t N, int64_t K, int group,
+                                   int inner_k_tiles, int nranks, int rank, void* const* peer_landing,
+                                   void* y_gathered, void* site_state, void* workspace, size_t workspace_bytes,
+                                   ao_stream_t stream) {
+    if (M == 0 || N == 0) return AO_OK;
+    int rc = ao_int4_gemv_push(x_bf16, x_row_stride, x_cols, packed, scale_and_zero, M, N, K, group, inner_k_tiles, nranks,
+                               rank, peer_landing, y_gathered, site_state, workspace, workspace_bytes, stream);
+    if (rc || nranks < 2) return rc;
+    return ao_gather_exchange(1, peer_landing, &y_gathered, &site_state, &M, &N, nranks, rank, /*push=*/0, workspace, stream);
 }

@@ -30,8 +30,11 @@
 //    at that time, issues one bulk async copy each, straight into the place the fragments live in, and the
 //    consumer group that meets a chunk first turns it into fragment order in place (a 4 x 4 word transpose per
 //    32 k) and publishes it on a "chunk ready" mbarrier.  The rest of x arrives behind the weight stream.
-//  * Row-sharded multi-GPU use (nranks > 1): the reducer warp stages the CTA's rows and exchanges them
-//    with the same CTA of every peer over peer-mapped memory (exchange_rows below).
+//  * Row-sharded multi-GPU use (nranks > 1): the reducer warp stages the CTA's rows and, at the end of the CTA,
+//    stores them into every peer's landing area over peer-mapped memory (push_rows below).  The kernel does not
+//    wait for the peers' rows: a layer must not end on the slowest rank, and its SMs should be free for the next
+//    layer's weight prefetch while the rows are in flight.  Whoever needs the gathered output collects it with
+//    the small gather-wait kernel (comm.cu).
 #pragma once
 #include <cstdlib>
 
@@ -89,9 +92,9 @@ struct Plan {
     uint32_t nib_mask, magic;  // 0x000F000F, bf16x2 (128, 128): runtime values so they stay in registers
     size_t ws_counters_off, ws_slots_off, ws_bytes;
     // output exchange over peer memory (nranks > 1): every CTA sends its rows to every peer as 8-byte
-    // {two bf16 rows, call number} words (peer_ll[r]: rank r's landing area [source rank][M][N/2] of such words) and
-    // collects the same rows of every peer from its own landing area into y_gathered [rank][M][N];
-    // local_state = this rank's {finished-CTA counter, number of calls so far}
+    // {two bf16 rows, call number} words.  peer_ll[r]: rank r's landing area of this call site, two buffers
+    // [call parity][source rank][M][N/2] of such words; the CTA's own rows also go to y_gathered [rank][M][N];
+    // local_state = the call site's {CTAs of this launch that have pushed, pushes so far, ...} on this rank
     int nranks, rank;
     int ystage_off;     // shared-memory staging of the CTA's output rows [M][16 * pairs per CTA]
     int rows_cta_max;   // 16 * max pairs per CTA
@@ -133,6 +136,12 @@ __device__ __forceinline__ uint2 ld_volatile_u2(const uint2* p) {
 }
 __device__ __forceinline__ void st_volatile_u2(uint2* p, uint32_t a, uint32_t b) {
     asm volatile("st.volatile.global.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(a), "r"(b) : "memory");
+}
+// 8-byte store into a peer's memory: a plain (weak) store, which is posted without waiting for the NVLink round
+// trip of the thread's previous store to that peer (volatile stores were observed to); the word is still written as
+// one unit
+__device__ __forceinline__ void st_peer_u2(uint2* p, uint32_t a, uint32_t b) {
+    asm volatile("st.global.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(a), "r"(b) : "memory");
 }
 
 // One warp finishes row pair p for its CTA (which has seen the pair's whole K range inside its slab): a direct bf16
@@ -237,24 +246,26 @@ __device__ __forceinline__ void stage_rows(const Plan& P, __nv_bfloat16* ys, con
     }
 }
 
-// One warp exchanges the CTA's rows (output rows 16 * pbeg .. of every batch row) with the same CTA of every peer.
-// Data and "it has arrived" travel in the same 8-byte store (two bf16 rows + the call number), which the hardware
-// writes as one unit, so no fence and no separate flag are needed: the receiver polls each word of its landing
-// area until it carries this call's number (bounded), and copies the rows into the gathered output.  Every rank
-// runs the same grid on the same shape, so CTA c of a peer owns exactly the rows CTA c collects here.
-static __device__ __noinline__ bool exchange_rows(const Plan& P, const __nv_bfloat16* ys, int pbeg, int npairs, int lane,
-                                                  unsigned call) {
+// One warp sends the CTA's rows (output rows 16 * pbeg .. of every batch row) to every peer and copies them into
+// this rank's own block of the gathered output.  Data and "it has arrived" travel in the same 8-byte store (two bf16
+// rows + the call number), which the hardware writes as one unit, so no fence and no separate flag are needed: a
+// receiver polls each word of its landing area until it carries the call's number.  The landing areas are double
+// buffered by the parity of the call number: a peer that is one call ahead writes into the other buffer, and it
+// cannot be two ahead, because its next push of this call site comes after its own gather-wait, which needs this
+// rank's push in between.
+static __device__ __noinline__ void push_rows(const Plan& P, const __nv_bfloat16* ys, int pbeg, int npairs, int lane,
+                                              unsigned call) {
     const int nrows = min(16 * npairs, P.N - 16 * pbeg);     // a lone last 8-row tile ends the matrix
     const int n2 = nrows / 2, half_n = P.N / 2;              // 4-byte row pairs
-    const size_t block = (size_t)P.M * half_n;                // words per source rank in a landing area
+    const size_t block = (size_t)P.M * half_n;                // words per source rank in a landing buffer
+    const size_t parity_off = (call & 1u) ? (size_t)P.nranks * block : 0;
     __syncwarp();
-    // send
     for (int i = 1; i < P.nranks; ++i) {
         const int r = (P.rank + i) % P.nranks;
-        uint2* dst = P.peer_ll[r] + (size_t)P.rank * block + 8 * pbeg;
+        uint2* dst = P.peer_ll[r] + parity_off + (size_t)P.rank * block + 8 * pbeg;
         for (int m = 0; m < P.M; ++m) {
             const uint32_t* src = reinterpret_cast<const uint32_t*>(ys + m * P.rows_cta_max);
-            for (int j = lane; j < n2; j += 32) st_volatile_u2(dst + (size_t)m * half_n + j, src[j], call);
+            for (int j = lane; j < n2; j += 32) st_peer_u2(dst + (size_t)m * half_n + j, src[j], call);
         }
     }
     // local block
@@ -266,44 +277,6 @@ static __device__ __noinline__ bool exchange_rows(const Plan& P, const __nv_bflo
             for (int j = lane; j < nrows / 8; j += 32) d[j] = src[j];
         }
     }
-    // receive: all (source, batch row, row pair) words of this CTA form one index space; a lane issues eight loads
-    // before it looks at any of them, so the polling costs a few memory latencies, not one per word
-    bool ok = true;
-    const uint64_t t0 = ptx::globaltimer_ns();
-    const int per_src = P.M * n2, total = (P.nranks - 1) * per_src;
-    const uint2* land = P.peer_ll[P.rank] + 8 * pbeg;
-    for (int b0 = 0; b0 < total && ok; b0 += 32 * 8) {   // uniform trip count: the vote below needs every lane
-        const int base = b0 + lane;
-        uint2 v[8];
-        const uint2* src[8];
-        uint32_t* dst[8];
-#pragma unroll
-        for (int q = 0; q < 8; ++q) {
-            const int i = base + 32 * q;
-            src[q] = nullptr;
-            if (i < total) {
-                const int si = i / per_src, rem = i - si * per_src;
-                const int m = rem / n2, j = rem - m * n2;
-                const int r = (P.rank + 1 + si) % P.nranks;
-                src[q] = land + (size_t)r * block + (size_t)m * half_n + j;
-                dst[q] = reinterpret_cast<uint32_t*>(P.y_gathered + (size_t)r * P.M * P.N + 16 * pbeg) + (size_t)m * half_n + j;
-                v[q] = ld_volatile_u2(src[q]);
-            }
-        }
-#pragma unroll
-        for (int q = 0; q < 8; ++q) {
-            if (src[q] == nullptr) continue;
-            while (v[q].y != call) {
-                if (ptx::globaltimer_ns() - t0 > 200000000ull) {   // 0.2 s
-                    ok = false;
-                    break;
-                }
-                v[q] = ld_volatile_u2(src[q]);
-            }
-            *dst[q] = v[q].x;
-        }
-        ok = __all_sync(0xffffffffu, ok);
-    }
     // the last CTA to finish advances the call number for the next launch
     if (lane == 0) {
         const unsigned done = atomicAdd(P.local_state, 1u);
@@ -312,7 +285,6 @@ static __device__ __noinline__ bool exchange_rows(const Plan& P, const __nv_bflo
             P.local_state[1] = call;
         }
     }
-    return ok;
 }
 
 template <int N_WORDS>
@@ -649,9 +621,8 @@ int4_gemv_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int Kx, con
             }
         }
         if (P.nranks > 1) {
-            // even after a failed wait the exchange runs, so that the other ranks are not left waiting for this one
-            if (!exchange_rows(P, reinterpret_cast<const __nv_bfloat16*>(smem + P.ystage_off), pbeg, pend - pbeg, lane, call))
-                ok = false;
+            // even after a failed wait the rows are sent, so that the other ranks are not left waiting for this one
+            push_rows(P, reinterpret_cast<const __nv_bfloat16*>(smem + P.ystage_off), pbeg, pend - pbeg, lane, call);
         }
         if (lane == 0) AO_TR(12);      // reducer done: last rows stored
         if (!ok && lane == 0) atomicExch(status, AO_ERR_TIMEOUT);

@@ -3,6 +3,8 @@ from .affine_quantized_tensor import (
     PlainAQTLayout,
     TensorCoreTiledAQTLayout,
     to_affine_quantized,
+    use_static_linear_outputs,
 )
 
-__all__ = ["AffineQuantizedTensor", "PlainAQTLayout", "TensorCoreTiledAQTLayout", "to_affine_quantized"]
+__all__ = ["AffineQuantizedTensor", "PlainAQTLayout", "TensorCoreTiledAQTLayout", "to_affine_quantized",
+           "use_static_linear_outputs"]

@@ -337,7 +337,7 @@ class _Int4LinearPlan:
     (each of those goes through __torch_function__) and does no argument validation beyond what changes per call."""
 
     __slots__ = ("packed", "sz", "group", "ikt", "N", "K", "n_out", "k_in", "device", "dev_index", "fn", "ws_fn",
-                 "p_packed", "p_sz", "ws_cache")
+                 "p_packed", "p_sz", "ws_cache", "static_out")
 
     def __init__(self, w):
         lt = w.layout_tensor
@@ -356,6 +356,7 @@ class _Int4LinearPlan:
         self.p_packed = self.packed.data_ptr()
         self.p_sz = self.sz.data_ptr()
         self.ws_cache = {}
+        self.static_out = None     # {M: output buffer} once use_static_linear_outputs() has switched it on
 
     def __call__(self, x, bias):
         k_in = self.k_in
@@ -363,7 +364,12 @@ class _Int4LinearPlan:
         if x2.stride(1) != 1 or (x2.stride(0) & 1) or (x2.data_ptr() & 3) or (k_in & 1):
             x2 = torch.nn.functional.pad(x2, (0, k_in & 1)).contiguous()
         M = x2.shape[0]
-        y = torch.empty((M, self.N), dtype=torch.bfloat16, device=self.device)
+        if self.static_out is None:
+            y = torch.empty((M, self.N), dtype=torch.bfloat16, device=self.device)
+        else:
+            y = self.static_out.get(M)
+            if y is None:
+                y = self.static_out[M] = torch.empty((M, self.N), dtype=torch.bfloat16, device=self.device)
         if M:
             stream = torch._C._cuda_getCurrentRawStream(self.dev_index)
             ws = _cabi.workspace_for(self.ws_cache, self.ws_fn, (M, self.N, self.K, self.group, self.ikt), self.device, stream)
@@ -375,8 +381,33 @@ class _Int4LinearPlan:
             y = y[:, : self.n_out]
         y = y.reshape(*x.shape[:-1], self.n_out)
         if bias is not None:
-            y += bias
+            y = y + bias if self.static_out is not None else y.add_(bias)
         return y
+
+
+def use_static_linear_outputs(module: torch.nn.Module, enabled: bool = True, outputs=None) -> None:
+    """Makes every int4 tensor_core_tiled linear of `module` write its result into one buffer per batch size that it
+    owns, instead of a fresh tensor per call.  A decode loop then allocates nothing per token, and a caller can read
+    the result where it lies (e.g. copy it to the host) without an extra device copy.  The price is the aliasing rule
+    of CUDA-graph static outputs: the tensor a call returns is overwritten by the layer's next call with the same
+    batch size.
+
+    `outputs` (optional): {submodule name: bf16 [M][out_features] contiguous CUDA tensor} - the caller's own buffers
+    for those layers and that batch size, e.g. slices of one staging buffer that leaves the device in a single copy."""
+    outputs = outputs or {}
+    for name, mod in module.named_modules():
+        w = getattr(mod, "weight", None)
+        if type(w) is AffineQuantizedTensor and w.extended_layout == "tensor_core_tiled" and w.dtype == torch.bfloat16:
+            if "_linear_plan" not in w.__dict__:
+                w.__dict__["_linear_plan"] = _Int4LinearPlan(w)
+            plan = w.__dict__["_linear_plan"]
+            plan.static_out = {} if enabled else None
+            buf = outputs.get(name)
+            if enabled and buf is not None:
+                if not (buf.is_cuda and buf.dtype == torch.bfloat16 and buf.dim() == 2 and buf.is_contiguous()
+                        and buf.shape[1] == plan.N and buf.device == plan.device):
+                    raise ValueError(f"output buffer of {name!r} must be a contiguous bf16 [M][{plan.N}] tensor on {plan.device}")
+                plan.static_out[int(buf.shape[0])] = buf
 
 
 def _quantized_linear_op(input_tensor, weight_qtensor, bias):

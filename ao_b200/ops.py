@@ -101,39 +101,65 @@ def weight_int4pack_mm(x: Tensor, packed: Tensor, group_size: int, scale_and_zer
 
 
 def gather_slot_bytes(world: int, M: int, N: int) -> int:
-    """Payload bytes one call site of weight_int4pack_mm_gather needs: output [world][M][N] bf16 + landing area."""
-    return (6 * world * M * N + 255) // 256 * 256
+    """Payload bytes one call site of weight_int4pack_mm_gather needs (counters, output [world][M][N], landing area)."""
+    from .comm import PeerExchange
+    return PeerExchange.site_bytes(world, M, N)
 
 
 def weight_int4pack_mm_gather(x: Tensor, packed: Tensor, group_size: int, scale_and_zero: Tensor, exchange,
-                              slot_offset_bytes: int = 0, workspace: Tensor = None) -> Tensor:
+                              slot_offset_bytes: int = 0, workspace: Tensor = None, wait: bool = True, site=None) -> Tensor:
     """Row-sharded weight_int4pack_mm with the output exchange fused into the kernel's epilogue.
 
-    Uses gather_slot_bytes(world, M, N_local) bytes of the exchange's payload (ao_b200.comm.PeerExchange) at
-    slot_offset_bytes on every rank: the gathered output [world][M][N_local] followed by the landing area the
-    peers' kernels store into.  Returns this rank's gathered view, complete when the kernel completes.  Every rank
-    must make the same calls in the same order; M <= 16; give consecutive call sites different slots."""
+    Uses the call site at `slot_offset_bytes` of the exchange's payload (ao_b200.comm.PeerExchange; gather_slot_bytes
+    bytes), or `site` (PeerExchange.reserve).  Every CTA of the GEMV stores its rows into all peers' landing areas as
+    it finishes; with wait=True a small second kernel collects the peers' rows, and the returned view
+    [world][M][N_local] is complete when that kernel completes.  With wait=False only this rank's own block is
+    written: call gather_wait(exchange, [sites]) later in the stream, before the same site is used again.  The view
+    is overwritten by the next call of the site.  Every rank must make the same calls in the same order; M <= 8."""
     _cabi.require_cuda(x, packed, scale_and_zero)
     torch._check(x.dim() == 2 and x.dtype == torch.bfloat16 and x.stride(1) == 1, lambda: "x must be 2-D bfloat16")
     ikt = packed.shape[3] * 2
     N, K = packed.shape[0] * 8, packed.shape[1] * ikt * 16
     M = x.shape[0]
     world, rank = exchange.world, exchange.rank
-    out = exchange.payload(slot_offset_bytes, (world, M, N), torch.bfloat16)
-    landing_off = slot_offset_bytes + 2 * world * M * N
-    torch._check(landing_off % 16 == 0 and slot_offset_bytes + gather_slot_bytes(world, M, N) <= exchange.payload_bytes,
-                 lambda: "exchange payload too small for this call site")
+    st = site if site is not None else exchange.site(slot_offset_bytes, M, N)
+    torch._check(st.M == M and st.N == N, lambda: "call site was reserved for a different shape")
     lib = _cabi.lib()
     nbytes = lib.ao_int4_gemv_workspace_bytes(M, N, K, group_size, ikt)
     torch._check(nbytes > 0, lambda: f"unsupported shape M={M} N={N} K={K} group={group_size}")
-    landing = exchange.peer_pointers(landing_off)
+    fn = lib.ao_int4_gemv_gather if wait else lib.ao_int4_gemv_push
     with torch.cuda.device(x.device):
         ws = _cabi.workspace(nbytes, x.device) if workspace is None else workspace
-        rc = lib.ao_int4_gemv_gather(_cabi.ptr(x), x.stride(0), x.shape[1], _cabi.ptr(packed), _cabi.ptr(scale_and_zero), M, N,
-                                     K, group_size, ikt, world, rank, landing, _cabi.ptr(out), exchange.local_state,
-                                     _cabi.ptr(ws), ws.numel(), _stream(x))
+        rc = fn(_cabi.ptr(x), x.stride(0), x.shape[1], _cabi.ptr(packed), _cabi.ptr(scale_and_zero), M, N, K, group_size, ikt,
+                world, rank, st.peer_landing, st.y_ptr, st.state, _cabi.ptr(ws), ws.numel(), _stream(x))
     _cabi.check(rc, "weight_int4pack_mm_gather")
-    return out
+    return st.y
+
+
+def gather_exchange(exchange, sites, push: bool = True, workspace: Tensor = None) -> None:
+    """All-gather of the given call sites (at most 8 layers) in one small kernel.  push=True: every rank's own block
+    site.y[rank] (written there by weight_int4pack_mm(..., out=site.y[rank])) is sent to all peers first; push=False:
+    the rows were already sent by weight_int4pack_mm_gather(..., wait=False).  When the kernel completes, every
+    site's gathered output site.y [world][M][N] is complete on this GPU."""
+    import ctypes
+    n, world = len(sites), exchange.world
+    torch._check(1 <= n <= 8, lambda: "gather_exchange takes 1 to 8 call sites")
+    landing = (ctypes.c_void_p * (n * world))(*[p for s in sites for p in s.peer_landing])
+    arr = ctypes.c_void_p * n
+    ys = arr(*[s.y_ptr for s in sites])
+    states = arr(*[s.state for s in sites])
+    Ms, Ns = _cabi.i64_array([s.M for s in sites]), _cabi.i64_array([s.N for s in sites])
+    dev = exchange.device
+    with torch.cuda.device(dev):
+        ws = _cabi.workspace(256, dev) if workspace is None else workspace
+        rc = _cabi.lib().ao_gather_exchange(n, landing, ys, states, Ms, Ns, world, exchange.rank, 1 if push else 0,
+                                            _cabi.ptr(ws), _cabi.stream_ptr(dev))
+    _cabi.check(rc, "gather_exchange")
+
+
+def gather_wait(exchange, sites, workspace: Tensor = None) -> None:
+    """The receiving half alone, for call sites whose rows were pushed by the GEMV epilogue (wait=False)."""
+    gather_exchange(exchange, sites, push=False, workspace=workspace)
 
 
 def int4_workspace_bytes(M: int, N: int, K: int, group_size: int, inner_k_tiles: int = 8) -> int:

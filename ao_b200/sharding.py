@@ -55,21 +55,26 @@ class RowShardedLinear(torch.nn.Module):
     full-width output on every rank."""
 
     def __init__(self, shard: torch.nn.Linear, out_features: int, multiple: int, group=None, exchange=None,
-                 slot_offset_bytes: int = 0):
+                 slot_offset_bytes: Optional[int] = None):
         super().__init__()
         self.shard = shard
         self.out_features = out_features
         self.multiple = multiple
         self.group = group
-        # optional fused exchange (ao_b200.comm.PeerExchange): decode batches of an int4 tensor_core_tiled shard
-        # store their outputs straight into every rank's buffer from the kernel's epilogue
+        # optional peer-memory exchange (ao_b200.comm.PeerExchange): decode batches of an int4 tensor_core_tiled shard
+        # write their rows into this rank's block of the gathered output and a small kernel stores them into every
+        # peer's memory and collects the peers' rows (no NCCL call on the decode path).  Every instance uses call
+        # sites of its own (one per batch size): the site at slot_offset_bytes if one is given, else sites reserved
+        # from the exchange on first use (every rank then has to run its layers in the same order the first time).
+        # The returned tensor is a view of the site's output buffer and is overwritten by this layer's next forward.
         self.exchange = exchange
         self.slot_offset_bytes = slot_offset_bytes
+        self._sites = {}
 
     @classmethod
     def from_linear(cls, linear: torch.nn.Linear, multiple: int = 8, group=None,
                     quantize_fn: Optional[Callable[[torch.nn.Module], object]] = None, exchange=None,
-                    slot_offset_bytes: int = 0) -> "RowShardedLinear":
+                    slot_offset_bytes: Optional[int] = None) -> "RowShardedLinear":
         world, rank = dist.get_world_size(group), dist.get_rank(group)
         lo, hi = row_shard_bounds(linear.out_features, world, rank, multiple)
         shard = torch.nn.Linear(linear.in_features, hi - lo, bias=linear.bias is not None, device=linear.weight.device,
@@ -96,9 +101,16 @@ class RowShardedLinear(torch.nn.Module):
         if x2.shape[0] > 8 or packed.shape[0] * 8 != w.shape[0] or x2.stride(1) != 1:
             return None
         from . import ops
-        out = ops.weight_int4pack_mm_gather(x2, packed, int(w.block_size[1]), lt.scale_and_zero, self.exchange,
-                                            self.slot_offset_bytes)            # [world][M][N / world]
-        M = x2.shape[0]
+        M, n_local = x2.shape[0], packed.shape[0] * 8
+        site = self._sites.get(M)
+        if site is None:
+            site = (self.exchange.reserve(M, n_local) if self.slot_offset_bytes is None
+                    else self.exchange.site(self.slot_offset_bytes, M, n_local))
+            self._sites[M] = site
+        # this rank's rows go straight into its block of the gathered output; one small kernel exchanges the blocks
+        ops.weight_int4pack_mm(x2, packed, int(w.block_size[1]), lt.scale_and_zero, out=site.y[self.exchange.rank])
+        ops.gather_exchange(self.exchange, [site], push=True)
+        out = site.y                                                           # [world][M][N / world]
         y = out.reshape(-1) if M == 1 else out.permute(1, 0, 2).reshape(M, -1)
         return y.reshape(*x.shape[:-1], self.out_features)
 

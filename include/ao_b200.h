@@ -186,24 +186,45 @@ int ao_int4_gemv(const void* x_bf16, int64_t x_row_stride, int64_t x_cols, const
                  int inner_k_tiles, void* y_bf16, void* workspace, size_t workspace_bytes,
                  ao_stream_t stream);
 
-/* The GEMV with the output exchange of a row-sharded layer in its epilogue (no counterpart in the reference, which
- * has no multi-GPU path for this operator).  Rank `rank` of `nranks` holds N rows of the weight.  Every CTA sends
- * its finished rows to every peer through peer-mapped memory (NVLink) as 8-byte words {two bf16 rows, call number}
- * - data and arrival in one store, no fence - and collects the same rows of every peer from its own landing area
- * (bounded polling: at most 0.2 s, then AO_ERR_TIMEOUT in the status word); when the kernel completes, y_gathered
- * [nranks][M][N] is complete on this GPU.
- *   peer_landing[r]  rank r's landing area for this call site: nranks * M * N / 2 words of 8 bytes, zero before the
- *                    first call; the entry of `rank` itself is this rank's own area (read here)
- *   y_gathered       this rank's output, bf16 [nranks][M][N], 16-byte aligned
- *   local_state      this rank's unsigned[2] {finished-CTA counter, calls so far}, zero before the first call,
- *                    shared by all call sites of the group
- * Every rank must issue the same sequence of calls with the same shapes.  A landing area / output may be reused
- * once two other exchanges of the group have been issued in between (e.g. one area per layer of a decoder block).
- * Needs K small enough for the activations to fit in shared memory (otherwise AO_ERR_UNSUPPORTED). */
+/* Output all-gather of row-sharded decode linears over peer memory (no counterpart in the reference, which has no
+ * multi-GPU path for this operator).  Rank `rank` of `nranks` holds N rows of each weight and computes y_r [M][N];
+ * every rank ends up with y_gathered [nranks][M][N].  Rows cross NVLink as 8-byte words {two bf16 rows, call number}
+ * - data and arrival in one store, no fence - into a landing area in the receiver's memory.
+ *
+ * ao_gather_exchange: for up to 8 call sites (layers) in one small kernel: with push != 0 it first stores this
+ *   rank's own block of each site's y_gathered (e.g. written there by ao_int4_gemv with y_bf16 = y_gathered +
+ *   rank * M * N) into every peer's landing area; then it polls the words of each site's landing buffer until they
+ *   carry the call's number (bounded: at most 0.2 s, then AO_ERR_TIMEOUT in the status word at workspace[0]) and
+ *   writes the peers' blocks of y_gathered.  When it completes, the gathered outputs are complete on this GPU.
+ * ao_int4_gemv_push: the GEMV whose CTAs send their rows themselves, as they finish, and write this rank's own block
+ *   of y_gathered; it does not wait for the peers.  Follow it with ao_gather_exchange(push = 0).  (A kernel's
+ *   completion waits for the acknowledgement of its NVLink writes - about 2.5 us on an NVSwitch node - so in a chain
+ *   of dependent microsecond kernels one exchange per step is cheaper than a push per layer; the fused push pays
+ *   when other work follows the GEMV that does not need its completion.)
+ * ao_int4_gemv_gather: ao_int4_gemv_push + ao_gather_exchange(push = 0) for one call site.
+ *
+ * Per call site (one per sharded layer and batch size), the same on every rank:
+ *   peer_landing[r]  rank r's landing area of the site: 2 * nranks * M * N / 2 words of 8 bytes (two buffers, used
+ *                    alternately by the parity of the call number), zero before the first call; the entry of `rank`
+ *                    is this rank's own area.  ao_gather_exchange takes nsites * nranks pointers, site-major
+ *   y_gathered       this rank's output, bf16 [nranks][M][N], 16-byte aligned; overwritten by the site's next call
+ *   site_state       this rank's unsigned[4] {pushed CTAs, pushes so far, CTAs done waiting, waits so far}, zero
+ *                    before the first call, 16-byte aligned
+ * Every rank must issue the same sequence of calls with the same shapes, and each push of a site must be followed by
+ * its wait before the site's next push (the wait may come later in the stream, after pushes of other sites).  The
+ * GEMV push needs K small enough for the activations to fit in shared memory (otherwise AO_ERR_UNSUPPORTED).  The
+ * current device must be the stream's device. */
+int ao_gather_exchange(int nsites, void* const* peer_landing, void* const* y_gathered, void* const* state,
+                       const int64_t* M, const int64_t* N, int nranks, int rank, int push, void* workspace,
+                       ao_stream_t stream);
+int ao_int4_gemv_push(const void* x_bf16, int64_t x_row_stride, int64_t x_cols, const int32_t* packed,
+                      const void* scale_and_zero, int64_t M, int64_t N, int64_t K, int group, int inner_k_tiles,
+                      int nranks, int rank, void* const* peer_landing, void* y_gathered, void* site_state,
+                      void* workspace, size_t workspace_bytes, ao_stream_t stream);
 int ao_int4_gemv_gather(const void* x_bf16, int64_t x_row_stride, int64_t x_cols, const int32_t* packed,
                         const void* scale_and_zero, int64_t M, int64_t N, int64_t K, int group,
                         int inner_k_tiles, int nranks, int rank, void* const* peer_landing,
-                        void* y_gathered, void* local_state, void* workspace, size_t workspace_bytes,
+                        void* y_gathered, void* site_state, void* workspace, size_t workspace_bytes,
                         ao_stream_t stream);
 
 /* Set-up helpers for the exchange (CUDA IPC): export the 64-byte handle of the allocation that contains ptr and

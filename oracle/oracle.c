@@ -558,6 +558,16 @@ void orc_int4_linear_dequant_then_matmul(const float* x, const uint8_t* codes, c
     }
 }
 
+/* Thread count of the OpenMP loops above: a launcher may have exported OMP_NUM_THREADS=1 for its child
+ * processes (torch.distributed.run does); the timed CPU baseline sets the count it reports explicitly. */
+void orc_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 int orc_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

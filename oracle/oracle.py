@@ -58,6 +58,18 @@ def num_threads() -> int:
     return int(lib().orc_num_threads())
 
 
+def set_num_threads(n: int) -> int:
+    """Sets the thread count of the OpenMP loops (0 or None: every core this process may run on); returns it."""
+    import os
+    if not n:
+        try:
+            n = len(os.sched_getaffinity(0))
+        except AttributeError:
+            n = os.cpu_count() or 1
+    lib().orc_set_num_threads(int(n))
+    return num_threads()
+
+
 # ----------------------------------------------------------------------------
 # block canonicalisation (quant_primitives.py:95-131)
 # ----------------------------------------------------------------------------

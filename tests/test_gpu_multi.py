@@ -1,6 +1,10 @@
-"""Two-GPU test of the fused output exchange (ao_int4_gemv_gather): every rank's gathered buffer must equal the
-concatenation of all ranks' single-GPU results, over repeated calls.  Skipped unless two GPUs are visible.
-Ranks are child processes; they leave only after a barrier, with nothing in flight."""
+"""Multi-GPU tests of the output exchange over peer memory (ao_int4_gemv_push / ao_gather_exchange): every rank's
+gathered buffer must equal the concatenation of all ranks' single-GPU results, bit for bit, over repeated calls that are
+NOT separated by host barriers: as push + wait per layer, as several GEMV pushes followed by one wait for all of them,
+and as plain GEMVs followed by one exchange kernel that pushes and waits.
+Runs for every world size in {2, 4, 8} that the box has GPUs for; skipped on a single GPU.
+Ranks are child processes; they leave only after a barrier, with nothing in flight.  NVLS is switched off in NCCL
+(the test's collectives are only the reference all-gather and the handle exchange)."""
 import os
 import socket
 
@@ -32,28 +36,55 @@ def _worker(rank, world, port, out_path):
         from ao_b200.comm import PeerExchange
         from tests import gpu_util as tu
         g = 64
-        shapes = [(1, 1024, 4096), (4, 2048, 4096), (1, 14336 // 2, 4096)]
-        slot = 0
+        shapes = [(1, 1024, 4096), (4, 2048, 4096), (1, 14336 // 2, 4096), (8, 512, 2048)]
         exch = PeerExchange(sum(ops.gather_slot_bytes(world, M, N) for M, N, K in shapes))
+        layers = []
         for it, (M, N, K) in enumerate(shapes):
             w = tu.make_weight((N, K), seed=100 * rank + it).to(dev)      # every rank has its own rows
             packed, sz = ops.int4_quantize_pack(w, g, 8)
-            x = torch.randn(M, K, generator=torch.Generator().manual_seed(it)).bfloat16().to(dev)   # replicated
-            y_local = ops.weight_int4pack_mm(x, packed, g, sz)
-            ref = [torch.empty_like(y_local) for _ in range(world)]
-            dist.all_gather(ref, y_local)
-            for rep in range(3):
-                out = ops.weight_int4pack_mm_gather(x, packed, g, sz, exch, slot_offset_bytes=slot)
-                torch.cuda.synchronize()
-                for r in range(world):
-                    if not torch.equal(out[r], ref[r]):
-                        ok, why = False, f"shape {(M, N, K)} rep {rep}: block {r} differs on rank {rank}"
-                dist.barrier()
-            slot += ops.gather_slot_bytes(world, M, N)
+            site = exch.reserve(M, N)
+            xs, refs = [], []
+            for rep in range(3):                                          # different activations per repetition
+                x = torch.randn(M, K, generator=torch.Generator().manual_seed(10 * it + rep)).bfloat16().to(dev)   # replicated
+                y_local = ops.weight_int4pack_mm(x, packed, g, sz)
+                ref = [torch.empty_like(y_local) for _ in range(world)]
+                dist.all_gather(ref, y_local)
+                xs.append(x)
+                refs.append(torch.stack(ref))
+            layers.append((packed, sz, site, xs, refs))
+        torch.cuda.synchronize()
+        dist.barrier()
+        # (1) push + wait per call, repetitions back to back with no host synchronisation in between: a fast rank runs
+        # ahead of a slow one by up to one call per site
+        outs = []
+        for rep in range(3):
+            for packed, sz, site, xs, refs in layers:
+                out = ops.weight_int4pack_mm_gather(xs[rep], packed, g, sz, exch, site=site)
+                outs.append((out.clone(), refs[rep], f"push+wait rep {rep} shape {tuple(refs[rep].shape)}"))
+        # (2) all layers pushed, then one wait for all of them
+        for rep in range(3):
+            for packed, sz, site, xs, refs in layers:
+                ops.weight_int4pack_mm_gather(xs[rep], packed, g, sz, exch, site=site, wait=False)
+            ops.gather_wait(exch, [ly[2] for ly in layers])
+            for packed, sz, site, xs, refs in layers:
+                outs.append((site.y.clone(), refs[rep], f"push..push wait rep {rep} shape {tuple(refs[rep].shape)}"))
+        # (3) plain GEMV into this rank's block, then one exchange kernel that pushes and waits for all layers
+        for rep in range(3):
+            for packed, sz, site, xs, refs in layers:
+                ops.weight_int4pack_mm(xs[rep], packed, g, sz, out=site.y[rank])
+            ops.gather_exchange(exch, [ly[2] for ly in layers], push=True)
+            for packed, sz, site, xs, refs in layers:
+                outs.append((site.y.clone(), refs[rep], f"gemv.. exchange rep {rep} shape {tuple(refs[rep].shape)}"))
+        torch.cuda.synchronize()
+        for out, ref, what in outs:
+            if not torch.equal(out, ref):
+                ok, why = False, f"{what}: gathered output differs on rank {rank}"
+                break
         if _cabi.workspace_status(dev) != 0:
             ok, why = False, "status word set"
+        dist.barrier()
         exch.close()
-    except Exception as e:  # report instead of leaving the other rank waiting
+    except Exception as e:  # report instead of leaving the other ranks waiting
         ok, why = False, f"{type(e).__name__}: {e}"
     torch.save((ok, why), f"{out_path}.{rank}")
     torch.cuda.synchronize()
@@ -64,10 +95,12 @@ def _worker(rank, world, port, out_path):
         pass
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_fused_gather_two_gpus(tmp_path):
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_fused_gather(world, tmp_path):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     import torch.multiprocessing as mp
-    world, port = 2, _free_port()
+    port = _free_port()
     out = str(tmp_path / "res")
     mp.spawn(_worker, args=(world, port, out), nprocs=world, join=True)
     for r in range(world):
