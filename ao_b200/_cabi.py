@@ -63,6 +63,9 @@ PROTOTYPES = {
     "ao_int4_tinygemm_linear_workspace_bytes": (_size, [_i64, _i64, _i64, _int, _int]),
     "ao_int4_tinygemm_linear": (_int, [_ptr, _i64, _i64, _ptr, _ptr, _i64, _i64, _i64, _int, _int, _ptr, _ptr,
                                        _size, _ptr]),
+    "ao_int4_tinygemm_linear_bias": (_int, [_ptr, _i64, _i64, _ptr, _ptr, _i64, _i64, _i64, _int, _int, _ptr, _ptr, _ptr,
+                                            _size, _ptr]),
+    "ao_int4_gemv_bias": (_int, [_ptr, _i64, _i64, _ptr, _ptr, _i64, _i64, _i64, _int, _int, _ptr, _ptr, _ptr, _size, _ptr]),
     "ao_int4_gemv_workspace_bytes": (_size, [_i64, _i64, _i64, _int, _int]),
     "ao_int4_gemv_static_scratch_max_bytes": (_size, []),
     "ao_int4_gemv_static_scratch": (_int, [_ptr, _i64, _i64, _ptr, _ptr, _i64, _i64, _i64, _int, _int, _ptr, _ptr]),

@@ -1,42 +1,34 @@
-"""PyTorch dispatcher registration of the operators (namespace `ao_b200`), the counterpart of the reference's
-TORCH_LIBRARY_FRAGMENT(torchao) + fake implementations (torchao/csrc/fp6_llm.cpp:5-8, torchao/ops.py:6-55):
+"""PyTorch dispatcher operators of this library, in the reference's own namespace:
 
-    torch.ops.ao_b200.quant_llm_linear(EXPONENT, MANTISSA, _in_feats, _weights, _scales, splitK) -> Tensor
-    torch.ops.ao_b200.weight_int4pack_mm(x, w, qGroupSize, qScaleAndZeros) -> Tensor
-    torch.ops.ao_b200.convert_weight_to_int4pack(int_data, innerKTiles) -> Tensor
+    torch.ops.torchao.quant_llm_linear(EXPONENT, MANTISSA, _in_feats, _weights, _scales, splitK) -> Tensor
+    torch.ops.torchao._weight_int4pack_mm(x, w, qGroupSize, qScaleAndZeros) -> Tensor
+    torch.ops.torchao._convert_weight_to_int4pack(int_data, innerKTiles) -> Tensor
 
-CUDA implementations call the C ABI through ao_b200.ops; the fake implementations carry the shape / dtype checks, so
-the ops trace under FakeTensor / torch.compile / export.  Inference only: no autograd formula, like the reference.
+The schemas and CUDA implementations are compiled C++ (ao_b200/csrc/torch/torch_binding.cpp: TORCH_LIBRARY_FRAGMENT /
+TORCH_LIBRARY_IMPL, as torchao/csrc/fp6_llm.cpp:5-8 and torchao/csrc/cuda/fp6_llm/fp6_linear.cu:198-200), built by
+`python -m ao_b200.build --torch` into ao_b200/lib/torch_ext/ao_b200_torch.so.  The fake (meta) implementations are
+registered here in Python with the shape / dtype checks, as the reference does (torchao/ops.py:6-55), so the operators
+trace under FakeTensor, torch.compile and export.  Inference only: no autograd formula, like the reference.
+
+Importing this module without the built extension raises: there is no Python fallback for the operators.
 """
+import ctypes
+import os
+
 import torch
-from torch import Tensor
 
-from . import ops
+from . import _cabi
+from .build import TORCH_EXT_PATH
 
-_lib = torch.library.Library("ao_b200", "DEF")
-_lib.define("quant_llm_linear(int EXPONENT, int MANTISSA, Tensor _in_feats, Tensor _weights, Tensor _scales, int splitK) -> Tensor")
-_lib.define("weight_int4pack_mm(Tensor x, Tensor w, int qGroupSize, Tensor qScaleAndZeros) -> Tensor")
-_lib.define("convert_weight_to_int4pack(Tensor int_data, int innerKTiles) -> Tensor")
-
-
-def _quant_llm_linear_cuda(EXPONENT, MANTISSA, _in_feats, _weights, _scales, splitK):
-    return ops.quant_llm_linear(EXPONENT, MANTISSA, _in_feats, _weights, _scales, splitK)
+if not os.path.exists(TORCH_EXT_PATH):
+    raise ImportError(f"{TORCH_EXT_PATH} is missing: build it with `python -m ao_b200.build --torch`. "
+                      "The torchao:: dispatcher operators have no Python fallback.")
+_cabi.lib()                                                   # fails loudly if libao_b200.so has not been built
+ctypes.CDLL(_cabi.LIB_PATH, mode=ctypes.RTLD_GLOBAL)          # the extension finds libao_b200.so by its soname
+torch.ops.load_library(TORCH_EXT_PATH)
 
 
-def _weight_int4pack_mm_cuda(x, w, qGroupSize, qScaleAndZeros):
-    return ops.weight_int4pack_mm(x, w, qGroupSize, qScaleAndZeros)
-
-
-def _convert_weight_to_int4pack_cuda(int_data, innerKTiles):
-    return ops.convert_weight_to_int4pack(int_data, innerKTiles)
-
-
-_lib.impl("quant_llm_linear", _quant_llm_linear_cuda, "CUDA")
-_lib.impl("weight_int4pack_mm", _weight_int4pack_mm_cuda, "CUDA")
-_lib.impl("convert_weight_to_int4pack", _convert_weight_to_int4pack_cuda, "CUDA")
-
-
-@torch.library.register_fake("ao_b200::quant_llm_linear")
+@torch.library.register_fake("torchao::quant_llm_linear")
 def _(EXPONENT, MANTISSA, _in_feats, _weights, _scales, splitK=1):
     torch._check(_in_feats.dim() == 2, lambda: f"input should be a 2d tensor, got {_in_feats.dim()}D")
     torch._check(_in_feats.dtype is torch.float16, lambda: f"weight must be FP16, got {_in_feats.dtype}")
@@ -52,7 +44,7 @@ def _(EXPONENT, MANTISSA, _in_feats, _weights, _scales, splitK=1):
     return _in_feats.new_empty((BS, OC))
 
 
-@torch.library.register_fake("ao_b200::weight_int4pack_mm")
+@torch.library.register_fake("torchao::_weight_int4pack_mm")
 def _(x, w, qGroupSize, qScaleAndZeros):
     torch._check(x.dim() == 2, lambda: "x must be a 2D tensor")
     torch._check(x.dtype is torch.bfloat16, lambda: f"expected x to be bf16, got {x.dtype}")
@@ -63,7 +55,7 @@ def _(x, w, qGroupSize, qScaleAndZeros):
     return x.new_empty((x.size(0), w.size(0) * 8))
 
 
-@torch.library.register_fake("ao_b200::convert_weight_to_int4pack")
+@torch.library.register_fake("torchao::_convert_weight_to_int4pack")
 def _(int_data, innerKTiles):
     torch._check(int_data.dim() == 2, lambda: "int_data must be 2-D [n][k]")
     torch._check(innerKTiles in (2, 4, 8), lambda: "innerKTiles must be 2, 4, or 8")

@@ -77,10 +77,39 @@ def build(force=False, verbose=False, extra_flags=()):
             sys.stderr.write(out)
     if failed:
         raise RuntimeError("building libao_b200.so failed")
-    link = [nvcc, "-shared", "-o", LIB_PATH] + objs + (["-ccbin", ccbin] if ccbin else []) + ["-lcudart_static", "-ldl", "-lrt", "-lpthread"]
+    link = [nvcc, "-shared", "-o", LIB_PATH] + objs + (["-ccbin", ccbin] if ccbin else []) + [
+        "-Xlinker", "-soname=libao_b200.so", "-lcudart_static", "-ldl", "-lrt", "-lpthread"]
     subprocess.check_call(link, env=env)
     return LIB_PATH
 
 
+TORCH_EXT_DIR = os.path.join(LIB_DIR, "torch_ext")
+TORCH_EXT_PATH = os.path.join(TORCH_EXT_DIR, "ao_b200_torch.so")
+TORCH_EXT_SRC = os.path.join(CSRC, "torch", "torch_binding.cpp")
+
+
+def build_torch_binding(force=False, verbose=False):
+    """Compiles csrc/torch/torch_binding.cpp (the TORCH_LIBRARY registration of torchao::quant_llm_linear,
+    torchao::_weight_int4pack_mm, torchao::_convert_weight_to_int4pack) against the installed torch and links it to
+    libao_b200.so; returns the path of ao_b200/lib/torch_ext/ao_b200_torch.so.  Host C++ only: no GPU needed."""
+    lib_path = build(force=False, verbose=verbose)
+    deps = [TORCH_EXT_SRC, lib_path, os.path.join(HERE, "..", "include", "ao_b200.h")]
+    if not force and os.path.exists(TORCH_EXT_PATH) and all(os.path.getmtime(d) <= os.path.getmtime(TORCH_EXT_PATH) for d in deps[:1] + deps[2:]):
+        return TORCH_EXT_PATH
+    os.makedirs(TORCH_EXT_DIR, exist_ok=True)
+    from torch.utils import cpp_extension
+    cpp_extension.load(
+        name="ao_b200_torch", sources=[TORCH_EXT_SRC], build_directory=TORCH_EXT_DIR, with_cuda=True,
+        extra_cflags=["-O2", "-std=c++17"],
+        # libao_b200.so is found by its soname: ao_b200/_torch_ops.py loads it before this library; the run path is
+        # a second way in for C++ users of the binding
+        extra_ldflags=[f"-L{LIB_DIR}", "-lao_b200", f"-Wl,-rpath,{LIB_DIR}"],
+        is_python_module=False, verbose=verbose)
+    assert os.path.exists(TORCH_EXT_PATH), TORCH_EXT_PATH
+    return TORCH_EXT_PATH
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    if "--torch" in sys.argv:
+        print(build_torch_binding(force="--force" in sys.argv, verbose="--verbose" in sys.argv))

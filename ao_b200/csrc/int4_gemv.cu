@@ -109,6 +109,7 @@ int make_plan(int64_t M, int64_t N, int64_t K, int g, int ikt, Plan* P) {
     P->rows_cta_max = 16 * ((P->NP + G - 1) / G);
     P->ystage_off = (off + 15) / 16 * 16;
     off = P->ystage_off + ((P->M * P->rows_cta_max * 2 + 15) / 16) * 16;
+    P->bias = nullptr;
     P->nranks = 1;
     P->rank = 0;
     P->local_state = nullptr;
@@ -143,11 +144,13 @@ extern "C" size_t ao_int4_gemv_workspace_bytes(int64_t M, int64_t N, int64_t K, 
 
 static int int4_gemv_impl(const void* x_bf16, int64_t x_row_stride, int64_t x_cols, const int32_t* packed,
                          const void* scale_and_zero, int64_t M, int64_t N, int64_t K, int group, int inner_k_tiles,
-                         void* y_bf16, void* workspace, size_t workspace_bytes, ao_stream_t stream) {
+                         void* y_bf16, const void* bias_bf16, void* workspace, size_t workspace_bytes, ao_stream_t stream) {
     if (M == 0 || N == 0) return AO_OK;
     gemv::Plan P;
     int rc = gemv::make_plan(M, N, K, group, inner_k_tiles, &P);
     if (rc) return rc;
+    if (bias_bf16 != nullptr && !aligned(bias_bf16, 2)) return AO_ERR_ALIGN;
+    P.bias = static_cast<const __nv_bfloat16*>(bias_bf16);
     if (x_cols < 2 || x_cols > K || x_cols % 2 != 0 || x_row_stride < x_cols || x_row_stride % 2 != 0) return AO_ERR_SHAPE;
     if (!aligned(x_bf16, 4) || !aligned(packed, 16) || !aligned(scale_and_zero, 16) || !aligned(y_bf16, 2) ||
         !aligned(workspace, 256))
@@ -169,7 +172,16 @@ extern "C" int ao_int4_gemv(const void* x_bf16, int64_t x_row_stride, int64_t x_
                             const void* scale_and_zero, int64_t M, int64_t N, int64_t K, int group, int inner_k_tiles,
                             void* y_bf16, void* workspace, size_t workspace_bytes, ao_stream_t stream) {
     return int4_gemv_impl(x_bf16, x_row_stride, x_cols, packed, scale_and_zero, M, N, K, group, inner_k_tiles, y_bf16,
-                          workspace, workspace_bytes, stream);
+                          nullptr, workspace, workspace_bytes, stream);
+}
+
+// ao_int4_gemv with the bias add of the linear fused into the store (used by ao_int4_tinygemm_linear_bias)
+extern "C" int ao_int4_gemv_bias(const void* x_bf16, int64_t x_row_stride, int64_t x_cols, const int32_t* packed,
+                                 const void* scale_and_zero, int64_t M, int64_t N, int64_t K, int group,
+                                 int inner_k_tiles, void* y_bf16, const void* bias_bf16, void* workspace,
+                                 size_t workspace_bytes, ao_stream_t stream) {
+    return int4_gemv_impl(x_bf16, x_row_stride, x_cols, packed, scale_and_zero, M, N, K, group, inner_k_tiles, y_bf16,
+                          bias_bf16, workspace, workspace_bytes, stream);
 }
 
 // The same kernel with the output exchange of a row-sharded layer in its epilogue: every CTA sends its rows to every

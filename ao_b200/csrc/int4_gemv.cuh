@@ -95,6 +95,7 @@ struct Plan {
     // {two bf16 rows, call number} words.  peer_ll[r]: rank r's landing area of this call site, two buffers
     // [call parity][source rank][M][N/2] of such words; the CTA's own rows also go to y_gathered [rank][M][N];
     // local_state = the call site's {CTAs of this launch that have pushed, pushes so far, ...} on this rank
+    const __nv_bfloat16* bias;   // optional [N]: y = bf16(bf16(acc) + bias), the bits of `y = linear(x, w); y += bias`
     int nranks, rank;
     int ystage_off;     // shared-memory staging of the CTA's output rows [M][16 * pairs per CTA]
     int rows_cta_max;   // 16 * max pairs per CTA
@@ -111,16 +112,24 @@ __device__ __forceinline__ void store_rows(const Plan& P, const float (&v)[NB][4
     const int row = lane >> 2, c = lane & 3;
     const int n_a = 16 * p + row, n_b = n_a + 8;
     const bool has_b = (2 * p + 1) < P.NT;
+    // with a bias: the result rounded to bf16, the bias added, rounded again (what the unfused add produces)
+    const bool biased = P.bias != nullptr;
+    const float b_a = biased ? __bfloat162float(P.bias[n_a]) : 0.f;
+    const float b_b = (biased && has_b) ? __bfloat162float(P.bias[n_b]) : 0.f;
+    auto out = [&](float acc, float b) {
+        const __nv_bfloat16 r = __float2bfloat16_rn(acc);
+        return biased ? __float2bfloat16_rn(__bfloat162float(r) + b) : r;
+    };
 #pragma unroll
     for (int nb = 0; nb < NB; ++nb) {
         const int m0 = nb * 8 + 2 * c;
         if (m0 < P.M) {
-            y[(size_t)m0 * P.N + n_a] = __float2bfloat16_rn(v[nb][0]);
-            if (has_b) y[(size_t)m0 * P.N + n_b] = __float2bfloat16_rn(v[nb][2]);
+            y[(size_t)m0 * P.N + n_a] = out(v[nb][0], b_a);
+            if (has_b) y[(size_t)m0 * P.N + n_b] = out(v[nb][2], b_b);
         }
         if (m0 + 1 < P.M) {
-            y[(size_t)(m0 + 1) * P.N + n_a] = __float2bfloat16_rn(v[nb][1]);
-            if (has_b) y[(size_t)(m0 + 1) * P.N + n_b] = __float2bfloat16_rn(v[nb][3]);
+            y[(size_t)(m0 + 1) * P.N + n_a] = out(v[nb][1], b_a);
+            if (has_b) y[(size_t)(m0 + 1) * P.N + n_b] = out(v[nb][3], b_b);
         }
     }
 }

@@ -6,7 +6,8 @@ namespace ao {
 namespace umma {
 size_t int4_umma_workspace_bytes(int64_t M, int64_t N, int64_t K, int g, int ikt);
 int int4_umma_linear(const void* x, int64_t ldx, int64_t x_cols, const int32_t* packed, const void* sz, int64_t M,
-                     int64_t N, int64_t K, int g, int ikt, void* y, void* ws, size_t ws_bytes, cudaStream_t st);
+                     int64_t N, int64_t K, int g, int ikt, void* y, const void* bias, void* ws, size_t ws_bytes,
+                     cudaStream_t st);
 }
 }  // namespace ao
 
@@ -23,32 +24,46 @@ extern "C" size_t ao_int4_tinygemm_linear_workspace_bytes(int64_t M, int64_t N, 
     return need;
 }
 
-extern "C" int ao_int4_tinygemm_linear(const void* x_bf16, int64_t x_row_stride, int64_t x_cols,
-                                       const int32_t* packed, const void* scale_and_zero, int64_t M, int64_t N,
-                                       int64_t K, int group, int inner_k_tiles, void* y_bf16, void* workspace,
-                                       size_t workspace_bytes, ao_stream_t stream) {
+extern "C" int ao_int4_gemv_bias(const void* x_bf16, int64_t x_row_stride, int64_t x_cols, const int32_t* packed,
+                                 const void* scale_and_zero, int64_t M, int64_t N, int64_t K, int group,
+                                 int inner_k_tiles, void* y_bf16, const void* bias_bf16, void* workspace,
+                                 size_t workspace_bytes, ao_stream_t stream);
+
+extern "C" int ao_int4_tinygemm_linear_bias(const void* x_bf16, int64_t x_row_stride, int64_t x_cols,
+                                            const int32_t* packed, const void* scale_and_zero, int64_t M, int64_t N,
+                                            int64_t K, int group, int inner_k_tiles, void* y_bf16,
+                                            const void* bias_bf16, void* workspace, size_t workspace_bytes,
+                                            ao_stream_t stream) {
     if (M < 0 || N < 0) return AO_ERR_SHAPE;
     if (M <= 8)
-        return ao_int4_gemv(x_bf16, x_row_stride, x_cols, packed, scale_and_zero, M, N, K, group, inner_k_tiles, y_bf16,
-                            workspace, workspace_bytes, stream);
+        return ao_int4_gemv_bias(x_bf16, x_row_stride, x_cols, packed, scale_and_zero, M, N, K, group, inner_k_tiles, y_bf16,
+                                 bias_bf16, workspace, workspace_bytes, stream);
     if (workspace == nullptr || workspace_bytes < 256 || !ao::aligned(workspace, 256)) return AO_ERR_WORKSPACE;
     {
         const int rc = ao::umma::int4_umma_linear(x_bf16, x_row_stride, x_cols, packed, scale_and_zero, M, N, K, group,
-                                                  inner_k_tiles, y_bf16, workspace, workspace_bytes, ao::as_stream(stream));
+                                                  inner_k_tiles, y_bf16, bias_bf16, workspace, workspace_bytes, ao::as_stream(stream));
         if (rc != AO_ERR_UNSUPPORTED) return rc;
     }
     if (M <= 16)
-        return ao_int4_gemv(x_bf16, x_row_stride, x_cols, packed, scale_and_zero, M, N, K, group, inner_k_tiles, y_bf16,
-                            workspace, workspace_bytes, stream);
+        return ao_int4_gemv_bias(x_bf16, x_row_stride, x_cols, packed, scale_and_zero, M, N, K, group, inner_k_tiles, y_bf16,
+                                 bias_bf16, workspace, workspace_bytes, stream);
     // row blocks of 16 through the same kernel, back to back on the stream
     const auto* x = static_cast<const __nv_bfloat16*>(x_bf16);
     auto* y = static_cast<__nv_bfloat16*>(y_bf16);
     for (int64_t m0 = 0; m0 < M; m0 += 16) {
         const int64_t mb = M - m0 < 16 ? M - m0 : 16;
         // every block uses the 16-row plan's workspace layout only if mb == 16; smaller tails need less
-        int rc = ao_int4_gemv(x + m0 * x_row_stride, x_row_stride, x_cols, packed, scale_and_zero, mb, N, K, group,
-                              inner_k_tiles, y + m0 * N, workspace, workspace_bytes, stream);
+        int rc = ao_int4_gemv_bias(x + m0 * x_row_stride, x_row_stride, x_cols, packed, scale_and_zero, mb, N, K, group,
+                                   inner_k_tiles, y + m0 * N, bias_bf16, workspace, workspace_bytes, stream);
         if (rc) return rc;
     }
     return AO_OK;
+}
+
+extern "C" int ao_int4_tinygemm_linear(const void* x_bf16, int64_t x_row_stride, int64_t x_cols,
+                                       const int32_t* packed, const void* scale_and_zero, int64_t M, int64_t N,
+                                       int64_t K, int group, int inner_k_tiles, void* y_bf16, void* workspace,
+                                       size_t workspace_bytes, ao_stream_t stream) {
+    return ao_int4_tinygemm_linear_bias(x_bf16, x_row_stride, x_cols, packed, scale_and_zero, M, N, K, group, inner_k_tiles,
+                                        y_bf16, nullptr, workspace, workspace_bytes, stream);
 }

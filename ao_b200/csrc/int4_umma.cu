@@ -89,7 +89,8 @@ size_t int4_umma_workspace_bytes(int64_t M, int64_t N, int64_t K, int g, int ikt
 
 // AO_ERR_UNSUPPORTED: the caller falls back to row blocks through the GEMV kernel.
 int int4_umma_linear(const void* x, int64_t ldx, int64_t x_cols, const int32_t* packed, const void* sz, int64_t M,
-                     int64_t N, int64_t K, int g, int ikt, void* y, void* ws, size_t ws_bytes, cudaStream_t st) {
+                     int64_t N, int64_t K, int g, int ikt, void* y, const void* bias, void* ws, size_t ws_bytes,
+                     cudaStream_t st) {
     Plan P;
     if (!shape_ok(M, N, K, g, ikt) || !make_plan(M, N, K, &P)) return AO_ERR_UNSUPPORTED;
     if (!aligned(x, 16) || (ldx * 2) % 16 != 0 || x_cols < 1 || x_cols > K || !aligned(packed, 16) || !aligned(sz, 16))
@@ -109,6 +110,7 @@ int int4_umma_linear(const void* x, int64_t ldx, int64_t x_cols, const int32_t* 
     prm.w = packed;
     prm.scale = sz;
     prm.y = y;
+    prm.bias = bias;
     prm.ws = static_cast<uint8_t*>(ws);
     prm.M = (int)M;
     prm.N = (int)N;

@@ -54,6 +54,7 @@ struct alignas(64) Params {
     void* y;
     uint8_t* ws;
     int M, N, K;
+    const void* bias;    // optional [N] in the output dtype: y = round(round(acc) + bias), the bits of an unfused add
 };
 
 template <int MT, class Policy>
@@ -108,6 +109,21 @@ __device__ __forceinline__ void store_out(void* y, size_t idx, float v) {
         static_cast<__nv_bfloat16*>(y)[idx] = __float2bfloat16_rn(v);
     else
         static_cast<__half*>(y)[idx] = __float2half_rn(v);
+}
+
+// the linear's result rounded to the output dtype, then the bias added and rounded again: exactly what
+// `y = linear(x, w); y += bias` produces (affine_quantized_tensor.py:638-640)
+template <bool BF16>
+__device__ __forceinline__ void store_out_bias(void* y, size_t idx, float v, float b) {
+    if constexpr (BF16)
+        static_cast<__nv_bfloat16*>(y)[idx] = __float2bfloat16_rn(__bfloat162float(__float2bfloat16_rn(v)) + b);
+    else
+        static_cast<__half*>(y)[idx] = __float2half_rn(__half2float(__float2half_rn(v)) + b);
+}
+template <bool BF16>
+__device__ __forceinline__ float load_bias(const void* bias, int n) {
+    if constexpr (BF16) return __bfloat162float(static_cast<const __nv_bfloat16*>(bias)[n]);
+    return __half2float(static_cast<const __half*>(bias)[n]);
 }
 
 template <int MT, class Policy>
@@ -244,6 +260,8 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_kernel(const __grid_c
         const int row = q * 32 + lane;              // tensor-memory lane
         const int n = n0 + Policy::out_row(row);    // the weight row it holds
         const float rs = n < N ? Policy::row_scale(p, n) : 0.f;
+        const bool has_bias = p.bias != nullptr;
+        const float bias_n = (has_bias && n < N) ? load_bias<Policy::kBF16>(p.bias, n) : 0.f;
         constexpr int kColsPerWarp = MT / 4;
         const int c_begin = part * kColsPerWarp;
         const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
@@ -260,7 +278,10 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_kernel(const __grid_c
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
                             const int m = m0 + c0 + j;
-                            if (m < M) store_out<Policy::kBF16>(p.y, (size_t)m * N + n, __uint_as_float(v[j]) * rs);
+                            if (m < M) {
+                                if (has_bias) store_out_bias<Policy::kBF16>(p.y, (size_t)m * N + n, __uint_as_float(v[j]) * rs, bias_n);
+                                else store_out<Policy::kBF16>(p.y, (size_t)m * N + n, __uint_as_float(v[j]) * rs);
+                            }
                         }
                     }
                 }
@@ -312,7 +333,10 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_kernel(const __grid_c
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
                             const int m = m0 + c0 + j;
-                            if (m < M) store_out<Policy::kBF16>(p.y, (size_t)m * N + n, acc[j] * rs);
+                            if (m < M) {
+                                if (has_bias) store_out_bias<Policy::kBF16>(p.y, (size_t)m * N + n, acc[j] * rs, bias_n);
+                                else store_out<Policy::kBF16>(p.y, (size_t)m * N + n, acc[j] * rs);
+                            }
                         }
                     }
                 }

@@ -100,7 +100,9 @@ class AffineQuantizedTensor(torch.Tensor):
         self.zero_point_domain = zero_point_domain
 
     def __repr__(self):
-        return (f"{self.__class__.__name__}(data={self.dequantize()}, shape={self.shape}, "
+        inner = getattr(self.layout_tensor, "packed_weight", getattr(self.layout_tensor, "int_data", None))
+        data = self.dequantize() if type(inner) is torch.Tensor else f"<{type(self.layout_tensor).__name__} while tracing>"
+        return (f"{self.__class__.__name__}(data={data}, shape={self.shape}, "
                 f"device={self.device}, dtype={self.dtype}, requires_grad={self.requires_grad})")
 
     def dequantize(self, output_dtype=None):
@@ -303,6 +305,9 @@ class TensorCoreTiledAQTLayout(AQTLayout):
         return self
 
     def __repr__(self):
+        if type(self.packed_weight) is not torch.Tensor:   # fake / functional tensors while tracing: nothing to unpack
+            return (f"TensorCoreTiledAQTLayout(packed_weight={tuple(self.packed_weight.shape)}, "
+                    f"scale_and_zero={tuple(self.scale_and_zero.shape)})")
         int_data, scale, zero_point = self.get_plain()
         return f"TensorCoreTiledAQTLayout(int_data={int_data}, scale={scale}, zero_point={zero_point})"
 
@@ -337,7 +342,7 @@ class _Int4LinearPlan:
     (each of those goes through __torch_function__) and does no argument validation beyond what changes per call."""
 
     __slots__ = ("packed", "sz", "group", "ikt", "N", "K", "n_out", "k_in", "device", "dev_index", "fn", "ws_fn",
-                 "p_packed", "p_sz", "ws_cache", "static_out")
+                 "p_packed", "p_sz", "ws_cache", "static_out", "fn_bias")
 
     def __init__(self, w):
         lt = w.layout_tensor
@@ -352,6 +357,7 @@ class _Int4LinearPlan:
         self.dev_index = self.device.index
         lib = _cabi.lib()
         self.fn = lib.ao_int4_tinygemm_linear
+        self.fn_bias = lib.ao_int4_tinygemm_linear_bias
         self.ws_fn = lib.ao_int4_tinygemm_linear_workspace_bytes
         self.p_packed = self.packed.data_ptr()
         self.p_sz = self.sz.data_ptr()
@@ -373,8 +379,17 @@ class _Int4LinearPlan:
         if M:
             stream = torch._C._cuda_getCurrentRawStream(self.dev_index)
             ws = _cabi.workspace_for(self.ws_cache, self.ws_fn, (M, self.N, self.K, self.group, self.ikt), self.device, stream)
-            rc = self.fn(x2.data_ptr(), x2.stride(0), x2.shape[1], self.p_packed, self.p_sz, M, self.N, self.K, self.group,
-                         self.ikt, y.data_ptr(), ws.data_ptr(), ws.numel(), stream)
+            # the bias add rides in the kernels' stores when it can (same bits as the separate add below)
+            fuse = (bias is not None and self.n_out == self.N and type(bias) in (torch.Tensor, torch.nn.Parameter)
+                    and bias.dtype is torch.bfloat16 and bias.is_contiguous() and bias.device == self.device
+                    and bias.numel() == self.N)
+            if fuse:
+                rc = self.fn_bias(x2.data_ptr(), x2.stride(0), x2.shape[1], self.p_packed, self.p_sz, M, self.N, self.K,
+                                  self.group, self.ikt, y.data_ptr(), bias.data_ptr(), ws.data_ptr(), ws.numel(), stream)
+                bias = None
+            else:
+                rc = self.fn(x2.data_ptr(), x2.stride(0), x2.shape[1], self.p_packed, self.p_sz, M, self.N, self.K,
+                             self.group, self.ikt, y.data_ptr(), ws.data_ptr(), ws.numel(), stream)
             if rc:
                 _cabi.check(rc, "int4 weight-only linear")
         if self.n_out != self.N:
@@ -410,6 +425,12 @@ def use_static_linear_outputs(module: torch.nn.Module, enabled: bool = True, out
                 plan.static_out[int(buf.shape[0])] = buf
 
 
+def _dispatcher_ops():
+    """torch.ops.torchao, with the compiled operator library loaded."""
+    from .. import _torch_ops  # noqa: F401
+    return torch.ops.torchao
+
+
 def _quantized_linear_op(input_tensor, weight_qtensor, bias):
     """Quantized F.linear (:539-671): the int4 tensor_core_tiled branch runs the sm_100a kernels."""
     if isinstance(weight_qtensor, AffineQuantizedTensor):
@@ -429,26 +450,18 @@ def _quantized_linear_op(input_tensor, weight_qtensor, bias):
             orig_dtype = input_tensor.dtype
             act_mat = input_tensor.reshape(-1, input_tensor.shape[-1]).to(torch.bfloat16)
             groupsize = weight_qtensor.block_size[1]
-            if type(weight_qtensor) is AffineQuantizedTensor and "_linear_plan" not in weight_qtensor.__dict__:
+            # (plain tensors only: under FakeTensor propagation or tracing there are no addresses to cache)
+            if (not torch.compiler.is_compiling() and type(weight_qtensor) is AffineQuantizedTensor
+                    and type(packed_weight) is torch.Tensor and type(input_tensor) is torch.Tensor
+                    and "_linear_plan" not in weight_qtensor.__dict__):
                 weight_qtensor.__dict__["_linear_plan"] = _Int4LinearPlan(weight_qtensor)   # later calls skip the checks
-            # the kernel reads the activation's missing (padded) columns as zero
-            y = ops.weight_int4pack_mm(act_mat, packed_weight, groupsize, scale_and_zero)
+            # through the dispatcher (torchao::_weight_int4pack_mm, the twin of the aten operator the reference calls
+            # here, :631), so that a traced graph contains the operator; the kernel reads the activation's missing
+            # (padded) columns as zero
+            y = _dispatcher_ops()._weight_int4pack_mm(act_mat, packed_weight, groupsize, scale_and_zero)
             orig_out_features = weight_qtensor.shape[-2]
             y = y[:, :orig_out_features]
             y = y.reshape(*orig_act_size[:-1], orig_out_features)
-            if bias is not None:
-                y += bias
-            return y.to(orig_dtype)
-        elif (_aqt_is_int8(weight_qtensor) and len(weight_qtensor.shape) == 2 and len(weight_qtensor.block_size) == 2
-              and weight_qtensor.block_size[0] == 1 and weight_qtensor.block_size[1] == weight_qtensor.shape[1]
-              and weight_qtensor.zero_point_domain == ZeroPointDomain.INT
-              and weight_qtensor.extended_layout == "plain"):
-            # per-channel int8 weight only (:646-666)
-            w_vals_int8_t = weight_qtensor.layout_tensor.int_data.t()
-            scale = weight_qtensor.layout_tensor.scale
-            orig_dtype = input_tensor.dtype
-            y = torch.mm(input_tensor.reshape(-1, input_tensor.shape[-1]), w_vals_int8_t.to(input_tensor.dtype)) * scale
-            y = y.reshape(*input_tensor.shape[:-1], y.shape[-1])
             if bias is not None:
                 y += bias
             return y.to(orig_dtype)
@@ -468,7 +481,9 @@ def _dense_route(func, input_tensor, weight_tensor, *rest):
 def functional_linear(*args, **kwargs):
     input_tensor, weight_tensor, bias = args[0], args[1], args[2] if len(args) > 2 else kwargs.get("bias")
     # decode fast path: plain bf16 CUDA activation on an int4 tensor_core_tiled weight whose plan is cached
-    plan = weight_tensor.__dict__.get("_linear_plan") if type(weight_tensor) is AffineQuantizedTensor else None
+    plan = None
+    if not torch.compiler.is_compiling() and type(weight_tensor) is AffineQuantizedTensor:
+        plan = weight_tensor.__dict__.get("_linear_plan")
     if plan is not None and type(input_tensor) is torch.Tensor and input_tensor.dtype is torch.bfloat16 and \
             input_tensor.device == plan.device:
         return plan(input_tensor, bias)

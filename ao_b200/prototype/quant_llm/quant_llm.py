@@ -159,7 +159,7 @@ class QuantLlmLinearWeight(Tensor):
 def _(*args, **kwargs):
     """quant_llm.py:419-445.  The reference looks splitK up in a per-shape table; the kernel here chooses
     its own K split, so the argument passed on is only a placeholder."""
-    from ...ops import quant_llm_linear
+    from ... import _torch_ops  # noqa: F401  (torch.ops.torchao.quant_llm_linear: the operator a traced graph shows)
 
     act = args[0]
     weight = args[1]
@@ -167,7 +167,7 @@ def _(*args, **kwargs):
     assert isinstance(weight, QuantLlmLinearWeight)
     out_dim, in_dim = weight.shape
     act_reshaped = act.reshape(-1, in_dim).half()
-    out = quant_llm_linear(weight.ebits, weight.mbits, act_reshaped, weight.fpx_data, weight.scale, splitK=1)
+    out = torch.ops.torchao.quant_llm_linear(weight.ebits, weight.mbits, act_reshaped, weight.fpx_data, weight.scale, 1)
     if bias is not None:
         out += bias
     return out.view(*act.shape[:-1], out_dim).to(act.dtype)

@@ -1,7 +1,7 @@
 """Model-level quantization API — torchao/quantization/quant_api.py:146-191, 255-318, 362-404.
 
 quantize(model, apply_tensor_subclass, filter_fn=None, set_inductor_config=True) walks the modules and swaps
-nn.Linear weights for tensor-subclass instances; int4_weight_only / int8_weight_only / fp6_llm_weight_only
+nn.Linear weights for tensor-subclass instances; int4_weight_only / fp6_llm_weight_only
 build the conversion functions.  `quantize_` is the spelling of later torchao releases for the same call.
 """
 from typing import Callable, Optional
@@ -14,7 +14,6 @@ __all__ = [
     "quantize",
     "quantize_",
     "int4_weight_only",
-    "int8_weight_only",
     "fp6_llm_weight_only",
     "quant_llm_fpx_weight_only",
 ]
@@ -80,17 +79,6 @@ def int4_weight_only(group_size=128, inner_k_tiles=8):
                                    inner_k_tiles=inner_k_tiles)
 
     return apply_int4_weight_only_quant
-
-
-def int8_weight_only():
-    """int8 weight-only symmetric per-channel quantization (torchao/quantization/quant_api.py:388-403)."""
-    def apply_int8wo_quant(weight):
-        from ..dtypes import to_affine_quantized
-
-        return to_affine_quantized(weight, MappingType.SYMMETRIC, (1, weight.shape[1]), torch.int8,
-                                   eps=torch.finfo(torch.float32).eps, zero_point_dtype=torch.int64)
-
-    return apply_int8wo_quant
 
 
 def quant_llm_fpx_weight_only(ebits: int, mbits: int):

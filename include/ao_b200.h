@@ -179,6 +179,18 @@ int ao_int4_tinygemm_linear(const void* x_bf16, int64_t x_row_stride, int64_t x_
                             int64_t K, int group, int inner_k_tiles, void* y_bf16, void* workspace,
                             size_t workspace_bytes, ao_stream_t stream);
 
+/* The same with the bias add of the linear fused into the kernels' stores (affine_quantized_tensor.py:638-640 adds it
+ * as a separate pass).  bias_bf16: bf16 [N] or NULL.  The result has the bits of the unfused sequence: the linear's
+ * output rounded to bf16, the bias added in fp32, rounded to bf16 again. */
+int ao_int4_tinygemm_linear_bias(const void* x_bf16, int64_t x_row_stride, int64_t x_cols,
+                                 const int32_t* packed, const void* scale_and_zero, int64_t M, int64_t N,
+                                 int64_t K, int group, int inner_k_tiles, void* y_bf16, const void* bias_bf16,
+                                 void* workspace, size_t workspace_bytes, ao_stream_t stream);
+int ao_int4_gemv_bias(const void* x_bf16, int64_t x_row_stride, int64_t x_cols, const int32_t* packed,
+                      const void* scale_and_zero, int64_t M, int64_t N, int64_t K, int group, int inner_k_tiles,
+                      void* y_bf16, const void* bias_bf16, void* workspace, size_t workspace_bytes,
+                      ao_stream_t stream);
+
 /* The GEMV kernel alone (1 <= M <= 16), same arguments and workspace rules. */
 size_t ao_int4_gemv_workspace_bytes(int64_t M, int64_t N, int64_t K, int group, int inner_k_tiles);
 int ao_int4_gemv(const void* x_bf16, int64_t x_row_stride, int64_t x_cols, const int32_t* packed,

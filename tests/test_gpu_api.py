@@ -120,14 +120,25 @@ def test_state_dict_roundtrip_and_flatten():
     assert isinstance(sd["0.weight"], AffineQuantizedTensor)
 
 
-def test_int8_weight_only_route():
-    from ao_b200.quantization import int8_weight_only, quantize
-    torch.manual_seed(3)
-    lin = torch.nn.Linear(256, 128, device="cuda", dtype=torch.bfloat16)
-    ref = copy.deepcopy(lin)
-    quantize(lin, int8_weight_only())
-    x = torch.randn(8, 256, device="cuda", dtype=torch.bfloat16)
-    assert _sqnr(ref(x), lin(x)) >= 30
+def test_bias_is_fused_with_the_bits_of_the_separate_add():
+    """F.linear with a bias on an int4 tensor_core_tiled weight: the kernels add the bias in their stores, and the
+    result has the bits of `y = linear(x, w); y += bias` (affine_quantized_tensor.py:638-640) for the decode kernel,
+    the tcgen05 kernel and the 16-row block route."""
+    from ao_b200 import ops
+    from ao_b200.quantization import int4_weight_only, quantize
+    torch.manual_seed(5)
+    lin = torch.nn.Linear(2048, 512, bias=True, device="cuda", dtype=torch.bfloat16)
+    with torch.no_grad():
+        lin.bias.mul_(3.0)
+    quantize(lin, int4_weight_only(group_size=64))
+    lt = lin.weight.layout_tensor
+    for M in (1, 5, 8, 16, 64, 300):
+        x = torch.randn(M, 2048, device="cuda", dtype=torch.bfloat16)
+        lin(x)                                   # first call builds the plan
+        y = lin(x)                               # fast path: fused bias
+        ref = ops.weight_int4pack_mm(x, lt.packed_weight, 64, lt.scale_and_zero)
+        ref += lin.bias
+        assert torch.equal(y, ref), f"M={M}"
 
 
 def test_filter_fn_and_transpose():
@@ -153,19 +164,25 @@ def test_clone_makes_independent_storage():
 
 
 def test_dispatcher_ops_opcheck():
-    """torch.ops.ao_b200.*: schema, fake-tensor and dispatch checks (test/test_ops.py:24-45 of the reference)."""
-    import ao_b200._torch_ops  # noqa: F401
+    """torch.ops.torchao.*: the four checks the reference runs on its operator (test/test_ops.py:24-45) - schema,
+    autograd registration, fake tensor, AOT dispatch with dynamic shapes - and equality with the direct calls."""
+    import torchao  # noqa: F401
     from ao_b200 import ops
     from torch.library import opcheck
-    utils = ["test_schema", "test_autograd_registration", "test_faketensor"]
+    utils = ["test_schema", "test_autograd_registration", "test_faketensor", "test_aot_dispatch_dynamic"]
     w = torch.randint(256, (256, 512 // 8 * 6), dtype=torch.uint8, device="cuda")
     s = torch.rand(256, dtype=torch.float16, device="cuda") + 0.5
     x = torch.rand(5, 512, dtype=torch.float16, device="cuda") + 0.5
-    opcheck(torch.ops.ao_b200.quant_llm_linear, (3, 2, x, w, s, 1), test_utils=utils)
-    assert torch.equal(torch.ops.ao_b200.quant_llm_linear(3, 2, x, w, s, 1), ops.quant_llm_linear(3, 2, x, w, s, 1))
+    opcheck(torch.ops.torchao.quant_llm_linear, (3, 2, x, w, s, 1), test_utils=utils)
+    assert torch.equal(torch.ops.torchao.quant_llm_linear(3, 2, x, w, s, 1), ops.quant_llm_linear(3, 2, x, w, s, 1))
+    assert torch.equal(torchao.ops.quant_llm_linear(3, 2, x, w, s, 1), ops.quant_llm_linear(3, 2, x, w, s, 1))
     codes = torch.randint(0, 16, (64, 1024), dtype=torch.int32, device="cuda")
-    opcheck(torch.ops.ao_b200.convert_weight_to_int4pack, (codes, 8), test_utils=utils)
-    packed = torch.ops.ao_b200.convert_weight_to_int4pack(codes, 8)
+    opcheck(torch.ops.torchao._convert_weight_to_int4pack, (codes, 8), test_utils=utils)
+    packed = torch.ops.torchao._convert_weight_to_int4pack(codes, 8)
+    assert torch.equal(packed, ops.convert_weight_to_int4pack(codes, 8))
     sz = torch.rand(1024 // 64, 64, 2, device="cuda").bfloat16()
     xb = torch.randn(3, 1024, device="cuda").bfloat16()
-    opcheck(torch.ops.ao_b200.weight_int4pack_mm, (xb, packed, 64, sz), test_utils=utils)
+    opcheck(torch.ops.torchao._weight_int4pack_mm, (xb, packed, 64, sz), test_utils=utils)
+    assert torch.equal(torch.ops.torchao._weight_int4pack_mm(xb, packed, 64, sz), ops.weight_int4pack_mm(xb, packed, 64, sz))
+    with pytest.raises(RuntimeError, match="is not supported"):
+        torch.ops.torchao.quant_llm_linear(2, 1, x, torch.zeros(256, 256, dtype=torch.uint8, device="cuda"), s, 1)
