@@ -11,6 +11,10 @@
 //   warps 3-18 dequantise raw bytes in registers and write the 16-bit operand tile (layout chosen by the weight
 //              format's policy), in groups that take alternate iterations whole; after the K loop the same warps
 //              read the accumulator from tensor memory and store y.
+// With several token tiles (M > 256, when it saves waves of CTAs: make_plan) a CTA keeps TWO accumulators in tensor memory (2 x 256 columns, all of it) and
+// issues the MMAs of two adjacent token tiles against every dequantised operand stage: the dequantisation work per
+// MMA halves (it, not the tensor pipe, sets the pace of the one-tile form), at the same shared-memory footprint -
+// the x ring simply turns over twice per operand stage.
 // When the tiles alone would leave SMs idle, K is cut into slabs over gridDim.z; fp32 partial tiles meet in the
 // workspace and the CTA that completes a tile (atomic counter) adds them in slab order (deterministic).
 // Every wait is bounded; a wait that runs out sets the status word and the CTA still frees its tensor memory.
@@ -57,7 +61,7 @@ struct alignas(64) Params {
     const void* bias;    // optional [N] in the output dtype: y = round(round(acc) + bias), the bits of an unfused add
 };
 
-template <int MT, class Policy>
+template <int MT, class Policy, int TT = 1>
 struct Cfg {
     static constexpr int XBytes = MT * kKB * 2;
     // activation stages: the ring has to cover the TMA latency, so small tiles get more of them (a power of two)
@@ -75,20 +79,31 @@ struct Cfg {
     static constexpr int Rfit = (kSmemLimit - Fixed) / Policy::kRawBytes;
     static constexpr int R = Rfit > 8 ? 8 : Rfit;         // raw stages (each covers 128 k; the ring covers the copy latency)
     static_assert(R >= 2, "raw ring needs two stages");
-    static constexpr int TmemCols = MT < 32 ? 32 : MT;
+    static constexpr int TmemCols = MT * TT < 32 ? 32 : MT * TT;   // TT token tiles of MT columns each
+    static_assert(TmemCols <= 512, "tensor memory has 512 columns");
     static constexpr int SmemBytes = Fixed + R * Policy::kRawBytes;
 };
 
 // work split of one call
 struct Plan {
-    int MT, nsplit, row_tiles, m_tiles;
+    int MT, TT, nsplit, row_tiles, m_tiles;   // m_tiles: CTAs along M, each covering TT token tiles of MT rows
     size_t ws_bytes;
 };
 
 inline bool make_plan(int64_t M, int64_t N, int64_t K, Plan* P) {
     P->MT = M > 128 ? 256 : (M > 64 ? 128 : (M > 32 ? 64 : 32));
     P->row_tiles = (int)((N + kRows - 1) / kRows);
-    P->m_tiles = (int)((M + P->MT - 1) / P->MT);
+    // Two token tiles per CTA when that shortens the launch: a CTA with two tiles runs about 1.6 times as long as
+    // one with a single tile (measured at K = 8192: it is bound by the tensor pipe, the single-tile CTA by the
+    // dequantisation), and the grid runs in whole waves of one CTA per SM.
+    P->TT = 1;
+    if (P->MT == 256 && M > 256) {
+        const long long mt1 = (M + 255) / 256;
+        const long long waves1 = (P->row_tiles * mt1 + kNumSMs - 1) / kNumSMs;
+        const long long waves2 = (P->row_tiles * ((mt1 + 1) / 2) + kNumSMs - 1) / kNumSMs;
+        if (waves2 * 16 < waves1 * 10) P->TT = 2;
+    }
+    P->m_tiles = (int)((M + P->MT * P->TT - 1) / (P->MT * P->TT));
     const long long tiles = (long long)P->row_tiles * P->m_tiles;
     if (tiles > kMaxTiles) return false;
     // K slabs over gridDim.z when the tiles alone leave SMs idle; every slab keeps at least 8 iterations of 128 k
@@ -98,6 +113,7 @@ inline bool make_plan(int64_t M, int64_t N, int64_t K, Plan* P) {
     if (P->MT == 256 && nsplit > 2) nsplit = 2;
     while (nsplit > 1 && nit / nsplit < 8) --nsplit;
     if (nsplit < 1) nsplit = 1;
+    if (P->TT > 1) nsplit = 1;   // (that many tiles fill the machine by themselves)
     P->nsplit = nsplit;
     P->ws_bytes = kHeaderBytes + (size_t)kMaxTiles * 4 + (nsplit > 1 ? (size_t)tiles * nsplit * kRows * P->MT * 4 : 0);
     return true;
@@ -126,9 +142,9 @@ __device__ __forceinline__ float load_bias(const void* bias, int n) {
     return __half2float(static_cast<const __half*>(bias)[n]);
 }
 
-template <int MT, class Policy>
+template <int MT, class Policy, int TT>
 __global__ void __launch_bounds__(kThreads, 1) umma_linear_kernel(const __grid_constant__ Params p) {
-    using C = Cfg<MT, Policy>;
+    using C = Cfg<MT, Policy, TT>;
     constexpr int R = C::R;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = ptx::smem_addr(smem_raw);
@@ -142,7 +158,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_kernel(const __grid_c
     const uint32_t tmem_slot = acc_full + 8, flag_slot = tmem_slot + 4;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int M = p.M, N = p.N;
-    const int n0 = blockIdx.x * kRows, m0 = blockIdx.y * MT;
+    const int n0 = blockIdx.x * kRows, m0 = blockIdx.y * (MT * TT);   // first row of the CTA's first token tile
     const int nsplit = gridDim.z, z = blockIdx.z;
     const int nit_all = p.K / kRawK;
     const int it_begin = (int)(((long long)z * nit_all) / nsplit), it_end = (int)(((long long)(z + 1) * nit_all) / nsplit);
@@ -195,14 +211,15 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_kernel(const __grid_c
     } else if (warp == 1) {
         // ---------------- activations: one operand stage per 64 k ----------------
         if (lane == 0) {
-            for (int kb = 0; kb < 2 * nit; ++kb) {
-                const int s = kb & (SX - 1);
-                if (!ptx::mbar_wait_bounded(x_empty + 8 * s, (static_cast<uint32_t>(kb >> C::SXShift) & 1u) ^ 1u, kWaitPolls)) {
+            // x stage number xi = kb * TT + t: token tile t of k block kb (a tile beyond M reads as zeros)
+            for (int xi = 0; xi < 2 * nit * TT; ++xi) {
+                const int s = xi & (SX - 1), kb = xi / TT, t = xi % TT;
+                if (!ptx::mbar_wait_bounded(x_empty + 8 * s, (static_cast<uint32_t>(xi >> C::SXShift) & 1u) ^ 1u, kWaitPolls)) {
                     ok = false;
                     break;
                 }
                 ptx::mbar_arrive_expect_tx(full_x + 8 * s, C::XBytes);
-                ptx::tma_load_2d(x_base + s * C::XBytes, &p.map_x, (2 * it_begin + kb) * kKB, m0, full_x + 8 * s);
+                ptx::tma_load_2d(x_base + s * C::XBytes, &p.map_x, (2 * it_begin + kb) * kKB, m0 + t * MT, full_x + 8 * s);
             }
         }
     } else if (warp == 2) {
@@ -210,23 +227,31 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_kernel(const __grid_c
         if (lane == 0) {
             constexpr uint32_t idesc = ptx::umma_idesc(kRows, MT, Policy::kBF16, Policy::kAMajorMN);
             constexpr uint32_t a_step = Policy::kAMajorMN ? (2048 >> 4) : (32 >> 4);   // descriptor units per k16
-            for (int kb = 0; kb < 2 * nit; ++kb) {
-                const int s = kb & (kS - 1), sx = kb & (SX - 1);
+            for (int kb = 0; kb < 2 * nit && ok; ++kb) {
+                const int s = kb & (kS - 1);
                 const uint32_t ph = static_cast<uint32_t>(kb >> C::SAShift) & 1u;
-                if (!ptx::mbar_wait_bounded(full_a + 8 * s, ph, kWaitPolls) ||
-                    !ptx::mbar_wait_bounded(full_x + 8 * sx, static_cast<uint32_t>(kb >> C::SXShift) & 1u, kWaitPolls)) {
+                if (!ptx::mbar_wait_bounded(full_a + 8 * s, ph, kWaitPolls)) {
                     ok = false;
                     break;
                 }
-                ptx::tcgen05_fence_after_thread_sync();
                 const uint64_t da = Policy::kAMajorMN ? ptx::umma_desc_mn_sw128(a_base + s * kABytes)
                                                       : ptx::umma_desc_k_sw128(a_base + s * kABytes);
-                const uint64_t db = ptx::umma_desc_k_sw128(x_base + sx * C::XBytes);
 #pragma unroll
-                for (int k4 = 0; k4 < kKB / 16; ++k4)
-                    ptx::umma_f16_ss(tmem_base, da + a_step * k4, db + 2 * k4, idesc, (kb | k4) != 0 ? 1u : 0u);
-                ptx::umma_commit(empty + 8 * s);
-                ptx::umma_commit(x_empty + 8 * sx);
+                for (int t = 0; t < TT; ++t) {
+                    // token tile t: its x stage against the same operand stage, into its own accumulator columns
+                    const int xi = kb * TT + t, sx = xi & (SX - 1);
+                    if (!ptx::mbar_wait_bounded(full_x + 8 * sx, static_cast<uint32_t>(xi >> C::SXShift) & 1u, kWaitPolls)) {
+                        ok = false;
+                        break;
+                    }
+                    ptx::tcgen05_fence_after_thread_sync();
+                    const uint64_t db = ptx::umma_desc_k_sw128(x_base + sx * C::XBytes);
+#pragma unroll
+                    for (int k4 = 0; k4 < kKB / 16; ++k4)
+                        ptx::umma_f16_ss(tmem_base + t * MT, da + a_step * k4, db + 2 * k4, idesc, (kb | k4) != 0 ? 1u : 0u);
+                    ptx::umma_commit(x_empty + 8 * sx);
+                }
+                if (ok) ptx::umma_commit(empty + 8 * s);
             }
             if (ok) ptx::umma_commit(acc_full);
         }
@@ -269,15 +294,18 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_kernel(const __grid_c
             if (ok) {
                 ptx::tcgen05_fence_after_thread_sync();
 #pragma unroll 1
-                for (int c0 = c_begin; c0 < c_begin + kColsPerWarp; c0 += 8) {
-                    if (m0 + c0 >= M) break;   // uniform across the warp
+                for (int cc = 0; cc < TT * kColsPerWarp; cc += 8) {
+                    // column cc of this warp's share: token tile cc / kColsPerWarp, column c0 inside the tile
+                    const int t = cc / kColsPerWarp, c0 = c_begin + (cc - t * kColsPerWarp);
+                    const int mt = m0 + t * MT;
+                    if (mt + c0 >= M) continue;   // uniform across the warp
                     uint32_t v[8];
-                    ptx::tmem_ld_32x32b_x8(t_lane + c0, v);
+                    ptx::tmem_ld_32x32b_x8(t_lane + t * MT + c0, v);
                     ptx::tmem_ld_wait();
                     if (n < N) {
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
-                            const int m = m0 + c0 + j;
+                            const int m = mt + c0 + j;
                             if (m < M) {
                                 if (has_bias) store_out_bias<Policy::kBF16>(p.y, (size_t)m * N + n, __uint_as_float(v[j]) * rs, bias_n);
                                 else store_out<Policy::kBF16>(p.y, (size_t)m * N + n, __uint_as_float(v[j]) * rs);
@@ -352,13 +380,13 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_kernel(const __grid_c
     }
 }
 
-template <int MT, class Policy>
+template <int MT, class Policy, int TT = 1>
 int launch(const Plan& P, const Params& prm, cudaStream_t st) {
-    auto kern = umma_linear_kernel<MT, Policy>;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<MT, Policy>::SmemBytes) != cudaSuccess)
+    auto kern = umma_linear_kernel<MT, Policy, TT>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<MT, Policy, TT>::SmemBytes) != cudaSuccess)
         return AO_ERR_LAUNCH;
     dim3 grid(P.row_tiles, P.m_tiles, P.nsplit);
-    kern<<<grid, kThreads, Cfg<MT, Policy>::SmemBytes, st>>>(prm);
+    kern<<<grid, kThreads, Cfg<MT, Policy, TT>::SmemBytes, st>>>(prm);
     return launch_status();
 }
 
@@ -368,7 +396,7 @@ int launch_mt(const Plan& P, const Params& prm, cudaStream_t st) {
         case 32: return launch<32, Policy>(P, prm, st);
         case 64: return launch<64, Policy>(P, prm, st);
         case 128: return launch<128, Policy>(P, prm, st);
-        default: return launch<256, Policy>(P, prm, st);
+        default: return P.TT == 2 ? launch<256, Policy, 2>(P, prm, st) : launch<256, Policy>(P, prm, st);
     }
 }
 

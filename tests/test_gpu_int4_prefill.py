@@ -44,6 +44,27 @@ def test_prefill_vs_oracle(N, K, g):
     assert _cabi.workspace_status("cuda") == 0
 
 
+@pytest.mark.parametrize("g", [32, 64, 128, 256])
+@pytest.mark.parametrize("M", [1700, 2048, 2304])
+def test_prefill_two_token_tiles_per_block(M, g):
+    """With many token tiles each thread block multiplies one dequantised weight stage into two token tiles (two
+    accumulators in tensor memory).  With 9472 weight rows that form is the one chosen at these M (it needs fewer
+    waves of blocks); M = 1700 leaves the last block one ragged tile and one tile entirely past the end, M = 2304
+    an odd number of token tiles.  The result must also equal,
+    bit for bit, the rows computed 256 at a time (the one-tile form accumulates in the same order)."""
+    from ao_b200 import _cabi, ops
+    N, K = 9472, 512
+    packed, sz, wd = _quantized(N, K, g, seed=M + g)
+    x = torch.randn(M, K, generator=torch.Generator().manual_seed(M)).bfloat16()
+    y = ops.weight_int4pack_mm(x.cuda(), packed, g, sz)
+    assert y.shape == (M, N)
+    _check(y, np.ascontiguousarray(x.float().numpy()) @ wd.T, f"M={M}")
+    y256 = torch.cat([ops.weight_int4pack_mm(x[i:i + 256].cuda(), packed, g, sz) for i in range(0, M, 256)])
+    assert torch.equal(y, y256)
+    assert torch.equal(y, ops.weight_int4pack_mm(x.cuda(), packed, g, sz)), "two runs must give identical bits"
+    assert _cabi.workspace_status("cuda") == 0
+
+
 def test_prefill_matches_decode_kernel_rows():
     """The same activation rows through the decode kernel (16 at a time) and through the prefill kernel."""
     from ao_b200 import ops
