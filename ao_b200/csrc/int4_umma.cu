@@ -125,3 +125,10 @@ int int4_umma_linear(const void* x, int64_t ldx, int64_t x_cols, const int32_t* 
 
 }  // namespace umma
 }  // namespace ao
+
+#if defined(AO_UMMA_TRACE) && AO_UMMA_TRACE
+// trace builds: copy the timeline of this translation unit's kernels out (512 slots)
+extern "C" int ao_debug_read_umma_trace(unsigned long long* host_out) {
+    return (int)cudaMemcpyFromSymbol(host_out, ao::umma::g_utrace, sizeof(unsigned long long) * 512);
+}
+#endif

@@ -10,11 +10,20 @@
 //              commit that frees the stage;
 //   warps 3-18 dequantise raw bytes in registers and write the 16-bit operand tile (layout chosen by the weight
 //              format's policy), in groups that take alternate iterations whole; after the K loop the same warps
-//              read the accumulator from tensor memory and store y.
-// With several token tiles (M > 256, when it saves waves of CTAs: make_plan) a CTA keeps TWO accumulators in tensor memory (2 x 256 columns, all of it) and
-// issues the MMAs of two adjacent token tiles against every dequantised operand stage: the dequantisation work per
-// MMA halves (it, not the tensor pipe, sets the pace of the one-tile form), at the same shared-memory footprint -
-// the x ring simply turns over twice per operand stage.
+//              read the accumulator from tensor memory and store y;
+//   warp 19    is a second MMA-issuing warp for token tiles of up to 128 columns.
+// Measured on B200: a 128 x N x 16 MMA occupies the tensor pipe for max(N / 2, 45) cycles (64 x N x 16 takes the
+// same time), and the issuing thread's two waits and two commits per operand stage cost it about as long as four
+// such MMAs at N = 256.  Hence three forms of the K loop:
+//   * MT <= 128: two issuing threads take turns, each accumulating into its own tensor-memory columns (the order of
+//     additions stays fixed; the epilogue adds the two).  At MT = 32 the hand-over is per iteration of 128 k instead
+//     of per operand stage: one activation stage holds both 64-k tiles, the two operand stages share one full and
+//     one empty barrier, eight MMAs per pair of waits and pair of commits.
+//   * MT = 256, one token tile: one issuing thread, one accumulator.
+//   * several token tiles (M > 256, when it saves waves of CTAs: make_plan): the CTA keeps TWO accumulators of 256
+//     columns (all of tensor memory) and issues the MMAs of two adjacent token tiles against every dequantised
+//     operand stage: the dequantisation work per MMA halves (it, not the tensor pipe, sets the pace of the one-tile
+//     form), at the same shared-memory footprint - the x ring simply turns over twice per operand stage.
 // When the tiles alone would leave SMs idle, K is cut into slabs over gridDim.z; fp32 partial tiles meet in the
 // workspace and the CTA that completes a tile (atomic counter) adds them in slab order (deterministic).
 // Every wait is bounded; a wait that runs out sets the status word and the CTA still frees its tensor memory.
@@ -36,12 +45,25 @@
 namespace ao {
 namespace umma {
 
+// Device-side timeline (a build with -DAO_UMMA_TRACE=1 only): globaltimer stamps of the first CTA's roles, read back
+// by ao_debug_read_umma_trace.  Slots: 16 g + 2 i (+1): dequant group g < 4, its i-th iteration, waits passed
+// (dequantised and signalled); 64 + kb: the MMA thread has operand stage kb; 96 + kb: its MMAs are issued;
+// 128 + it: raw stage it issued; 160: CTA start; 161: accumulator complete; 162: epilogue done; 256 + kb: the MMA
+// thread has the activation stage; 288 + kb: MMAs issued, before the commits.
+#if defined(AO_UMMA_TRACE) && AO_UMMA_TRACE
+static __device__ unsigned long long g_utrace[512];
+#define AO_UTR(cond, slot) do { if ((cond) && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (slot) < 512) g_utrace[(slot)] = ptx::globaltimer_ns(); } while (0)
+#else
+#define AO_UTR(cond, slot) do { } while (0)
+#endif
+
 constexpr int kRows = 128;            // weight rows per CTA
 constexpr int kKB = 64;               // k per operand stage (one 128-byte swizzle atom of 16-bit elements)
 constexpr int kRawK = 128;            // k per raw stage / dequant iteration
 constexpr int kABytes = kRows * kKB * 2;       // 16 KiB
 constexpr int kDequantWarps = 16;
-constexpr int kThreads = (3 + kDequantWarps) * 32;
+constexpr int kMmaWarp2 = 3 + kDequantWarps;   // second MMA-issuing warp (the first is warp 2)
+constexpr int kThreads = (4 + kDequantWarps) * 32;
 constexpr int kWaitPolls = 2000;
 constexpr int kHeaderBytes = 256;
 constexpr int kMaxTiles = 16384;      // completion counters (same workspace region as the decode kernels')
@@ -61,25 +83,42 @@ struct alignas(64) Params {
     const void* bias;    // optional [N] in the output dtype: y = round(round(acc) + bias), the bits of an unfused add
 };
 
+#ifndef AO_UMMA_NG_SMALL
+#define AO_UMMA_NG_SMALL 4
+#endif
+
 template <int MT, class Policy, int TT = 1>
 struct Cfg {
     static constexpr int XBytes = MT * kKB * 2;
-    // activation stages: the ring has to cover the TMA latency, so small tiles get more of them (a power of two)
-    static constexpr int SX = MT <= 32 ? 8 : 4;
-    static constexpr int SXShift = MT <= 32 ? 3 : 2;
-    // operand stages: with small token tiles the MMAs are short and the ring has to cover the latency from the last
-    // dequantised byte to the commit that frees the stage
+    // The narrowest token tiles (MT = 32): an MMA is short (45 cycles), so the waits and commits its issuing
+    // thread executes around it decide the pace.  There everything is handed over per ITERATION of 128 k
+    // instead of per operand stage of 64 k: one activation stage holds both 64-k tiles (two TMA copies on one
+    // barrier), the two operand stages of an iteration share one full / one empty barrier, and the issuing thread
+    // runs eight MMAs per pair of waits and pair of commits.
+    static constexpr bool kIter = MT <= 32 && TT == 1;
+    static constexpr int XStage = kIter ? 2 * XBytes : XBytes;
+    // activation stages (a power of two): the ring has to cover the TMA latency
+    static constexpr int SX = 4;
+    static constexpr int SXShift = 2;
+    // dequant warp groups: each group takes every NG-th iteration whole, so that the latency of one iteration
+    // (copy wait, dequant, proxy fence, barrier) overlaps with the other groups' iterations; the operand ring holds
+    // SA / 2 iterations (two stages each), at least one per group
+    static constexpr int NG = MT <= 64 ? AO_UMMA_NG_SMALL : 2;
+    static constexpr int GW = kDequantWarps / NG;
     static constexpr int SA = MT <= 64 ? 8 : 4;
     static constexpr int SAShift = MT <= 64 ? 3 : 2;
-    // dequant warp groups: each group takes every NG-th iteration whole, so that the latency of one iteration
-    // (copy wait, dequant, proxy fence, barrier) overlaps with the other groups' iterations; 2 * NG <= SA
-    static constexpr int NG = MT <= 64 ? 4 : 2;
-    static constexpr int GW = kDequantWarps / NG;
-    static constexpr int Fixed = 1024 + SA * kABytes + SX * XBytes + 512;
+    static_assert(SA >= 2 * NG, "the operand ring needs an iteration per dequant group");
+    static constexpr int Fixed = 1024 + SA * kABytes + SX * XStage + 512;
     static constexpr int Rfit = (kSmemLimit - Fixed) / Policy::kRawBytes;
     static constexpr int R = Rfit > 8 ? 8 : Rfit;         // raw stages (each covers 128 k; the ring covers the copy latency)
-    static_assert(R >= 2, "raw ring needs two stages");
-    static constexpr int TmemCols = MT * TT < 32 ? 32 : MT * TT;   // TT token tiles of MT columns each
+    // A group waits for its raw stage by phase parity, which tells two consecutive uses of a stage apart and no more:
+    // the NG groups work on NG consecutive iterations at once, so these must all be different stages.
+    static_assert(R >= 2 && R >= NG, "the raw ring needs a stage per dequant group");
+    // MMA-issuing threads and accumulators per token tile.  For tiles of up to 128 columns two warps issue, taking
+    // turns (operand stage by operand stage, or iteration by iteration for the narrow tiles), each into its own
+    // accumulator so that the order of the additions stays fixed; the epilogue adds the two.
+    static constexpr int NACC = (TT == 1 && MT <= 128) ? 2 : 1;
+    static constexpr int TmemCols = MT * TT * NACC < 32 ? 32 : MT * TT * NACC;   // TT token tiles x NACC accumulators of MT columns
     static_assert(TmemCols <= 512, "tensor memory has 512 columns");
     static constexpr int SmemBytes = Fixed + R * Policy::kRawBytes;
 };
@@ -119,6 +158,27 @@ inline bool make_plan(int64_t M, int64_t N, int64_t K, Plan* P) {
     return true;
 }
 
+// eight accumulator columns of this thread's tensor-memory lane, added over the NACC accumulators in index order
+// (nused <= NACC of them were written: a CTA with a single iteration has work for one issuing thread only)
+template <int NACC, int MT>
+__device__ __forceinline__ void load_acc8(uint32_t taddr, uint32_t (&v)[8], int nused) {
+    ptx::tmem_ld_32x32b_x8(taddr, v);
+    if constexpr (NACC > 1) {
+        uint32_t w[NACC - 1][8];
+#pragma unroll
+        for (int a = 1; a < NACC; ++a) ptx::tmem_ld_32x32b_x8(taddr + a * MT, w[a - 1]);
+        ptx::tmem_ld_wait();
+#pragma unroll
+        for (int a = 1; a < NACC; ++a)
+            if (a < nused) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + __uint_as_float(w[a - 1][j]));
+            }
+    } else {
+        ptx::tmem_ld_wait();
+    }
+}
+
 template <bool BF16>
 __device__ __forceinline__ void store_out(void* y, size_t idx, float v) {
     if constexpr (BF16)
@@ -151,7 +211,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_kernel(const __grid_c
     const uint32_t base = (raw_addr + 1023u) & ~1023u;   // operand tiles need 1024-byte alignment
     uint8_t* sbase = smem_raw + (base - raw_addr);
     constexpr int SX = C::SX, kS = C::SA;
-    const uint32_t a_base = base, x_base = a_base + kS * kABytes, raw_base = x_base + SX * C::XBytes;
+    const uint32_t a_base = base, x_base = a_base + kS * kABytes, raw_base = x_base + SX * C::XStage;
     const uint32_t bar_base = raw_base + R * Policy::kRawBytes;
     const uint32_t full_a = bar_base, empty = full_a + 8 * kS, full_x = empty + 8 * kS, x_empty = full_x + 8 * SX;
     const uint32_t raw_full = x_empty + 8 * SX, raw_empty = raw_full + 8 * 8, acc_full = raw_empty + 8 * 8;
@@ -165,6 +225,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_kernel(const __grid_c
     const int nit = it_end - it_begin;     // iterations of 128 k for this CTA
     int* status = reinterpret_cast<int*>(p.ws);
 
+    AO_UTR(tid == 0, 160);
     if (tid == 0) {
         for (int s = 0; s < kS; ++s) {
             ptx::mbar_init(full_a + 8 * s, C::GW);
@@ -178,7 +239,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_kernel(const __grid_c
             ptx::mbar_init(raw_full + 8 * b, 1);
             ptx::mbar_init(raw_empty + 8 * b, C::GW);
         }
-        ptx::mbar_init(acc_full, 1);
+        ptx::mbar_init(acc_full, C::NACC);
         ptx::fence_mbar_init();
     }
     if (warp == 2) {
@@ -202,6 +263,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_kernel(const __grid_c
                     break;
                 }
                 Policy::issue_raw(p, raw_base + rb * Policy::kRawBytes, raw_full + 8 * rb, (it_begin + it) * kRawK, n0);
+                AO_UTR(it < 32, 128 + it);
                 if (++rb == R) {
                     rb = 0;
                     ph ^= 1u;
@@ -210,7 +272,19 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_kernel(const __grid_c
         }
     } else if (warp == 1) {
         // ---------------- activations: one operand stage per 64 k ----------------
-        if (lane == 0) {
+        if (lane == 0 && C::kIter) {
+            // one stage per iteration: the two 64-k tiles of the 128 k, one barrier
+            for (int it = 0; it < nit; ++it) {
+                const int s = it & (SX - 1);
+                if (!ptx::mbar_wait_bounded(x_empty + 8 * s, (static_cast<uint32_t>(it >> C::SXShift) & 1u) ^ 1u, kWaitPolls)) {
+                    ok = false;
+                    break;
+                }
+                ptx::mbar_arrive_expect_tx(full_x + 8 * s, C::XStage);
+                ptx::tma_load_2d(x_base + s * C::XStage, &p.map_x, 2 * (it_begin + it) * kKB, m0, full_x + 8 * s);
+                ptx::tma_load_2d(x_base + s * C::XStage + C::XBytes, &p.map_x, (2 * (it_begin + it) + 1) * kKB, m0, full_x + 8 * s);
+            }
+        } else if (lane == 0) {
             // x stage number xi = kb * TT + t: token tile t of k block kb (a tile beyond M reads as zeros)
             for (int xi = 0; xi < 2 * nit * TT; ++xi) {
                 const int s = xi & (SX - 1), kb = xi / TT, t = xi % TT;
@@ -222,18 +296,46 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_kernel(const __grid_c
                 ptx::tma_load_2d(x_base + s * C::XBytes, &p.map_x, (2 * it_begin + kb) * kKB, m0 + t * MT, full_x + 8 * s);
             }
         }
-    } else if (warp == 2) {
-        // ---------------- MMA issue ----------------
-        if (lane == 0) {
-            constexpr uint32_t idesc = ptx::umma_idesc(kRows, MT, Policy::kBF16, Policy::kAMajorMN);
-            constexpr uint32_t a_step = Policy::kAMajorMN ? (2048 >> 4) : (32 >> 4);   // descriptor units per k16
-            for (int kb = 0; kb < 2 * nit && ok; ++kb) {
+    } else if (warp == 2 || warp == kMmaWarp2) {
+        // ---------------- MMA issue: issuer w takes the operand stages kb = w, w + NACC, ... ----------------
+        const int w = warp == 2 ? 0 : 1;
+        constexpr uint32_t idesc = ptx::umma_idesc(kRows, MT, Policy::kBF16, Policy::kAMajorMN);
+        constexpr uint32_t a_step = Policy::kAMajorMN ? (2048 >> 4) : (32 >> 4);   // descriptor units per k16
+        if (lane == 0 && w < C::NACC && C::kIter) {
+            // issuer w takes the iterations w, w + NACC, ...: eight MMAs per pair of waits and pair of commits
+            for (int it = w; it < nit && ok; it += C::NACC) {
+                const int s0 = (2 * it) & (kS - 1), sx = it & (SX - 1);
+                if (!ptx::mbar_wait_bounded(full_a + 8 * s0, static_cast<uint32_t>((2 * it) >> C::SAShift) & 1u, kWaitPolls) ||
+                    !ptx::mbar_wait_bounded(full_x + 8 * sx, static_cast<uint32_t>(it >> C::SXShift) & 1u, kWaitPolls)) {
+                    ok = false;
+                    break;
+                }
+                AO_UTR(it < 16, 64 + 2 * it);
+                ptx::tcgen05_fence_after_thread_sync();
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const uint64_t da = Policy::kAMajorMN ? ptx::umma_desc_mn_sw128(a_base + (s0 + h) * kABytes)
+                                                          : ptx::umma_desc_k_sw128(a_base + (s0 + h) * kABytes);
+                    const uint64_t db = ptx::umma_desc_k_sw128(x_base + sx * C::XStage + h * C::XBytes);
+#pragma unroll
+                    for (int k4 = 0; k4 < kKB / 16; ++k4)
+                        ptx::umma_f16_ss(tmem_base + w * MT, da + a_step * k4, db + 2 * k4, idesc,
+                                         (it >= C::NACC || h != 0 || k4 != 0) ? 1u : 0u);
+                }
+                ptx::umma_commit(x_empty + 8 * sx);
+                ptx::umma_commit(empty + 8 * s0);
+                AO_UTR(it < 16, 96 + 2 * it);
+            }
+            if (ok) ptx::umma_commit(acc_full);
+        } else if (lane == 0 && w < C::NACC) {
+            for (int kb = w; kb < 2 * nit && ok; kb += C::NACC) {
                 const int s = kb & (kS - 1);
                 const uint32_t ph = static_cast<uint32_t>(kb >> C::SAShift) & 1u;
                 if (!ptx::mbar_wait_bounded(full_a + 8 * s, ph, kWaitPolls)) {
                     ok = false;
                     break;
                 }
+                AO_UTR(kb < 32, 64 + kb);
                 const uint64_t da = Policy::kAMajorMN ? ptx::umma_desc_mn_sw128(a_base + s * kABytes)
                                                       : ptx::umma_desc_k_sw128(a_base + s * kABytes);
 #pragma unroll
@@ -244,14 +346,18 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_kernel(const __grid_c
                         ok = false;
                         break;
                     }
+                    AO_UTR(kb < 32 && t == 0, 256 + kb);
                     ptx::tcgen05_fence_after_thread_sync();
                     const uint64_t db = ptx::umma_desc_k_sw128(x_base + sx * C::XBytes);
 #pragma unroll
                     for (int k4 = 0; k4 < kKB / 16; ++k4)
-                        ptx::umma_f16_ss(tmem_base + t * MT, da + a_step * k4, db + 2 * k4, idesc, (kb | k4) != 0 ? 1u : 0u);
+                        ptx::umma_f16_ss(tmem_base + (t * C::NACC + w) * MT, da + a_step * k4, db + 2 * k4, idesc,
+                                         (kb >= C::NACC || k4 != 0) ? 1u : 0u);
+                    AO_UTR(kb < 32 && t == 0, 288 + kb);
                     ptx::umma_commit(x_empty + 8 * sx);
                 }
                 if (ok) ptx::umma_commit(empty + 8 * s);
+                AO_UTR(kb < 32, 96 + kb);
             }
             if (ok) ptx::umma_commit(acc_full);
         }
@@ -266,21 +372,25 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_kernel(const __grid_c
             const uint32_t eph = (static_cast<uint32_t>(it >> (C::SAShift - 1)) & 1u) ^ 1u;
             if (!ptx::mbar_wait_bounded(raw_full + 8 * rb, rph, kWaitPolls) ||
                 !ptx::mbar_wait_bounded(empty + 8 * s0, eph, kWaitPolls) ||
-                !ptx::mbar_wait_bounded(empty + 8 * (s0 + 1), eph, kWaitPolls)) {
+                (!C::kIter && !ptx::mbar_wait_bounded(empty + 8 * (s0 + 1), eph, kWaitPolls))) {
                 ok = false;
                 break;
             }
+            AO_UTR(wi == 0 && lane == 0 && it / C::NG < 8, 16 * grp + 2 * (it / C::NG));
             Policy::template dequant<C::GW>(raw_base + rb * Policy::kRawBytes, a_base + s0 * kABytes, wi, lane);
             ptx::fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
                 ptx::mbar_arrive(full_a + 8 * s0);
-                ptx::mbar_arrive(full_a + 8 * (s0 + 1));
+                if (!C::kIter) ptx::mbar_arrive(full_a + 8 * (s0 + 1));
                 ptx::mbar_arrive(raw_empty + 8 * rb);
             }
+            AO_UTR(wi == 0 && lane == 0 && it / C::NG < 8, 16 * grp + 2 * (it / C::NG) + 1);
         }
         // ---------------- epilogue: lane quarter (warp % 4) x column quarter (dw / 4) ----------------
         if (ok && !ptx::mbar_wait_bounded(acc_full, 0u, kWaitPolls)) ok = false;
+        AO_UTR(dw == 0 && lane == 0, 161);
+        const int nacc_used = C::kIter ? (nit < C::NACC ? nit : C::NACC) : C::NACC;
         const int q = warp & 3, part = dw >> 2;
         const int row = q * 32 + lane;              // tensor-memory lane
         const int n = n0 + Policy::out_row(row);    // the weight row it holds
@@ -300,8 +410,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_kernel(const __grid_c
                     const int mt = m0 + t * MT;
                     if (mt + c0 >= M) continue;   // uniform across the warp
                     uint32_t v[8];
-                    ptx::tmem_ld_32x32b_x8(t_lane + t * MT + c0, v);
-                    ptx::tmem_ld_wait();
+                    load_acc8<C::NACC, MT>(t_lane + t * C::NACC * MT + c0, v, nacc_used);
                     if (n < N) {
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
@@ -327,8 +436,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_kernel(const __grid_c
                 for (int c0 = c_begin; c0 < c_begin + kColsPerWarp; c0 += 8) {
                     if (m0 + c0 >= M) break;
                     uint32_t v[8];
-                    ptx::tmem_ld_32x32b_x8(t_lane + c0, v);
-                    ptx::tmem_ld_wait();
+                    load_acc8<C::NACC, MT>(t_lane + c0, v, nacc_used);
 #pragma unroll
                     for (int j = 0; j < 8; ++j) mine[(size_t)(c0 + j) * kRows + row] = __uint_as_float(v[j]);
                 }
@@ -372,6 +480,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_kernel(const __grid_c
         }
     }
     if (!ok && lane == 0) atomicExch(status, AO_ERR_TIMEOUT);
+    AO_UTR(tid == 3 * 32, 162);
     ptx::tcgen05_fence_before_thread_sync();
     __syncthreads();
     if (warp == 2) {
