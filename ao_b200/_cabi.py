@@ -60,6 +60,7 @@ PROTOTYPES = {
     "ao_to_scaled_tc_fpx": (_int, [_ptr, _int, _i64, _i64, _int, _int, _ptr, _ptr, _ptr, _size, _ptr]),
     "ao_from_scaled_tc_fpx": (_int, [_ptr, _i64, _i64, _int, _int, _ptr, _ptr, _ptr]),
     "ao_fpx_linear": (_int, [_int, _int, _ptr, _i64, _ptr, _ptr, _i64, _i64, _i64, _ptr, _ptr, _size, _ptr]),
+    "ao_fpx_linear_bias": (_int, [_int, _int, _ptr, _i64, _ptr, _ptr, _ptr, _i64, _i64, _i64, _ptr, _ptr, _size, _ptr]),
     "ao_int4_tinygemm_linear_workspace_bytes": (_size, [_i64, _i64, _i64, _int, _int]),
     "ao_int4_tinygemm_linear": (_int, [_ptr, _i64, _i64, _ptr, _ptr, _i64, _i64, _i64, _int, _int, _ptr, _ptr,
                                        _size, _ptr]),

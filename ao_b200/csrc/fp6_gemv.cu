@@ -53,10 +53,12 @@ struct Plan {
     int xs_off, zero_off, part_off, bar_off, smem_bytes;
     Format fmt;        // decode constants of the 6-bit format, runtime values (kept in registers)
     size_t ws_counters_off, ws_slots_off, ws_bytes;
+    const __half* bias;   // optional [N]: y = round(round(acc * scale) + bias), the bits of `out += bias` after the op
 };
 
 static int make_plan(int64_t M, int64_t N, int64_t K, int fmt_id, Plan* P) {
     P->fmt = make_format(fmt_id);
+    P->bias = nullptr;
     const int tile_bytes = P->fmt.nbits == 6 ? 768 : 640;   // packed bytes of 64 rows x 16 k
     if (M < 1 || M > 16) return AO_ERR_SHAPE;
     if (N < 64 || N % 64 != 0 || K < 64 || K % 64 != 0) return AO_ERR_SHAPE;
@@ -142,6 +144,7 @@ static int make_plan(int64_t M, int64_t N, int64_t K, int fmt_id, Plan* P) {
 // post_scale * scale[row] of the eight rows this lane stores of row block a (fragment fr: rows e and e + 8)
 struct RowScales {
     float s0[4], s1[4];
+    float b0[4], b1[4];   // bias of the same rows (0 without a bias)
 };
 __device__ __forceinline__ RowScales load_row_scales(const Plan& P, int a, int lane, const __half* __restrict__ scale) {
     RowScales r;
@@ -151,8 +154,17 @@ __device__ __forceinline__ RowScales load_row_scales(const Plan& P, int a, int l
         const int n0 = a * 64 + fr * 16 + row;
         r.s0[fr] = P.fmt.post_scale * __half2float(scale[n0]);
         r.s1[fr] = P.fmt.post_scale * __half2float(scale[n0 + 8]);
+        r.b0[fr] = P.bias != nullptr ? __half2float(P.bias[n0]) : 0.f;
+        r.b1[fr] = P.bias != nullptr ? __half2float(P.bias[n0 + 8]) : 0.f;
     }
     return r;
+}
+
+// the product rounded to fp16, then (with a bias) the bias added and rounded again: what
+// `out = quant_llm_linear(...); out += bias` produces (quant_llm.py:433-445)
+__device__ __forceinline__ __half out_f16(float v, float bias, bool has_bias) {
+    const __half h = __float2half_rn(v);
+    return has_bias ? __float2half_rn(__half2float(h) + bias) : h;
 }
 
 // rows of fragment fr (16 rows) of row block a: store y = acc * 2^12 * scale[row]
@@ -160,20 +172,21 @@ template <int NB>
 __device__ __forceinline__ void store_block(const Plan& P, const float (&v)[4][NB][4], int a, int lane, const RowScales& rs,
                                             __half* __restrict__ y) {
     const int row = lane >> 2, c = lane & 3;
+    const bool hb = P.bias != nullptr;
 #pragma unroll
     for (int fr = 0; fr < 4; ++fr) {
         const int n0 = a * 64 + fr * 16 + row, n1 = n0 + 8;
-        const float s0 = rs.s0[fr], s1 = rs.s1[fr];
+        const float s0 = rs.s0[fr], s1 = rs.s1[fr], b0 = rs.b0[fr], b1 = rs.b1[fr];
 #pragma unroll
         for (int nb = 0; nb < NB; ++nb) {
             const int m0 = nb * 8 + 2 * c;
             if (m0 < P.M) {
-                y[(size_t)m0 * P.N + n0] = __float2half_rn(v[fr][nb][0] * s0);
-                y[(size_t)m0 * P.N + n1] = __float2half_rn(v[fr][nb][2] * s1);
+                y[(size_t)m0 * P.N + n0] = out_f16(v[fr][nb][0] * s0, b0, hb);
+                y[(size_t)m0 * P.N + n1] = out_f16(v[fr][nb][2] * s1, b1, hb);
             }
             if (m0 + 1 < P.M) {
-                y[(size_t)(m0 + 1) * P.N + n0] = __float2half_rn(v[fr][nb][1] * s0);
-                y[(size_t)(m0 + 1) * P.N + n1] = __float2half_rn(v[fr][nb][3] * s1);
+                y[(size_t)(m0 + 1) * P.N + n0] = out_f16(v[fr][nb][1] * s0, b0, hb);
+                y[(size_t)(m0 + 1) * P.N + n1] = out_f16(v[fr][nb][3] * s1, b1, hb);
             }
         }
     }
@@ -576,8 +589,7 @@ static int launch_bits(const Plan& P, const void* x, long long ldx, const void* 
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    const char* off = getenv("AO_B200_NO_PDL");
-    attr[0].val.programmaticStreamSerializationAllowed = (off && off[0] == '1') ? 0 : 1;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     if (cudaLaunchKernelEx(&cfg, kern, static_cast<const __half*>(x), ldx, static_cast<const uint8_t*>(wq),
@@ -603,7 +615,7 @@ namespace ao {
 namespace umma {
 size_t fp6_umma_workspace_bytes(int64_t M, int64_t N, int64_t K);
 int fp6_umma_linear(int fmt, const void* x, int64_t ldx, const uint8_t* packed, const void* scale, int64_t M, int64_t N,
-                    int64_t K, void* y, void* ws, size_t ws_bytes, cudaStream_t st);
+                    int64_t K, void* y, const void* bias, void* ws, size_t ws_bytes, cudaStream_t st);
 }  // namespace umma
 }  // namespace ao
 
@@ -625,17 +637,20 @@ size_t gemv_workspace_bytes(int64_t M, int64_t N, int64_t K, int fmt = ao::fp6::
 }
 
 int gemv(int fmt, const void* x_f16, int64_t x_row_stride, const uint8_t* packed, const void* scale_f16, int64_t M,
-         int64_t N, int64_t K, void* y_f16, void* workspace, size_t workspace_bytes, ao_stream_t stream) {
+         int64_t N, int64_t K, void* y_f16, const void* bias_f16, void* workspace, size_t workspace_bytes,
+         ao_stream_t stream) {
     if (M == 0 || N == 0) return AO_OK;
     fp6::Plan P;
     int rc = fp6::make_plan(M, N, K, fmt, &P);
     if (rc == AO_ERR_UNSUPPORTED && M > 8) {
-        rc = gemv(fmt, x_f16, x_row_stride, packed, scale_f16, 8, N, K, y_f16, workspace, workspace_bytes, stream);
+        rc = gemv(fmt, x_f16, x_row_stride, packed, scale_f16, 8, N, K, y_f16, bias_f16, workspace, workspace_bytes, stream);
         if (rc) return rc;
         return gemv(fmt, static_cast<const __half*>(x_f16) + 8 * x_row_stride, x_row_stride, packed, scale_f16, M - 8, N, K,
-                    static_cast<__half*>(y_f16) + 8 * N, workspace, workspace_bytes, stream);
+                    static_cast<__half*>(y_f16) + 8 * N, bias_f16, workspace, workspace_bytes, stream);
     }
     if (rc) return rc;
+    if (!aligned(bias_f16, 2)) return AO_ERR_ALIGN;
+    P.bias = static_cast<const __half*>(bias_f16);
     if (x_row_stride < K || x_row_stride % 2 != 0) return AO_ERR_SHAPE;
     if (!aligned(x_f16, 4) || !aligned(packed, 16) || !aligned(scale_f16, 2) || !aligned(y_f16, 2) ||
         !aligned(workspace, 256))
@@ -665,23 +680,24 @@ size_t linear_workspace_bytes(int64_t M, int64_t N, int64_t K) {
 }
 
 int linear(int fmt, const void* x_f16, int64_t x_row_stride, const uint8_t* packed, const void* scale_f16, int64_t M,
-           int64_t N, int64_t K, void* y_f16, void* workspace, size_t workspace_bytes, ao_stream_t stream) {
+           int64_t N, int64_t K, void* y_f16, const void* bias_f16, void* workspace, size_t workspace_bytes,
+           ao_stream_t stream) {
     if (M < 0 || N < 0) return AO_ERR_SHAPE;
     if (M <= 8)
-        return gemv(fmt, x_f16, x_row_stride, packed, scale_f16, M, N, K, y_f16, workspace, workspace_bytes, stream);
+        return gemv(fmt, x_f16, x_row_stride, packed, scale_f16, M, N, K, y_f16, bias_f16, workspace, workspace_bytes, stream);
     if (workspace == nullptr || workspace_bytes < 256 || !aligned(workspace, 256)) return AO_ERR_WORKSPACE;
     {
-        const int rc = umma::fp6_umma_linear(fmt, x_f16, x_row_stride, packed, scale_f16, M, N, K, y_f16, workspace,
+        const int rc = umma::fp6_umma_linear(fmt, x_f16, x_row_stride, packed, scale_f16, M, N, K, y_f16, bias_f16, workspace,
                                              workspace_bytes, as_stream(stream));
         if (rc != AO_ERR_UNSUPPORTED) return rc;
     }
     if (M <= 16)
-        return gemv(fmt, x_f16, x_row_stride, packed, scale_f16, M, N, K, y_f16, workspace, workspace_bytes, stream);
+        return gemv(fmt, x_f16, x_row_stride, packed, scale_f16, M, N, K, y_f16, bias_f16, workspace, workspace_bytes, stream);
     const auto* x = static_cast<const __half*>(x_f16);
     auto* y = static_cast<__half*>(y_f16);
     for (int64_t m0 = 0; m0 < M; m0 += 16) {
         const int64_t mb = M - m0 < 16 ? M - m0 : 16;
-        int rc = gemv(fmt, x + m0 * x_row_stride, x_row_stride, packed, scale_f16, mb, N, K, y + m0 * N, workspace,
+        int rc = gemv(fmt, x + m0 * x_row_stride, x_row_stride, packed, scale_f16, mb, N, K, y + m0 * N, bias_f16, workspace,
                       workspace_bytes, stream);
         if (rc) return rc;
     }
@@ -695,7 +711,7 @@ extern "C" size_t ao_fp6_gemv_workspace_bytes(int64_t M, int64_t N, int64_t K) {
 extern "C" int ao_fp6_gemv(const void* x_f16, int64_t x_row_stride, const uint8_t* packed, const void* scale_f16,
                            int64_t M, int64_t N, int64_t K, void* y_f16, void* workspace, size_t workspace_bytes,
                            ao_stream_t stream) {
-    return gemv(ao::fp6::kE3M2, x_f16, x_row_stride, packed, scale_f16, M, N, K, y_f16, workspace, workspace_bytes, stream);
+    return gemv(ao::fp6::kE3M2, x_f16, x_row_stride, packed, scale_f16, M, N, K, y_f16, nullptr, workspace, workspace_bytes, stream);
 }
 
 // torchao::quant_llm_linear for e3m2
@@ -704,7 +720,7 @@ extern "C" size_t ao_fp6_linear_workspace_bytes(int64_t M, int64_t N, int64_t K)
 extern "C" int ao_fp6_linear(const void* x_f16, int64_t x_row_stride, const uint8_t* packed, const void* scale_f16,
                              int64_t M, int64_t N, int64_t K, void* y_f16, void* workspace, size_t workspace_bytes,
                              ao_stream_t stream) {
-    return linear(ao::fp6::kE3M2, x_f16, x_row_stride, packed, scale_f16, M, N, K, y_f16, workspace, workspace_bytes, stream);
+    return linear(ao::fp6::kE3M2, x_f16, x_row_stride, packed, scale_f16, M, N, K, y_f16, nullptr, workspace, workspace_bytes, stream);
 }
 
 // torchao::quant_llm_linear: (EXPONENT, MANTISSA) = (3, 2), (2, 3), (2, 2) or (3, 1)
@@ -713,5 +729,15 @@ extern "C" int ao_fpx_linear(int ebits, int mbits, const void* x_f16, int64_t x_
                              size_t workspace_bytes, ao_stream_t stream) {
     const int fmt = ao::fp6::format_id(ebits, mbits);
     if (fmt < 0) return AO_ERR_UNSUPPORTED;
-    return linear(fmt, x_f16, x_row_stride, packed, scale_f16, M, N, K, y_f16, workspace, workspace_bytes, stream);
+    return linear(fmt, x_f16, x_row_stride, packed, scale_f16, M, N, K, y_f16, nullptr, workspace, workspace_bytes, stream);
+}
+
+// the same with the bias add of the reference's linear dispatch (quant_llm.py:444-445) fused into the stores:
+// bias_f16 [N] fp16 or null; y = round_f16(round_f16(x @ W^T) + bias)
+extern "C" int ao_fpx_linear_bias(int ebits, int mbits, const void* x_f16, int64_t x_row_stride, const uint8_t* packed,
+                                  const void* scale_f16, const void* bias_f16, int64_t M, int64_t N, int64_t K, void* y_f16,
+                                  void* workspace, size_t workspace_bytes, ao_stream_t stream) {
+    const int fmt = ao::fp6::format_id(ebits, mbits);
+    if (fmt < 0) return AO_ERR_UNSUPPORTED;
+    return linear(fmt, x_f16, x_row_stride, packed, scale_f16, M, N, K, y_f16, bias_f16, workspace, workspace_bytes, stream);
 }

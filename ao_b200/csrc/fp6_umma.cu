@@ -96,7 +96,7 @@ size_t fp6_umma_workspace_bytes(int64_t M, int64_t N, int64_t K) {
 
 // AO_ERR_UNSUPPORTED: the caller falls back to row blocks through the decode kernel.
 int fp6_umma_linear(int fmt, const void* x, int64_t ldx, const uint8_t* packed, const void* scale, int64_t M, int64_t N,
-                    int64_t K, void* y, void* ws, size_t ws_bytes, cudaStream_t st) {
+                    int64_t K, void* y, const void* bias, void* ws, size_t ws_bytes, cudaStream_t st) {
     Plan P;
     if (!fp6_shape_ok(M, N, K) || !make_plan(M, N, K, &P)) return AO_ERR_UNSUPPORTED;
     if (!aligned(x, 16) || (ldx * 2) % 16 != 0 || ldx < K || !aligned(packed, 16)) return AO_ERR_UNSUPPORTED;
@@ -109,6 +109,7 @@ int fp6_umma_linear(int fmt, const void* x, int64_t ldx, const uint8_t* packed, 
     prm.w = packed;
     prm.scale = scale;
     prm.y = y;
+    prm.bias = bias;
     prm.ws = static_cast<uint8_t*>(ws);
     prm.M = (int)M;
     prm.N = (int)N;

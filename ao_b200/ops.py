@@ -223,6 +223,20 @@ def quant_llm_linear(EXPONENT: int, MANTISSA: int, _in_feats: Tensor, _weights: 
     """Quant-LLM linear layer A @ W.T (torchao/ops.py:15-55).  _in_feats fp16 [BS][IC], _weights packed FPx uint8
     [OC][IC/8*nbits], _scales fp16 [OC] -> fp16 [BS][OC].  Formats: e3m2, e2m3 (fp6), e2m2, e3m1 (fp5); `splitK` is accepted and ignored (the
     kernel chooses its own K split)."""
+    return _quant_llm_linear(EXPONENT, MANTISSA, _in_feats, _weights, _scales, None)
+
+
+def quant_llm_linear_bias(EXPONENT: int, MANTISSA: int, _in_feats: Tensor, _weights: Tensor, _scales: Tensor,
+                          bias: Tensor) -> Tensor:
+    """quant_llm_linear followed by `out += bias` (the linear dispatch of QuantLlmLinearWeight,
+    torchao/prototype/quant_llm/quant_llm.py:433-445) in one kernel: the add happens in the kernel's stores, on the
+    fp16-rounded product, so the bits are those of the separate add.  bias fp16 [OC]."""
+    torch._check(bias.dim() == 1 and bias.dtype is torch.float16 and bias.shape[0] == _weights.shape[0],
+                 lambda: f"bias must be FP16 [OC], got {bias.dtype} {tuple(bias.shape)}")
+    return _quant_llm_linear(EXPONENT, MANTISSA, _in_feats, _weights, _scales, bias)
+
+
+def _quant_llm_linear(EXPONENT, MANTISSA, _in_feats, _weights, _scales, bias):
     torch._check(_in_feats.dim() == 2, lambda: f"input should be a 2d tensor, got {_in_feats.dim()}D")
     torch._check(_in_feats.dtype is torch.float16, lambda: f"weight must be FP16, got {_in_feats.dtype}")
     torch._check(_weights.dim() == 2, lambda: f"weight should be a 2d tensor, got {_weights.dim()}D")
@@ -251,8 +265,14 @@ def quant_llm_linear(EXPONENT: int, MANTISSA: int, _in_feats: Tensor, _weights: 
     torch._check(nbytes > 0, lambda: f"unsupported fp6 linear shape BS={BS} OC={OC} IC={IC}")
     with torch.cuda.device(x.device):
         ws = _cabi.workspace(nbytes, x.device)
-        rc = lib.ao_fpx_linear(EXPONENT, MANTISSA, _cabi.ptr(x), x.stride(0), _cabi.ptr(w), _cabi.ptr(s), BS, OC, IC, _cabi.ptr(y),
-                               _cabi.ptr(ws), ws.numel(), _stream(x))
+        if bias is None:
+            rc = lib.ao_fpx_linear(EXPONENT, MANTISSA, _cabi.ptr(x), x.stride(0), _cabi.ptr(w), _cabi.ptr(s), BS, OC, IC,
+                                   _cabi.ptr(y), _cabi.ptr(ws), ws.numel(), _stream(x))
+        else:
+            _cabi.require_cuda(bias)
+            b = bias.contiguous()
+            rc = lib.ao_fpx_linear_bias(EXPONENT, MANTISSA, _cabi.ptr(x), x.stride(0), _cabi.ptr(w), _cabi.ptr(s), _cabi.ptr(b),
+                                        BS, OC, IC, _cabi.ptr(y), _cabi.ptr(ws), ws.numel(), _stream(x))
     _cabi.check(rc, "quant_llm_linear")
     return y
 

@@ -167,6 +167,12 @@ def _(*args, **kwargs):
     assert isinstance(weight, QuantLlmLinearWeight)
     out_dim, in_dim = weight.shape
     act_reshaped = act.reshape(-1, in_dim).half()
+    if (bias is not None and type(bias) in (Tensor, torch.nn.Parameter) and bias.dtype is torch.float16 and bias.dim() == 1
+            and bias.is_cuda and not torch.compiler.is_compiling()):
+        # eager calls: the add happens in the kernel's stores (same bits as the separate add below)
+        from ... import ops
+        out = ops.quant_llm_linear_bias(weight.ebits, weight.mbits, act_reshaped, weight.fpx_data, weight.scale, bias.detach())
+        return out.view(*act.shape[:-1], out_dim).to(act.dtype)
     out = torch.ops.torchao.quant_llm_linear(weight.ebits, weight.mbits, act_reshaped, weight.fpx_data, weight.scale, 1)
     if bias is not None:
         out += bias

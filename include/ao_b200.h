@@ -323,6 +323,13 @@ int ao_fpx_linear(int ebits, int mbits, const void* x_f16, int64_t x_row_stride,
                   const void* scale_f16, int64_t M, int64_t N, int64_t K, void* y_f16, void* workspace,
                   size_t workspace_bytes, ao_stream_t stream);
 
+/* ao_fpx_linear with the bias add of the reference's linear dispatch fused into the stores
+ * (torchao/prototype/quant_llm/quant_llm.py:433-445: `out = quant_llm_linear(...); out += bias`): bias_f16 [N] fp16 or
+ * NULL; y = round_f16(round_f16(x @ W^T) + bias), the bits the separate add gives. */
+int ao_fpx_linear_bias(int ebits, int mbits, const void* x_f16, int64_t x_row_stride, const uint8_t* packed,
+                       const void* scale_f16, const void* bias_f16, int64_t M, int64_t N, int64_t K, void* y_f16,
+                       void* workspace, size_t workspace_bytes, ao_stream_t stream);
+
 /* The decode kernel alone (1 <= M <= 16). */
 size_t ao_fp6_gemv_workspace_bytes(int64_t M, int64_t N, int64_t K);
 int ao_fp6_gemv(const void* x_f16, int64_t x_row_stride, const uint8_t* packed, const void* scale_f16,

@@ -141,6 +141,30 @@ def test_bias_is_fused_with_the_bits_of_the_separate_add():
         assert torch.equal(y, ref), f"M={M}"
 
 
+def test_fp6_bias_is_fused_with_the_bits_of_the_separate_add():
+    """F.linear with an fp16 bias on a QuantLlmLinearWeight: one kernel, and the bits of
+    `out = quant_llm_linear(...); out += bias` (quant_llm.py:433-445) on the decode kernel (with and without K slabs),
+    the tcgen05 kernel and the 16-row block route; for every FPx format."""
+    from ao_b200 import ops
+    from ao_b200.prototype.quant_llm import quant_llm_fpx_weight_only
+    from ao_b200.quantization import quantize
+    torch.manual_seed(6)
+    for ebits, mbits in ((3, 2), (2, 3), (2, 2), (3, 1)):
+        lin = torch.nn.Linear(1024, 512, bias=True, device="cuda", dtype=torch.float16)
+        with torch.no_grad():
+            lin.bias.mul_(3.0)
+        quantize(lin, quant_llm_fpx_weight_only(ebits, mbits))
+        w = lin.weight
+        for M in (1, 5, 8, 16, 64, 300):
+            x = torch.randn(M, 1024, device="cuda", dtype=torch.float16)
+            y = lin(x)
+            ref = ops.quant_llm_linear(ebits, mbits, x, w.fpx_data, w.scale)
+            ref += lin.bias
+            assert y.dtype == torch.float16 and torch.equal(y, ref), f"e{ebits}m{mbits} M={M}"
+        with pytest.raises(RuntimeError):
+            ops.quant_llm_linear_bias(ebits, mbits, x, w.fpx_data, w.scale, lin.bias.float())
+
+
 def test_filter_fn_and_transpose():
     from ao_b200.dtypes import AffineQuantizedTensor
     from ao_b200.quantization import int4_weight_only, quantize
