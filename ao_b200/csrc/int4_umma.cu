@@ -8,7 +8,7 @@
 // Dequant: a packed word already is an MMA fragment (8 codes of one row), so codes -> bf16 (128 + q) with one
 // logic op per register, (q - 8) * s + z with two bf16x2 FMAs, and one stmatrix writes 8 rows x 32 k into the
 // swizzled K-major operand tile.
-#include "umma_linear.cuh"
+#include "umma_linear_ts.cuh"
 
 namespace ao {
 namespace umma {
@@ -69,6 +69,46 @@ struct TinygemmPolicy {
         }
     }
 
+    // Operand in tensor memory: one thread, weight row `row` of the CTA's 128.  The row's codes sit in the words of the
+    // four lanes 4r .. 4r + 3 of its 8-row tile (r = row % 8): word j of lane 4r + c holds, as the pair (nibble i,
+    // nibble i + 4), the codes of k = 32 j + 8 i + 2c and the next k, i.e. the content of column 16 j + 4 i + c.
+    static constexpr bool kRowDequant = true;
+    static __device__ __forceinline__ void dequant_row(uint32_t raw, int row, uint32_t t_addr) {
+        const uint32_t nib = 0x000F000Fu, magic = 0x43004300u, one2 = 0x3F803F80u, m136 = 0xC308C308u;
+        const uint32_t wbase = raw + (row >> 3) * 512 + (row & 7) * 64;
+        uint32_t w[4][4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const uint4 v = ptx::lds128(wbase + c * 16);
+            w[c][0] = v.x; w[c][1] = v.y; w[c][2] = v.z; w[c][3] = v.w;
+        }
+        // (scale, zero) of this row: group gi of the raw stage at + gi * 512
+        const uint32_t sc_addr = raw + kWBytes + row * 4;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            uint32_t col[32];
+            uint32_t s2 = 0, z2 = 0;
+#pragma unroll
+            for (int jj = 0; jj < 2; ++jj) {
+                const int j = 2 * h + jj;
+                if (jj == 0 || GSHIFT == 5) {
+                    const int gi = GSHIFT >= 7 ? 0 : (j * 32) >> GSHIFT;
+                    const uint32_t sz = ptx::lds32(sc_addr + gi * (kRows * 4));
+                    s2 = __byte_perm(sz, sz, 0x1010);
+                    z2 = __byte_perm(sz, sz, 0x3232);
+                }
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const uint32_t qv = ptx::and_or(w[c][j] >> (4 * i), nib, magic);      // bf16 pair (128 + q)
+                        col[16 * jj + 4 * i + c] = fma_bf16x2(fma_bf16x2(qv, one2, m136), s2, z2);   // (q - 8) * s + z
+                    }
+            }
+            ptx::tmem_st_32x32b_x32(t_addr + 32 * h, col);
+        }
+    }
+
     static __device__ __forceinline__ int out_row(int row) { return row; }
     static __device__ __forceinline__ float row_scale(const Params&, int) { return 1.f; }
 };
@@ -116,10 +156,10 @@ int int4_umma_linear(const void* x, int64_t ldx, int64_t x_cols, const int32_t* 
     prm.N = (int)N;
     prm.K = (int)K;
     switch (g) {
-        case 32: return launch_mt<TinygemmPolicy<5>>(P, prm, st);
-        case 64: return launch_mt<TinygemmPolicy<6>>(P, prm, st);
-        case 128: return launch_mt<TinygemmPolicy<7>>(P, prm, st);
-        default: return launch_mt<TinygemmPolicy<8>>(P, prm, st);
+        case 32: return launch_mt_ts<TinygemmPolicy<5>>(P, prm, st);
+        case 64: return launch_mt_ts<TinygemmPolicy<6>>(P, prm, st);
+        case 128: return launch_mt_ts<TinygemmPolicy<7>>(P, prm, st);
+        default: return launch_mt_ts<TinygemmPolicy<8>>(P, prm, st);
     }
 }
 

@@ -202,6 +202,103 @@ __device__ __forceinline__ float load_bias(const void* bias, int n) {
     return __half2float(static_cast<const __half*>(bias)[n]);
 }
 
+// Epilogue of the dequant warps (warps 3 .. 3 + kDequantWarps - 1): lane quarter (warp % 4) x column quarter
+// ((warp - 3) / 4) of the accumulator(s) -> y, or, with K slabs, -> this slab's workspace slot, after which the CTA that
+// completes the tile adds the slabs in order.  flag: a word of shared memory for the "last slab" broadcast.
+template <int MT, class Policy, int NACC, int TT>
+__device__ __forceinline__ void epilogue(const Params& p, uint32_t tmem_base, int warp, int lane, int n0, int m0,
+                                         int nacc_used, bool ok, volatile int* flag) {
+    const int M = p.M, N = p.N;
+    const int nsplit = gridDim.z, z = blockIdx.z;
+    const int tid = threadIdx.x, dw = warp - 3;
+    const int q = warp & 3, part = dw >> 2;
+    const int row = q * 32 + lane;              // tensor-memory lane
+    const int n = n0 + Policy::out_row(row);    // the weight row it holds
+    const float rs = n < N ? Policy::row_scale(p, n) : 0.f;
+    const bool has_bias = p.bias != nullptr;
+    const float bias_n = (has_bias && n < N) ? load_bias<Policy::kBF16>(p.bias, n) : 0.f;
+    constexpr int kColsPerWarp = MT / 4;
+    const int c_begin = part * kColsPerWarp;
+    const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+    if (nsplit == 1) {
+        if (ok) {
+            ptx::tcgen05_fence_after_thread_sync();
+#pragma unroll 1
+            for (int cc = 0; cc < TT * kColsPerWarp; cc += 8) {
+                // column cc of this warp's share: token tile cc / kColsPerWarp, column c0 inside the tile
+                const int t = cc / kColsPerWarp, c0 = c_begin + (cc - t * kColsPerWarp);
+                const int mt = m0 + t * MT;
+                if (mt + c0 >= M) continue;   // uniform across the warp
+                uint32_t v[8];
+                load_acc8<NACC, MT>(t_lane + t * NACC * MT + c0, v, nacc_used);
+                if (n < N) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const int m = mt + c0 + j;
+                        if (m < M) {
+                            if (has_bias) store_out_bias<Policy::kBF16>(p.y, (size_t)m * N + n, __uint_as_float(v[j]) * rs, bias_n);
+                            else store_out<Policy::kBF16>(p.y, (size_t)m * N + n, __uint_as_float(v[j]) * rs);
+                        }
+                    }
+                }
+            }
+        }
+    } else {
+        // K slabs: fp32 partial tile [column][lane] into this slab's workspace slot; the CTA that completes the
+        // tile (atomic counter) adds the slabs in order and stores; the counter is left at zero.
+        const int tile_id = blockIdx.y * gridDim.x + blockIdx.x;
+        float* slots = reinterpret_cast<float*>(p.ws + kHeaderBytes + (size_t)kMaxTiles * 4);
+        const size_t slot_elems = (size_t)kRows * MT;
+        float* mine = slots + ((size_t)tile_id * nsplit + z) * slot_elems;
+        if (ok) {
+            ptx::tcgen05_fence_after_thread_sync();
+#pragma unroll 1
+            for (int c0 = c_begin; c0 < c_begin + kColsPerWarp; c0 += 8) {
+                if (m0 + c0 >= M) break;
+                uint32_t v[8];
+                load_acc8<NACC, MT>(t_lane + c0, v, nacc_used);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) mine[(size_t)(c0 + j) * kRows + row] = __uint_as_float(v[j]);
+            }
+        }
+        __threadfence();
+        ptx::named_barrier_sync(1, kDequantWarps * 32);
+                if (tid == 3 * 32) {
+            int* counter = reinterpret_cast<int*>(p.ws + kHeaderBytes) + tile_id;
+            const int old = atomicAdd(counter, 1);
+            *flag = (old + 1 == nsplit) ? 1 : 0;
+            if (old + 1 == nsplit) *counter = 0;   // every slab has arrived: ready for the next call
+        }
+        ptx::named_barrier_sync(1, kDequantWarps * 32);
+        if (*flag) {
+            __threadfence();
+            const float* tile_slots = slots + (size_t)tile_id * nsplit * slot_elems;
+#pragma unroll 1
+            for (int c0 = c_begin; c0 < c_begin + kColsPerWarp; c0 += 8) {
+                if (m0 + c0 >= M) break;
+                float acc[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+                for (int zz = 0; zz < nsplit; ++zz) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        acc[j] += ptx::ldcg_f32(tile_slots + (size_t)zz * slot_elems + (size_t)(c0 + j) * kRows + row);
+                }
+                if (n < N) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const int m = m0 + c0 + j;
+                        if (m < M) {
+                            if (has_bias) store_out_bias<Policy::kBF16>(p.y, (size_t)m * N + n, acc[j] * rs, bias_n);
+                            else store_out<Policy::kBF16>(p.y, (size_t)m * N + n, acc[j] * rs);
+                        }
+                    }
+                }
+            }
+        }
+    }
+}
+
 template <int MT, class Policy, int TT>
 __global__ void __launch_bounds__(kThreads, 1) umma_linear_kernel(const __grid_constant__ Params p) {
     using C = Cfg<MT, Policy, TT>;
@@ -217,7 +314,6 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_kernel(const __grid_c
     const uint32_t raw_full = x_empty + 8 * SX, raw_empty = raw_full + 8 * 8, acc_full = raw_empty + 8 * 8;
     const uint32_t tmem_slot = acc_full + 8, flag_slot = tmem_slot + 4;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int M = p.M, N = p.N;
     const int n0 = blockIdx.x * kRows, m0 = blockIdx.y * (MT * TT);   // first row of the CTA's first token tile
     const int nsplit = gridDim.z, z = blockIdx.z;
     const int nit_all = p.K / kRawK;
@@ -391,93 +487,8 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_kernel(const __grid_c
         if (ok && !ptx::mbar_wait_bounded(acc_full, 0u, kWaitPolls)) ok = false;
         AO_UTR(dw == 0 && lane == 0, 161);
         const int nacc_used = C::kIter ? (nit < C::NACC ? nit : C::NACC) : C::NACC;
-        const int q = warp & 3, part = dw >> 2;
-        const int row = q * 32 + lane;              // tensor-memory lane
-        const int n = n0 + Policy::out_row(row);    // the weight row it holds
-        const float rs = n < N ? Policy::row_scale(p, n) : 0.f;
-        const bool has_bias = p.bias != nullptr;
-        const float bias_n = (has_bias && n < N) ? load_bias<Policy::kBF16>(p.bias, n) : 0.f;
-        constexpr int kColsPerWarp = MT / 4;
-        const int c_begin = part * kColsPerWarp;
-        const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
-        if (nsplit == 1) {
-            if (ok) {
-                ptx::tcgen05_fence_after_thread_sync();
-#pragma unroll 1
-                for (int cc = 0; cc < TT * kColsPerWarp; cc += 8) {
-                    // column cc of this warp's share: token tile cc / kColsPerWarp, column c0 inside the tile
-                    const int t = cc / kColsPerWarp, c0 = c_begin + (cc - t * kColsPerWarp);
-                    const int mt = m0 + t * MT;
-                    if (mt + c0 >= M) continue;   // uniform across the warp
-                    uint32_t v[8];
-                    load_acc8<C::NACC, MT>(t_lane + t * C::NACC * MT + c0, v, nacc_used);
-                    if (n < N) {
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            const int m = mt + c0 + j;
-                            if (m < M) {
-                                if (has_bias) store_out_bias<Policy::kBF16>(p.y, (size_t)m * N + n, __uint_as_float(v[j]) * rs, bias_n);
-                                else store_out<Policy::kBF16>(p.y, (size_t)m * N + n, __uint_as_float(v[j]) * rs);
-                            }
-                        }
-                    }
-                }
-            }
-        } else {
-            // K slabs: fp32 partial tile [column][lane] into this slab's workspace slot; the CTA that completes the
-            // tile (atomic counter) adds the slabs in order and stores; the counter is left at zero.
-            const int tile_id = blockIdx.y * gridDim.x + blockIdx.x;
-            float* slots = reinterpret_cast<float*>(p.ws + kHeaderBytes + (size_t)kMaxTiles * 4);
-            const size_t slot_elems = (size_t)kRows * MT;
-            float* mine = slots + ((size_t)tile_id * nsplit + z) * slot_elems;
-            if (ok) {
-                ptx::tcgen05_fence_after_thread_sync();
-#pragma unroll 1
-                for (int c0 = c_begin; c0 < c_begin + kColsPerWarp; c0 += 8) {
-                    if (m0 + c0 >= M) break;
-                    uint32_t v[8];
-                    load_acc8<C::NACC, MT>(t_lane + c0, v, nacc_used);
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) mine[(size_t)(c0 + j) * kRows + row] = __uint_as_float(v[j]);
-                }
-            }
-            __threadfence();
-            ptx::named_barrier_sync(1, kDequantWarps * 32);
-            volatile int* flag = reinterpret_cast<volatile int*>(sbase + (flag_slot - base));
-            if (tid == 3 * 32) {
-                int* counter = reinterpret_cast<int*>(p.ws + kHeaderBytes) + tile_id;
-                const int old = atomicAdd(counter, 1);
-                *flag = (old + 1 == nsplit) ? 1 : 0;
-                if (old + 1 == nsplit) *counter = 0;   // every slab has arrived: ready for the next call
-            }
-            ptx::named_barrier_sync(1, kDequantWarps * 32);
-            if (*flag) {
-                __threadfence();
-                const float* tile_slots = slots + (size_t)tile_id * nsplit * slot_elems;
-#pragma unroll 1
-                for (int c0 = c_begin; c0 < c_begin + kColsPerWarp; c0 += 8) {
-                    if (m0 + c0 >= M) break;
-                    float acc[8];
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-                    for (int zz = 0; zz < nsplit; ++zz) {
-#pragma unroll
-                        for (int j = 0; j < 8; ++j)
-                            acc[j] += ptx::ldcg_f32(tile_slots + (size_t)zz * slot_elems + (size_t)(c0 + j) * kRows + row);
-                    }
-                    if (n < N) {
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            const int m = m0 + c0 + j;
-                            if (m < M) {
-                                if (has_bias) store_out_bias<Policy::kBF16>(p.y, (size_t)m * N + n, acc[j] * rs, bias_n);
-                                else store_out<Policy::kBF16>(p.y, (size_t)m * N + n, acc[j] * rs);
-                            }
-                        }
-                    }
-                }
-            }
-        }
+        epilogue<MT, Policy, C::NACC, TT>(p, tmem_base, warp, lane, n0, m0, nacc_used, ok,
+                                          reinterpret_cast<volatile int*>(sbase + (flag_slot - base)));
     }
     if (!ok && lane == 0) atomicExch(status, AO_ERR_TIMEOUT);
     AO_UTR(tid == 3 * 32, 162);

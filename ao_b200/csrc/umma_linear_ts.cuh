@@ -1,0 +1,237 @@
+// The prefill-shaped weight-only linear with the DEQUANTISED WEIGHTS IN TENSOR MEMORY (tcgen05.mma with the A operand
+// taken from tensor memory, the activations from shared memory), for one token tile per CTA:
+//   y[M][N] = x[M][K] @ dequant(W)[N][K]^T.
+// Same product orientation, warp roles, K slabs, bounded waits and epilogue as umma_linear.cuh; what differs is the path
+// of the dequantised operand.  There the 16 dequant warps write a swizzled 16-bit tile to shared memory (stmatrix, proxy
+// fence) and a ring of such tiles (64 - 128 KB) feeds the MMA.  Here every dequant thread owns ONE weight row of the CTA's
+// 128 - the row whose tensor-memory lane it can address (lane = 32 * (warp % 4) + lane id) - turns that row's 128 k of an
+// iteration into 64 registers of 16-bit pairs and stores them with tcgen05.st into 64 columns of its lane: row i in lane
+// i, column c = (k = 2c, 2c + 1), exactly the layout the MMA reads for an operand in tensor memory.
+// Tensor memory (512 columns): accumulators in columns [0, 256) (one of 256 columns, or two of up to 128 for the two
+// issuing threads), four operand slots of 64 columns (one iteration each) in [256, 512).
+// What that buys: no operand ring in shared memory (the activation ring and the raw ring get the room: 8 raw stages in
+// flight per SM), no swizzle arithmetic, no proxy fence, per-row scale loads instead of byte permutes; and four
+// iterations in dequantisation at once (four groups of four warps, one warp per lane quarter) against four slots, so a
+// group's wait for the MMAs that read its slot overlaps the other groups' work.
+//
+// A weight format takes part by providing, besides what umma_linear.cuh lists,
+//   kRowDequant = true
+//   dequant_row(raw, row, t_addr)   one thread: the 128 k of weight row `row` (0..127 inside the CTA) of the raw stage at
+//                                   `raw` -> 64 columns at tensor-memory address t_addr (two tcgen05.st of 32 columns,
+//                                   executed by the whole warp)
+#pragma once
+#include "umma_linear.cuh"
+
+namespace ao {
+namespace umma {
+
+template <int MT, class Policy>
+struct CfgTS {
+    static constexpr int NACC = MT <= 128 ? 2 : 1;           // issuing threads = accumulators
+    static constexpr int XK = MT <= 128 ? 128 : 64;           // k per activation stage
+    static constexpr int XBytes = MT * kKB * 2;               // one 64-k activation tile
+    static constexpr int XStage = XBytes * (XK / kKB);
+    static constexpr int SX = MT <= 64 ? 8 : 4;               // activation stages (a power of two)
+    static constexpr int SXShift = MT <= 64 ? 3 : 2;
+    static constexpr int NG = 4, GW = kDequantWarps / NG;     // dequant groups; one warp per lane quarter in each
+    static constexpr int NSLOT = 4;                           // operand slots in tensor memory, one per group
+    static constexpr int ACol0 = 256, AColsPerIt = kRawK / 2;
+    static constexpr int Fixed = 1024 + SX * XStage + 512;
+    static constexpr int Rfit = (kSmemLimit - Fixed) / Policy::kRawBytes;
+    static constexpr int R = Rfit > 8 ? 8 : Rfit;
+    static_assert(GW == 4, "a dequant group has one warp per lane quarter of tensor memory");
+    static_assert(NG == NSLOT, "group g owns operand slot g");
+    static_assert(R >= NG, "the raw ring needs a stage per dequant group");
+    static_assert(NACC * MT <= ACol0, "accumulators and operand slots share the 512 columns");
+    static constexpr int SmemBytes = Fixed + R * Policy::kRawBytes;
+};
+
+template <int MT, class Policy>
+__global__ void __launch_bounds__(kThreads, 1) umma_linear_ts_kernel(const __grid_constant__ Params p) {
+    using C = CfgTS<MT, Policy>;
+    constexpr int R = C::R, SX = C::SX;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = ptx::smem_addr(smem_raw);
+    const uint32_t base = (raw_addr + 1023u) & ~1023u;   // activation tiles need 1024-byte alignment
+    uint8_t* sbase = smem_raw + (base - raw_addr);
+    const uint32_t x_base = base, raw_base = x_base + SX * C::XStage;
+    const uint32_t bar_base = raw_base + R * Policy::kRawBytes;
+    const uint32_t full_a = bar_base, a_empty = full_a + 8 * C::NSLOT, full_x = a_empty + 8 * C::NSLOT;
+    const uint32_t x_empty = full_x + 8 * SX, raw_full = x_empty + 8 * SX, raw_empty = raw_full + 8 * 8;
+    const uint32_t acc_full = raw_empty + 8 * 8, tmem_slot = acc_full + 8, flag_slot = tmem_slot + 4;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n0 = blockIdx.x * kRows, m0 = blockIdx.y * MT;
+    const int nsplit = gridDim.z, z = blockIdx.z;
+    const int nit_all = p.K / kRawK;
+    const int it_begin = (int)(((long long)z * nit_all) / nsplit), it_end = (int)(((long long)(z + 1) * nit_all) / nsplit);
+    const int nit = it_end - it_begin;     // iterations of 128 k for this CTA
+    int* status = reinterpret_cast<int*>(p.ws);
+
+    AO_UTR(tid == 0, 160);
+    if (tid == 0) {
+        for (int s = 0; s < C::NSLOT; ++s) {
+            ptx::mbar_init(full_a + 8 * s, C::GW);
+            ptx::mbar_init(a_empty + 8 * s, 1);
+        }
+        for (int s = 0; s < SX; ++s) {
+            ptx::mbar_init(full_x + 8 * s, 1);
+            ptx::mbar_init(x_empty + 8 * s, 1);
+        }
+        for (int b = 0; b < R; ++b) {
+            ptx::mbar_init(raw_full + 8 * b, 1);
+            ptx::mbar_init(raw_empty + 8 * b, C::GW);
+        }
+        ptx::mbar_init(acc_full, C::NACC);
+        ptx::fence_mbar_init();
+    }
+    if (warp == 2) {
+        ptx::tmem_alloc(tmem_slot, 512);
+        ptx::tmem_relinquish_alloc_permit();
+    }
+    ptx::tcgen05_fence_before_thread_sync();
+    __syncthreads();
+    ptx::tcgen05_fence_after_thread_sync();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(sbase + (tmem_slot - base));
+    bool ok = true;
+
+    if (warp == 0) {
+        // ---------------- packed weights and scales: one raw stage per iteration ----------------
+        if (lane == 0) {
+            int rb = 0;
+            uint32_t ph = 1;   // a fresh barrier counts as "previous phase complete"
+            for (int it = 0; it < nit; ++it) {
+                if (!ptx::mbar_wait_bounded(raw_empty + 8 * rb, ph, kWaitPolls)) {
+                    ok = false;
+                    break;
+                }
+                Policy::issue_raw(p, raw_base + rb * Policy::kRawBytes, raw_full + 8 * rb, (it_begin + it) * kRawK, n0);
+                if (++rb == R) {
+                    rb = 0;
+                    ph ^= 1u;
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- activations: stage xi holds XK k (one or two 64-k tiles on one barrier) ----------------
+        if (lane == 0) {
+            constexpr int kTiles = C::XK / kKB;
+            const int nstage = nit * (kRawK / C::XK);
+            for (int xi = 0; xi < nstage; ++xi) {
+                const int s = xi & (SX - 1);
+                if (!ptx::mbar_wait_bounded(x_empty + 8 * s, (static_cast<uint32_t>(xi >> C::SXShift) & 1u) ^ 1u, kWaitPolls)) {
+                    ok = false;
+                    break;
+                }
+                ptx::mbar_arrive_expect_tx(full_x + 8 * s, C::XStage);
+#pragma unroll
+                for (int h = 0; h < kTiles; ++h)
+                    ptx::tma_load_2d(x_base + s * C::XStage + h * C::XBytes, &p.map_x,
+                                     ((it_begin * (kRawK / C::XK) + xi) * kTiles + h) * kKB, m0, full_x + 8 * s);
+            }
+        }
+    } else if (warp == 2 || warp == kMmaWarp2) {
+        // ---------------- MMA issue: issuer w takes the iterations w, w + NACC, ... ----------------
+        const int w = warp == 2 ? 0 : 1;
+        constexpr uint32_t idesc = ptx::umma_idesc(kRows, MT, Policy::kBF16, false);
+        if (lane == 0 && w < C::NACC) {
+            for (int it = w; it < nit && ok; it += C::NACC) {
+                const int slot = it & (C::NSLOT - 1);
+                if (!ptx::mbar_wait_bounded(full_a + 8 * slot, static_cast<uint32_t>(it >> 2) & 1u, kWaitPolls)) {
+                    ok = false;
+                    break;
+                }
+                AO_UTR(it < 16, 64 + 2 * it);
+                const uint32_t a_cols = tmem_base + C::ACol0 + slot * C::AColsPerIt;
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    // the 64-k activation tile of this half: its own stage (XK = 64) or half of the iteration's stage
+                    const int xi = C::XK == kKB ? 2 * it + h : it;
+                    const int sx = xi & (SX - 1);
+                    if (C::XK == kKB || h == 0) {
+                        if (!ptx::mbar_wait_bounded(full_x + 8 * sx, static_cast<uint32_t>(xi >> C::SXShift) & 1u, kWaitPolls)) {
+                            ok = false;
+                            break;
+                        }
+                        ptx::tcgen05_fence_after_thread_sync();
+                    }
+                    const uint64_t db = ptx::umma_desc_k_sw128(x_base + sx * C::XStage + (C::XK == kKB ? 0 : h) * C::XBytes);
+#pragma unroll
+                    for (int k4 = 0; k4 < kKB / 16; ++k4)
+                        ptx::umma_f16_ts(tmem_base + w * MT, a_cols + h * (kKB / 2) + k4 * 8, db + 2 * k4, idesc,
+                                         (it >= C::NACC || h != 0 || k4 != 0) ? 1u : 0u);
+                    if (C::XK == kKB || h == 1) ptx::umma_commit(x_empty + 8 * sx);
+                }
+                if (ok) ptx::umma_commit(a_empty + 8 * slot);
+                AO_UTR(it < 16, 96 + 2 * it);
+            }
+            if (ok) ptx::umma_commit(acc_full);
+        }
+    } else {
+        // ---------------- dequantise: group grp takes the iterations grp, grp + 4, ... into operand slot grp; every
+        // thread the weight row of its tensor-memory lane; then the epilogue ----------------
+        const int dw = warp - 3;
+        const int grp = dw >> 2, q = warp & 3;
+        const int row = Policy::out_row(q * 32 + lane);
+        const uint32_t t_slot = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + C::ACol0 + grp * C::AColsPerIt;
+        for (int it = grp; it < nit && ok; it += C::NG) {
+            const int rb = it % R;
+            const uint32_t rph = static_cast<uint32_t>(it / R) & 1u;
+            const uint32_t eph = (static_cast<uint32_t>(it >> 2) & 1u) ^ 1u;
+            if (!ptx::mbar_wait_bounded(raw_full + 8 * rb, rph, kWaitPolls) ||
+                !ptx::mbar_wait_bounded(a_empty + 8 * grp, eph, kWaitPolls)) {
+                ok = false;
+                break;
+            }
+            ptx::tcgen05_fence_after_thread_sync();
+            AO_UTR(q == 0 && lane == 0 && (it >> 2) < 8, 16 * grp + 2 * (it >> 2));
+            Policy::dequant_row(raw_base + rb * Policy::kRawBytes, row, t_slot);
+            ptx::tmem_st_wait();
+            ptx::tcgen05_fence_before_thread_sync();
+            __syncwarp();
+            if (lane == 0) {
+                ptx::mbar_arrive(full_a + 8 * grp);
+                ptx::mbar_arrive(raw_empty + 8 * rb);
+            }
+            AO_UTR(q == 0 && lane == 0 && (it >> 2) < 8, 16 * grp + 2 * (it >> 2) + 1);
+        }
+        if (ok && !ptx::mbar_wait_bounded(acc_full, 0u, kWaitPolls)) ok = false;
+        AO_UTR(dw == 0 && lane == 0, 161);
+        const int nacc_used = nit < C::NACC ? nit : C::NACC;
+        epilogue<MT, Policy, C::NACC, 1>(p, tmem_base, warp, lane, n0, m0, nacc_used, ok,
+                                         reinterpret_cast<volatile int*>(sbase + (flag_slot - base)));
+    }
+    if (!ok && lane == 0) atomicExch(status, AO_ERR_TIMEOUT);
+    AO_UTR(tid == 3 * 32, 162);
+    ptx::tcgen05_fence_before_thread_sync();
+    __syncthreads();
+    if (warp == 2) {
+        ptx::tcgen05_fence_after_thread_sync();
+        ptx::tmem_dealloc(tmem_base, 512);
+    }
+}
+
+template <int MT, class Policy>
+int launch_ts(const Plan& P, const Params& prm, cudaStream_t st) {
+    auto kern = umma_linear_ts_kernel<MT, Policy>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, CfgTS<MT, Policy>::SmemBytes) != cudaSuccess)
+        return AO_ERR_LAUNCH;
+    dim3 grid(P.row_tiles, P.m_tiles, P.nsplit);
+    kern<<<grid, kThreads, CfgTS<MT, Policy>::SmemBytes, st>>>(prm);
+    return launch_status();
+}
+
+// one token tile per CTA: operand in tensor memory; two token tiles per CTA (both accumulators fill tensor memory):
+// operand ring in shared memory
+template <class Policy>
+int launch_mt_ts(const Plan& P, const Params& prm, cudaStream_t st) {
+    static_assert(Policy::kRowDequant, "the weight format has no per-row dequantisation");
+    switch (P.MT) {
+        case 32: return launch_ts<32, Policy>(P, prm, st);
+        case 64: return launch_ts<64, Policy>(P, prm, st);
+        case 128: return launch_ts<128, Policy>(P, prm, st);
+        default: return P.TT == 2 ? launch<256, Policy, 2>(P, prm, st) : launch_ts<256, Policy>(P, prm, st);
+    }
+}
+
+}  // namespace umma
+}  // namespace ao
