@@ -7,7 +7,7 @@
 // m16n8k16 fragment; decode_fragment gives four fp16 registers (value / 2^12) = four 8x8 matrices that one
 // stmatrix writes into the swizzled K-major operand tile.  2^12 * scale[row] is applied to the fp32 accumulator.
 #include "fp6_decode.cuh"
-#include "umma_linear.cuh"
+#include "umma_linear_ts.cuh"
 
 namespace ao {
 namespace umma {
@@ -76,6 +76,52 @@ struct Fp6Policy {
         }
     }
 
+    // Operand in tensor memory: the raw stage as above.
+    static constexpr bool kRowDequant = true;
+    static __device__ __forceinline__ void issue_raw_ts(const Params& p, uint32_t dst, uint32_t bar, int k0, int n0) {
+        issue_raw(p, dst, bar, k0, n0);
+    }
+    // One thread: k = 64 h .. 64 h + 63 (four k16 tiles) of weight row `row` of the CTA's 128.  Row = 64 blk + 16 fr +
+    // 8 rh + e: in every k16 tile the four words of lanes 4e .. 4e + 3 (c = 0..3) of fragment fr hold, in bytes 1 and 3
+    // (rh = 0) or 0 and 2 (rh = 1), the row's codes of k = 2c, 2c + 1 (high nibbles / fields) and 2c + 8, 2c + 9 (low
+    // nibbles / fields): the contents of columns c and c + 4 of the tile's eight.  The same arithmetic as
+    // decode_fragment, for one row of the fragment's two.
+    static __device__ __forceinline__ void dequant_row_half(uint32_t raw, int row, int h, uint32_t t_addr) {
+        const fp6::Format F = fp6::make_format(FMT);
+        const int blk = row >> 6, fr = (row >> 4) & 3, rh = (row >> 3) & 1, e = row & 7;
+        const uint32_t rot_a = rh ? F.rot[1] : F.rot[0], rot_b = rh ? F.rot[3] : F.rot[2];
+        const uint32_t p4 = raw + blk * kBlk + kP2 + fr * 128 + e * 16;
+        uint32_t col[32];
+#pragma unroll
+        for (int jt = 0; jt < 4; ++jt) {
+            const int j = 4 * h + jt;
+            const uint4 q4 = ptx::lds128(p4 + j * 512);
+            const uint32_t w4[4] = {q4.x, q4.y, q4.z, q4.w};
+            if constexpr (kNBits == 6) {
+                const uint4 q2 = ptx::lds128(raw + blk * kBlk + j * kHi + (fr >> 1) * 128 + e * 16);
+                const uint32_t w2[4] = {q2.x, q2.y, q2.z, q2.w};
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const uint32_t t = (fr & 1) ? (w2[c] << 4) : w2[c];   // this fragment's fields in bits 7..4 of every byte
+                    const uint32_t v = rh ? t : (t >> 8);                 // this row's bytes in the place of bytes 0, 2
+                    col[8 * jt + c] = ptx::and_or((v & fp6::kFieldHi) * F.k_hi, F.mh, fp6::rotl(w4[c], rot_a) & F.m4);
+                    col[8 * jt + 4 + c] = ptx::and_or((v & fp6::kFieldLo) * F.k_lo, F.mh, fp6::rotl(w4[c], rot_b) & F.m4);
+                }
+            } else {
+                const uint4 q1 = ptx::lds128(raw + blk * kBlk + j * kHi + e * 16);
+                const uint32_t w1[4] = {q1.x, q1.y, q1.z, q1.w};
+                const uint32_t sgn = 0x80008000u;
+                const int sh = 8 * rh + 2 * fr;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    col[8 * jt + c] = ptx::and_or(w1[c] << sh, sgn, fp6::rotl(w4[c], rot_a) & F.m4);
+                    col[8 * jt + 4 + c] = ptx::and_or(w1[c] << (sh + 1), sgn, fp6::rotl(w4[c], rot_b) & F.m4);
+                }
+            }
+        }
+        ptx::tmem_st_32x32b_x32(t_addr, col);
+    }
+
     static __device__ __forceinline__ int out_row(int row) { return row; }
     static __device__ __forceinline__ float row_scale(const Params& p, int n) {
         return fp6::make_format(FMT).post_scale * __half2float(static_cast<const __half*>(p.scale)[n]);
@@ -115,10 +161,10 @@ int fp6_umma_linear(int fmt, const void* x, int64_t ldx, const uint8_t* packed, 
     prm.N = (int)N;
     prm.K = (int)K;
     switch (fmt) {
-        case fp6::kE3M2: return launch_mt<Fp6Policy<fp6::kE3M2>>(P, prm, st);
-        case fp6::kE2M3: return launch_mt<Fp6Policy<fp6::kE2M3>>(P, prm, st);
-        case fp6::kE2M2: return launch_mt<Fp6Policy<fp6::kE2M2>>(P, prm, st);
-        case fp6::kE3M1: return launch_mt<Fp6Policy<fp6::kE3M1>>(P, prm, st);
+        case fp6::kE3M2: return launch_mt_ts<Fp6Policy<fp6::kE3M2>>(P, prm, st);
+        case fp6::kE2M3: return launch_mt_ts<Fp6Policy<fp6::kE2M3>>(P, prm, st);
+        case fp6::kE2M2: return launch_mt_ts<Fp6Policy<fp6::kE2M2>>(P, prm, st);
+        case fp6::kE3M1: return launch_mt_ts<Fp6Policy<fp6::kE3M1>>(P, prm, st);
     }
     return AO_ERR_UNSUPPORTED;
 }

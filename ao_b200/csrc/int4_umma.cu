@@ -69,44 +69,51 @@ struct TinygemmPolicy {
         }
     }
 
-    // Operand in tensor memory: one thread, weight row `row` of the CTA's 128.  The row's codes sit in the words of the
+    // Operand in tensor memory.  The raw stage is copied as 128-byte lines with the 128-byte swizzle (p.map_z: the packed
+    // weights as uint32 [N/8 tiles][K/32 lines][32 words]): line L = 4 T + r / 2 of the stage holds rows r, r + 1 of
+    // tile T's lanes, and the 16-byte chunk (4 (r % 2) + c) of lane 4r + c sits at chunk position (chunk ^ (L % 8)), so
+    // that the eight rows a quarter-warp reads at once fall into eight different bank groups.
+    static constexpr bool kRowDequant = true;
+    static __device__ __forceinline__ void issue_raw_ts(const Params& p, uint32_t dst, uint32_t bar, int k0, int n0) {
+        ptx::mbar_arrive_expect_tx(bar, kWBytes + kScaleRows * 512);
+        ptx::tma_load_3d(dst, &p.map_z, 0, k0 / 32, n0 / 8, bar);
+        ptx::tma_load_2d(dst + kWBytes, &p.map_s, n0, k0 >> GSHIFT, bar);
+    }
+    // One thread: k = 64 h .. 64 h + 63 of weight row `row` of the CTA's 128.  The row's codes sit in the words of the
     // four lanes 4r .. 4r + 3 of its 8-row tile (r = row % 8): word j of lane 4r + c holds, as the pair (nibble i,
     // nibble i + 4), the codes of k = 32 j + 8 i + 2c and the next k, i.e. the content of column 16 j + 4 i + c.
-    static constexpr bool kRowDequant = true;
-    static __device__ __forceinline__ void dequant_row(uint32_t raw, int row, uint32_t t_addr) {
+    static __device__ __forceinline__ void dequant_row_half(uint32_t raw, int row, int h, uint32_t t_addr) {
         const uint32_t nib = 0x000F000Fu, magic = 0x43004300u, one2 = 0x3F803F80u, m136 = 0xC308C308u;
-        const uint32_t wbase = raw + (row >> 3) * 512 + (row & 7) * 64;
-        uint32_t w[4][4];
+        const int r = row & 7, L = (row >> 3) * 4 + (r >> 1);
+        const uint32_t line = raw + L * 128 + h * 8;
+        const int chunk0 = 4 * (r & 1), key = L & 7;
+        uint32_t w[4][2];
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-            const uint4 v = ptx::lds128(wbase + c * 16);
-            w[c][0] = v.x; w[c][1] = v.y; w[c][2] = v.z; w[c][3] = v.w;
+            const uint2 v = ptx::lds64(line + (((chunk0 + c) ^ key) << 4));   // words j = 2h, 2h + 1 of lane 4r + c
+            w[c][0] = v.x; w[c][1] = v.y;
         }
         // (scale, zero) of this row: group gi of the raw stage at + gi * 512
         const uint32_t sc_addr = raw + kWBytes + row * 4;
+        uint32_t col[32];
+        uint32_t s2 = 0, z2 = 0;
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            uint32_t col[32];
-            uint32_t s2 = 0, z2 = 0;
-#pragma unroll
-            for (int jj = 0; jj < 2; ++jj) {
-                const int j = 2 * h + jj;
-                if (jj == 0 || GSHIFT == 5) {
-                    const int gi = GSHIFT >= 7 ? 0 : (j * 32) >> GSHIFT;
-                    const uint32_t sz = ptx::lds32(sc_addr + gi * (kRows * 4));
-                    s2 = __byte_perm(sz, sz, 0x1010);
-                    z2 = __byte_perm(sz, sz, 0x3232);
-                }
-#pragma unroll
-                for (int i = 0; i < 4; ++i)
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        const uint32_t qv = ptx::and_or(w[c][j] >> (4 * i), nib, magic);      // bf16 pair (128 + q)
-                        col[16 * jj + 4 * i + c] = fma_bf16x2(fma_bf16x2(qv, one2, m136), s2, z2);   // (q - 8) * s + z
-                    }
+        for (int jj = 0; jj < 2; ++jj) {
+            if (jj == 0 || GSHIFT == 5) {
+                const int gi = GSHIFT >= 7 ? 0 : ((2 * h + jj) * 32) >> GSHIFT;
+                const uint32_t sz = ptx::lds32(sc_addr + gi * (kRows * 4));
+                s2 = __byte_perm(sz, sz, 0x1010);
+                z2 = __byte_perm(sz, sz, 0x3232);
             }
-            ptx::tmem_st_32x32b_x32(t_addr + 32 * h, col);
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const uint32_t qv = ptx::and_or(w[c][jj] >> (4 * i), nib, magic);                 // bf16 pair (128 + q)
+                    col[16 * jj + 4 * i + c] = fma_bf16x2(fma_bf16x2(qv, one2, m136), s2, z2);       // (q - 8) * s + z
+                }
         }
+        ptx::tmem_st_32x32b_x32(t_addr, col);
     }
 
     static __device__ __forceinline__ int out_row(int row) { return row; }
@@ -146,7 +153,10 @@ int int4_umma_linear(const void* x, int64_t ldx, int64_t x_cols, const int32_t* 
     if (!make_tensor_map_2d(&prm.map_s, CU_TENSOR_MAP_DATA_TYPE_UINT32, sz, (uint64_t)N, (uint64_t)(K / g), (uint64_t)N * 4,
                             kRows, scale_rows))
         return AO_ERR_LAUNCH;
-    prm.map_z = prm.map_s;
+    // the weights again as 128-byte lines, swizzled, for the kernel that keeps the dequantised operand in tensor memory
+    if (!make_tensor_map_3d(&prm.map_z, CU_TENSOR_MAP_DATA_TYPE_UINT32, packed, 32, (uint64_t)(K / 32), (uint64_t)(N / 8),
+                            128, (uint64_t)K * 4, 32, kRawK / 32, kRows / 8, CU_TENSOR_MAP_SWIZZLE_128B))
+        return AO_ERR_LAUNCH;
     prm.w = packed;
     prm.scale = sz;
     prm.y = y;

@@ -137,6 +137,14 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const void* tenso
         : "memory");
 }
 
+__device__ __forceinline__ void tma_load_3d(uint32_t dst_smem, const void* tensor_map, int x, int y, int z, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(
+            dst_smem),
+        "l"(tensor_map), "r"(x), "r"(y), "r"(z), "r"(bar)
+        : "memory");
+}
+
 // (a & b) | c in one logic instruction; b and c should be runtime values so that they stay in registers
 __device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {
     uint32_t d;
@@ -248,6 +256,13 @@ __device__ __forceinline__ void umma_f16_ss(uint32_t tmem_d, uint64_t desc_a, ui
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
         : "memory");
+}
+
+// whole warp (converged): true in exactly one lane
+__device__ __forceinline__ bool elect_one() {
+    uint32_t p;
+    asm volatile("{\n\t.reg .pred P;\n\telect.sync _|P, 0xffffffff;\n\tselp.u32 %0, 1, 0, P;\n\t}" : "=r"(p));
+    return p != 0;
 }
 
 // D[tmem] (+)= A[tmem] * B[smem desc]: the A operand (128 rows x 16 k of 16-bit elements) sits in tensor memory, row i in

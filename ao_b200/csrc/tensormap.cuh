@@ -38,4 +38,18 @@ inline bool make_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dt, const v
               CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// 3-D tensor: inner extent d0 (contiguous), then d1 with pitch1_bytes, then d2 with pitch2_bytes; box b0 x b1 x b2.
+inline bool make_tensor_map_3d(CUtensorMap* map, CUtensorMapDataType dt, const void* base, uint64_t d0, uint64_t d1,
+                               uint64_t d2, uint64_t pitch1_bytes, uint64_t pitch2_bytes, uint32_t b0, uint32_t b1,
+                               uint32_t b2, CUtensorMapSwizzle swizzle) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[3] = {d0, d1, d2};
+    const cuuint64_t strides[2] = {pitch1_bytes, pitch2_bytes};
+    const cuuint32_t box[3] = {b0, b1, b2};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    return fn(map, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
+              CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 }  // namespace ao

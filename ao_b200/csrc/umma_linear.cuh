@@ -397,65 +397,93 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_kernel(const __grid_c
         const int w = warp == 2 ? 0 : 1;
         constexpr uint32_t idesc = ptx::umma_idesc(kRows, MT, Policy::kBF16, Policy::kAMajorMN);
         constexpr uint32_t a_step = Policy::kAMajorMN ? (2048 >> 4) : (32 >> 4);   // descriptor units per k16
-        if (lane == 0 && w < C::NACC && C::kIter) {
+        // The whole warp walks the loop converged (waits, descriptors: warp-uniform values) and one elected lane issues,
+        // so that the MMAs' operands stay in uniform registers: under `if (lane == 0)` an MMA cost its thread about 100
+        // cycles of operand moves on a scheduler shared with four dequant warps.
+        if (w < C::NACC && C::kIter) {
             // issuer w takes the iterations w, w + NACC, ...: eight MMAs per pair of waits and pair of commits
             for (int it = w; it < nit && ok; it += C::NACC) {
                 const int s0 = (2 * it) & (kS - 1), sx = it & (SX - 1);
-                if (!ptx::mbar_wait_bounded(full_a + 8 * s0, static_cast<uint32_t>((2 * it) >> C::SAShift) & 1u, kWaitPolls) ||
-                    !ptx::mbar_wait_bounded(full_x + 8 * sx, static_cast<uint32_t>(it >> C::SXShift) & 1u, kWaitPolls)) {
+                bool got = ptx::mbar_wait_bounded(full_a + 8 * s0, static_cast<uint32_t>((2 * it) >> C::SAShift) & 1u, kWaitPolls) &&
+                           ptx::mbar_wait_bounded(full_x + 8 * sx, static_cast<uint32_t>(it >> C::SXShift) & 1u, kWaitPolls);
+                got = __all_sync(0xffffffffu, got);   // the warp stays converged even if a wait runs out
+                if (!got) {
                     ok = false;
                     break;
                 }
-                AO_UTR(it < 16, 64 + 2 * it);
                 ptx::tcgen05_fence_after_thread_sync();
+                if (ptx::elect_one()) {
+                    AO_UTR(it < 16, 64 + 2 * it);
 #pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const uint64_t da = Policy::kAMajorMN ? ptx::umma_desc_mn_sw128(a_base + (s0 + h) * kABytes)
-                                                          : ptx::umma_desc_k_sw128(a_base + (s0 + h) * kABytes);
-                    const uint64_t db = ptx::umma_desc_k_sw128(x_base + sx * C::XStage + h * C::XBytes);
+                    for (int h = 0; h < 2; ++h) {
+                        const uint64_t da = Policy::kAMajorMN ? ptx::umma_desc_mn_sw128(a_base + (s0 + h) * kABytes)
+                                                              : ptx::umma_desc_k_sw128(a_base + (s0 + h) * kABytes);
+                        const uint64_t db = ptx::umma_desc_k_sw128(x_base + sx * C::XStage + h * C::XBytes);
 #pragma unroll
-                    for (int k4 = 0; k4 < kKB / 16; ++k4)
-                        ptx::umma_f16_ss(tmem_base + w * MT, da + a_step * k4, db + 2 * k4, idesc,
-                                         (it >= C::NACC || h != 0 || k4 != 0) ? 1u : 0u);
+                        for (int k4 = 0; k4 < kKB / 16; ++k4)
+                            ptx::umma_f16_ss(tmem_base + w * MT, da + a_step * k4, db + 2 * k4, idesc,
+                                             (it >= C::NACC || h != 0 || k4 != 0) ? 1u : 0u);
+                    }
+                    ptx::umma_commit(x_empty + 8 * sx);
+                    ptx::umma_commit(empty + 8 * s0);
+                    AO_UTR(it < 16, 96 + 2 * it);
                 }
-                ptx::umma_commit(x_empty + 8 * sx);
-                ptx::umma_commit(empty + 8 * s0);
-                AO_UTR(it < 16, 96 + 2 * it);
+                __syncwarp();
             }
-            if (ok) ptx::umma_commit(acc_full);
-        } else if (lane == 0 && w < C::NACC) {
+            if (ok && ptx::elect_one()) ptx::umma_commit(acc_full);
+            __syncwarp();
+        } else if (w < C::NACC) {
             for (int kb = w; kb < 2 * nit && ok; kb += C::NACC) {
                 const int s = kb & (kS - 1);
                 const uint32_t ph = static_cast<uint32_t>(kb >> C::SAShift) & 1u;
-                if (!ptx::mbar_wait_bounded(full_a + 8 * s, ph, kWaitPolls)) {
+                // the operand stage and the first token tile's activation stage: the whole warp waits; the elected lane
+                // waits for the second token tile's stage itself, after it has issued the first tile's MMAs
+                bool got = ptx::mbar_wait_bounded(full_a + 8 * s, ph, kWaitPolls) &&
+                           ptx::mbar_wait_bounded(full_x + 8 * ((kb * TT) & (SX - 1)),
+                                                  static_cast<uint32_t>((kb * TT) >> C::SXShift) & 1u, kWaitPolls);
+                got = __all_sync(0xffffffffu, got);
+                if (!got) {
                     ok = false;
                     break;
                 }
-                AO_UTR(kb < 32, 64 + kb);
-                const uint64_t da = Policy::kAMajorMN ? ptx::umma_desc_mn_sw128(a_base + s * kABytes)
-                                                      : ptx::umma_desc_k_sw128(a_base + s * kABytes);
+                ptx::tcgen05_fence_after_thread_sync();
+                if (ptx::elect_one()) {
+                    AO_UTR(kb < 32, 64 + kb);
+                    const uint64_t da = Policy::kAMajorMN ? ptx::umma_desc_mn_sw128(a_base + s * kABytes)
+                                                          : ptx::umma_desc_k_sw128(a_base + s * kABytes);
 #pragma unroll
-                for (int t = 0; t < TT; ++t) {
-                    // token tile t: its x stage against the same operand stage, into its own accumulator columns
-                    const int xi = kb * TT + t, sx = xi & (SX - 1);
-                    if (!ptx::mbar_wait_bounded(full_x + 8 * sx, static_cast<uint32_t>(xi >> C::SXShift) & 1u, kWaitPolls)) {
+                    for (int t = 0; t < TT; ++t) {
+                        // token tile t: its x stage against the same operand stage, into its own accumulator columns
+                        const int xi = kb * TT + t, sx = xi & (SX - 1);
+                        if (t > 0) {
+                            if (!ptx::mbar_wait_bounded(full_x + 8 * sx, static_cast<uint32_t>(xi >> C::SXShift) & 1u, kWaitPolls)) {
+                                got = false;
+                                break;
+                            }
+                            ptx::tcgen05_fence_after_thread_sync();
+                        }
+                        const uint64_t db = ptx::umma_desc_k_sw128(x_base + sx * C::XBytes);
+#pragma unroll
+                        for (int k4 = 0; k4 < kKB / 16; ++k4)
+                            ptx::umma_f16_ss(tmem_base + (t * C::NACC + w) * MT, da + a_step * k4, db + 2 * k4, idesc,
+                                             (kb >= C::NACC || k4 != 0) ? 1u : 0u);
+                        ptx::umma_commit(x_empty + 8 * sx);
+                    }
+                    if (got) ptx::umma_commit(empty + 8 * s);
+                    AO_UTR(kb < 32, 96 + kb);
+                }
+                if (TT > 1) {
+                    got = __all_sync(0xffffffffu, got);   // (also reconverges the warp)
+                    if (!got) {
                         ok = false;
                         break;
                     }
-                    AO_UTR(kb < 32 && t == 0, 256 + kb);
-                    ptx::tcgen05_fence_after_thread_sync();
-                    const uint64_t db = ptx::umma_desc_k_sw128(x_base + sx * C::XBytes);
-#pragma unroll
-                    for (int k4 = 0; k4 < kKB / 16; ++k4)
-                        ptx::umma_f16_ss(tmem_base + (t * C::NACC + w) * MT, da + a_step * k4, db + 2 * k4, idesc,
-                                         (kb >= C::NACC || k4 != 0) ? 1u : 0u);
-                    AO_UTR(kb < 32 && t == 0, 288 + kb);
-                    ptx::umma_commit(x_empty + 8 * sx);
+                } else {
+                    __syncwarp();
                 }
-                if (ok) ptx::umma_commit(empty + 8 * s);
-                AO_UTR(kb < 32, 96 + kb);
             }
-            if (ok) ptx::umma_commit(acc_full);
+            if (ok && ptx::elect_one()) ptx::umma_commit(acc_full);
+            __syncwarp();
         }
     } else {
         // ---------------- dequantise (128 rows x 128 k per iteration), then epilogue ----------------

@@ -10,15 +10,26 @@
 // Tensor memory (512 columns): accumulators in columns [0, 256) (one of 256 columns, or two of up to 128 for the two
 // issuing threads), four operand slots of 64 columns (one iteration each) in [256, 512).
 // What that buys: no operand ring in shared memory (the activation ring and the raw ring get the room: 8 raw stages in
-// flight per SM), no swizzle arithmetic, no proxy fence, per-row scale loads instead of byte permutes; and four
-// iterations in dequantisation at once (four groups of four warps, one warp per lane quarter) against four slots, so a
-// group's wait for the MMAs that read its slot overlaps the other groups' work.
+// flight per SM), no stmatrix address arithmetic, no proxy fence, per-row scale loads instead of byte permutes; and
+// more operand slots (4) than dequant groups (2 groups of 8 warps: two warps per lane quarter, one per 64-k half), so
+// a group never waits for the MMAs that read the slot it has just filled - it goes on with its other slot.
+// MMA issue.  Measured: the tensor pipe runs an MMA for max(N / 2, 45) cycles and a commit for about 50.  The issuing
+// WARP walks its loop converged - waits, descriptors: warp-uniform values - and one elected lane (elect.sync) issues; a
+// loop under `if (lane == 0)` instead costs about 100 cycles per MMA in operand moves on a scheduler shared with four
+// dequant warps, and left the pipe idle between iterations.  Issued this way eight MMAs and their commits take 0.1 us
+// and queue up ahead of the pipe.
+//   * Token tiles of up to 128 columns: two warps issue alternate iterations, each into its own accumulator; the
+//     epilogue adds the two in a fixed order.
+//   * 256 columns (one accumulator): one warp issues.  (Two warps handing a token back and forth after ISSUING their
+//     MMAs do not keep the order of the additions: MMAs of different threads are only ordered by completion.)
+// Either way the order of the additions is fixed: results are bit-reproducible.
 //
 // A weight format takes part by providing, besides what umma_linear.cuh lists,
 //   kRowDequant = true
-//   dequant_row(raw, row, t_addr)   one thread: the 128 k of weight row `row` (0..127 inside the CTA) of the raw stage at
-//                                   `raw` -> 64 columns at tensor-memory address t_addr (two tcgen05.st of 32 columns,
-//                                   executed by the whole warp)
+//   issue_raw_ts(p, dst, bar, k0, n0)       as issue_raw, into the layout dequant_row_half reads
+//   dequant_row_half(raw, row, h, t_addr)   one thread: k = 64 h .. 64 h + 63 of weight row `row` (0..127 inside the CTA)
+//                                           of the raw stage at `raw` -> 32 columns at tensor-memory address t_addr (one
+//                                           tcgen05.st, executed by the whole warp)
 #pragma once
 #include "umma_linear.cuh"
 
@@ -27,22 +38,21 @@ namespace umma {
 
 template <int MT, class Policy>
 struct CfgTS {
-    static constexpr int NACC = MT <= 128 ? 2 : 1;           // issuing threads = accumulators
+    static constexpr int NACC = MT == 256 ? 1 : 2;            // issuing warps = accumulators (added in the epilogue)
     static constexpr int XK = MT <= 128 ? 128 : 64;           // k per activation stage
     static constexpr int XBytes = MT * kKB * 2;               // one 64-k activation tile
     static constexpr int XStage = XBytes * (XK / kKB);
     static constexpr int SX = MT <= 64 ? 8 : 4;               // activation stages (a power of two)
     static constexpr int SXShift = MT <= 64 ? 3 : 2;
-    static constexpr int NG = 4, GW = kDequantWarps / NG;     // dequant groups; one warp per lane quarter in each
-    static constexpr int NSLOT = 4;                           // operand slots in tensor memory, one per group
+    static constexpr int NG = 2, GW = kDequantWarps / NG;     // dequant groups: (lane quarter, 64-k half) per warp
+    static constexpr int NSLOT = 4;                           // operand slots in tensor memory: iteration it uses it % 4
     static constexpr int ACol0 = 256, AColsPerIt = kRawK / 2;
     static constexpr int Fixed = 1024 + SX * XStage + 512;
     static constexpr int Rfit = (kSmemLimit - Fixed) / Policy::kRawBytes;
     static constexpr int R = Rfit > 8 ? 8 : Rfit;
-    static_assert(GW == 4, "a dequant group has one warp per lane quarter of tensor memory");
-    static_assert(NG == NSLOT, "group g owns operand slot g");
-    static_assert(R >= NG, "the raw ring needs a stage per dequant group");
-    static_assert(NACC * MT <= ACol0, "accumulators and operand slots share the 512 columns");
+    static_assert(GW == 8, "a dequant group has two warps per lane quarter of tensor memory");
+    static_assert(NSLOT % NG == 0 && R >= NG, "slots and raw stages per dequant group");
+    static_assert(NACC * MT <= ACol0, "the accumulators and the operand slots share the 512 columns");
     static constexpr int SmemBytes = Fixed + R * Policy::kRawBytes;
 };
 
@@ -104,7 +114,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_ts_kernel(const __gri
                     ok = false;
                     break;
                 }
-                Policy::issue_raw(p, raw_base + rb * Policy::kRawBytes, raw_full + 8 * rb, (it_begin + it) * kRawK, n0);
+                Policy::issue_raw_ts(p, raw_base + rb * Policy::kRawBytes, raw_full + 8 * rb, (it_begin + it) * kRawK, n0);
                 if (++rb == R) {
                     rb = 0;
                     ph ^= 1u;
@@ -133,70 +143,94 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_ts_kernel(const __gri
         // ---------------- MMA issue: issuer w takes the iterations w, w + NACC, ... ----------------
         const int w = warp == 2 ? 0 : 1;
         constexpr uint32_t idesc = ptx::umma_idesc(kRows, MT, Policy::kBF16, false);
-        if (lane == 0 && w < C::NACC) {
+#ifndef AO_UMMA_ELECT
+#define AO_UMMA_ELECT 1
+#endif
+        // The whole warp walks the loop (waits, descriptors: warp-uniform values) and one elected lane issues, so that
+        // the operands of the MMAs can stay in uniform registers.
+        if (w < C::NACC && (AO_UMMA_ELECT || lane == 0)) {
             for (int it = w; it < nit && ok; it += C::NACC) {
+                // everything this iteration reads has to be there
                 const int slot = it & (C::NSLOT - 1);
-                if (!ptx::mbar_wait_bounded(full_a + 8 * slot, static_cast<uint32_t>(it >> 2) & 1u, kWaitPolls)) {
+                const int xi0 = C::XK == kKB ? 2 * it : it;          // first activation stage of the iteration
+                const int sx0 = xi0 & (SX - 1), sx1 = (xi0 + 1) & (SX - 1);
+                bool got = ptx::mbar_wait_bounded(full_a + 8 * slot, static_cast<uint32_t>(it >> 2) & 1u, kWaitPolls) &&
+                           ptx::mbar_wait_bounded(full_x + 8 * sx0, static_cast<uint32_t>(xi0 >> C::SXShift) & 1u, kWaitPolls) &&
+                           (C::XK != kKB ||
+                            ptx::mbar_wait_bounded(full_x + 8 * sx1, static_cast<uint32_t>((xi0 + 1) >> C::SXShift) & 1u, kWaitPolls));
+#if AO_UMMA_ELECT
+                got = __all_sync(0xffffffffu, got);   // the warp stays converged even if a wait runs out
+#endif
+                if (!got) {
                     ok = false;
                     break;
                 }
-                AO_UTR(it < 16, 64 + 2 * it);
                 const uint32_t a_cols = tmem_base + C::ACol0 + slot * C::AColsPerIt;
+                const uint64_t db0 = ptx::umma_desc_k_sw128(x_base + sx0 * C::XStage);
+                const uint64_t db1 = C::XK == kKB ? ptx::umma_desc_k_sw128(x_base + sx1 * C::XStage)
+                                                  : ptx::umma_desc_k_sw128(x_base + sx0 * C::XStage + C::XBytes);
+                ptx::tcgen05_fence_after_thread_sync();
+                const uint32_t d_cols = tmem_base + w * MT;
+                const bool first = it < C::NACC;
+#if AO_UMMA_ELECT
+                if (ptx::elect_one()) {
+#else
+                {
+#endif
+                AO_UTR(it < 32, 64 + it);
 #pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    // the 64-k activation tile of this half: its own stage (XK = 64) or half of the iteration's stage
-                    const int xi = C::XK == kKB ? 2 * it + h : it;
-                    const int sx = xi & (SX - 1);
-                    if (C::XK == kKB || h == 0) {
-                        if (!ptx::mbar_wait_bounded(full_x + 8 * sx, static_cast<uint32_t>(xi >> C::SXShift) & 1u, kWaitPolls)) {
-                            ok = false;
-                            break;
-                        }
-                        ptx::tcgen05_fence_after_thread_sync();
-                    }
-                    const uint64_t db = ptx::umma_desc_k_sw128(x_base + sx * C::XStage + (C::XK == kKB ? 0 : h) * C::XBytes);
+                for (int k4 = 0; k4 < kKB / 16; ++k4)
+                    ptx::umma_f16_ts(d_cols, a_cols + k4 * 8, db0 + 2 * k4, idesc, (!first || k4 != 0) ? 1u : 0u);
+                if (C::XK == kKB) ptx::umma_commit(x_empty + 8 * sx0);
 #pragma unroll
-                    for (int k4 = 0; k4 < kKB / 16; ++k4)
-                        ptx::umma_f16_ts(tmem_base + w * MT, a_cols + h * (kKB / 2) + k4 * 8, db + 2 * k4, idesc,
-                                         (it >= C::NACC || h != 0 || k4 != 0) ? 1u : 0u);
-                    if (C::XK == kKB || h == 1) ptx::umma_commit(x_empty + 8 * sx);
+                for (int k4 = 0; k4 < kKB / 16; ++k4)
+                    ptx::umma_f16_ts(d_cols, a_cols + kKB / 2 + k4 * 8, db1 + 2 * k4, idesc, 1u);
+                ptx::umma_commit(x_empty + 8 * (C::XK == kKB ? sx1 : sx0));
+                ptx::umma_commit(a_empty + 8 * slot);
+                AO_UTR(it < 32, 96 + it);
                 }
-                if (ok) ptx::umma_commit(a_empty + 8 * slot);
-                AO_UTR(it < 16, 96 + 2 * it);
+#if AO_UMMA_ELECT
+                __syncwarp();
+#endif
             }
+#if AO_UMMA_ELECT
+            if (ok && ptx::elect_one()) ptx::umma_commit(acc_full);
+            __syncwarp();
+#else
             if (ok) ptx::umma_commit(acc_full);
+#endif
         }
     } else {
-        // ---------------- dequantise: group grp takes the iterations grp, grp + 4, ... into operand slot grp; every
-        // thread the weight row of its tensor-memory lane; then the epilogue ----------------
+        // ---------------- dequantise: group grp takes the iterations grp, grp + 2, ... (operand slot it % 4); every thread
+        // one 64-k half of the weight row of its tensor-memory lane; then the epilogue ----------------
         const int dw = warp - 3;
-        const int grp = dw >> 2, q = warp & 3;
+        const int grp = dw >> 3, h = (dw >> 2) & 1, q = warp & 3;
         const int row = Policy::out_row(q * 32 + lane);
-        const uint32_t t_slot = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + C::ACol0 + grp * C::AColsPerIt;
+        const uint32_t t_lane_a = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + C::ACol0 + h * (kKB / 2);
         for (int it = grp; it < nit && ok; it += C::NG) {
-            const int rb = it % R;
+            const int rb = it % R, slot = it & (C::NSLOT - 1);
             const uint32_t rph = static_cast<uint32_t>(it / R) & 1u;
             const uint32_t eph = (static_cast<uint32_t>(it >> 2) & 1u) ^ 1u;
             if (!ptx::mbar_wait_bounded(raw_full + 8 * rb, rph, kWaitPolls) ||
-                !ptx::mbar_wait_bounded(a_empty + 8 * grp, eph, kWaitPolls)) {
+                !ptx::mbar_wait_bounded(a_empty + 8 * slot, eph, kWaitPolls)) {
                 ok = false;
                 break;
             }
             ptx::tcgen05_fence_after_thread_sync();
-            AO_UTR(q == 0 && lane == 0 && (it >> 2) < 8, 16 * grp + 2 * (it >> 2));
-            Policy::dequant_row(raw_base + rb * Policy::kRawBytes, row, t_slot);
+            AO_UTR(dw == 8 * grp && lane == 0 && (it >> 1) < 8, 16 * grp + 2 * (it >> 1));
+            Policy::dequant_row_half(raw_base + rb * Policy::kRawBytes, row, h, t_lane_a + slot * C::AColsPerIt);
             ptx::tmem_st_wait();
             ptx::tcgen05_fence_before_thread_sync();
             __syncwarp();
             if (lane == 0) {
-                ptx::mbar_arrive(full_a + 8 * grp);
+                ptx::mbar_arrive(full_a + 8 * slot);
                 ptx::mbar_arrive(raw_empty + 8 * rb);
             }
-            AO_UTR(q == 0 && lane == 0 && (it >> 2) < 8, 16 * grp + 2 * (it >> 2) + 1);
+            AO_UTR(dw == 8 * grp && lane == 0 && (it >> 1) < 8, 16 * grp + 2 * (it >> 1) + 1);
         }
         if (ok && !ptx::mbar_wait_bounded(acc_full, 0u, kWaitPolls)) ok = false;
         AO_UTR(dw == 0 && lane == 0, 161);
-        const int nacc_used = nit < C::NACC ? nit : C::NACC;
+        const int nacc_used = nit < C::NACC ? nit : C::NACC;   // (a single iteration leaves the second accumulator unwritten)
         epilogue<MT, Policy, C::NACC, 1>(p, tmem_base, warp, lane, n0, m0, nacc_used, ok,
                                          reinterpret_cast<volatile int*>(sbase + (flag_slot - base)));
     }
