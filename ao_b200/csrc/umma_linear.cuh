@@ -347,6 +347,10 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_kernel(const __grid_c
     ptx::tcgen05_fence_after_thread_sync();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(sbase + (tmem_slot - base));
     bool ok = true;
+    // Programmatic dependent launch: the next kernel of the stream may start its set-up now; this one reads what the
+    // previous kernel may have written (the activations) only after griddepcontrol.wait in the thread that loads them.
+    // The weights never depend on a previous kernel, so their copies start at once.
+    ptx::grid_launch_dependents();
 
     if (warp == 0) {
         // ---------------- packed weights and scales: one raw stage per iteration ----------------
@@ -368,6 +372,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_kernel(const __grid_c
         }
     } else if (warp == 1) {
         // ---------------- activations: one operand stage per 64 k ----------------
+        if (lane == 0) ptx::grid_dependency_wait();
         if (lane == 0 && C::kIter) {
             // one stage per iteration: the two 64-k tiles of the 128 k, one barrier
             for (int it = 0; it < nit; ++it) {
@@ -528,14 +533,32 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_kernel(const __grid_c
     }
 }
 
+// launch with programmatic stream serialization allowed (see the kernels' griddepcontrol calls)
+template <class Kern>
+int launch_pdl(Kern kern, dim3 grid, int smem_bytes, const Params& prm, cudaStream_t st) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem_bytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, kern, prm) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return AO_ERR_LAUNCH;
+    }
+    return AO_OK;
+}
+
 template <int MT, class Policy, int TT = 1>
 int launch(const Plan& P, const Params& prm, cudaStream_t st) {
     auto kern = umma_linear_kernel<MT, Policy, TT>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<MT, Policy, TT>::SmemBytes) != cudaSuccess)
         return AO_ERR_LAUNCH;
-    dim3 grid(P.row_tiles, P.m_tiles, P.nsplit);
-    kern<<<grid, kThreads, Cfg<MT, Policy, TT>::SmemBytes, st>>>(prm);
-    return launch_status();
+    return launch_pdl(kern, dim3(P.row_tiles, P.m_tiles, P.nsplit), Cfg<MT, Policy, TT>::SmemBytes, prm, st);
 }
 
 template <class Policy>

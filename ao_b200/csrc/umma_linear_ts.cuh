@@ -103,6 +103,10 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_ts_kernel(const __gri
     ptx::tcgen05_fence_after_thread_sync();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(sbase + (tmem_slot - base));
     bool ok = true;
+    // Programmatic dependent launch: the next kernel of the stream may start its set-up now; this one reads what the
+    // previous kernel may have written (the activations) only after griddepcontrol.wait in the thread that loads them.
+    // The weights never depend on a previous kernel, so their copies start at once.
+    ptx::grid_launch_dependents();
 
     if (warp == 0) {
         // ---------------- packed weights and scales: one raw stage per iteration ----------------
@@ -124,6 +128,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_ts_kernel(const __gri
     } else if (warp == 1) {
         // ---------------- activations: stage xi holds XK k (one or two 64-k tiles on one barrier) ----------------
         if (lane == 0) {
+            ptx::grid_dependency_wait();
             constexpr int kTiles = C::XK / kKB;
             const int nstage = nit * (kRawK / C::XK);
             for (int xi = 0; xi < nstage; ++xi) {
@@ -249,9 +254,7 @@ int launch_ts(const Plan& P, const Params& prm, cudaStream_t st) {
     auto kern = umma_linear_ts_kernel<MT, Policy>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, CfgTS<MT, Policy>::SmemBytes) != cudaSuccess)
         return AO_ERR_LAUNCH;
-    dim3 grid(P.row_tiles, P.m_tiles, P.nsplit);
-    kern<<<grid, kThreads, CfgTS<MT, Policy>::SmemBytes, st>>>(prm);
-    return launch_status();
+    return launch_pdl(kern, dim3(P.row_tiles, P.m_tiles, P.nsplit), CfgTS<MT, Policy>::SmemBytes, prm, st);
 }
 
 // one token tile per CTA: operand in tensor memory; two token tiles per CTA (both accumulators fill tensor memory):
