@@ -136,7 +136,7 @@ static bool fp6_shape_ok(int64_t M, int64_t N, int64_t K) {
 
 size_t fp6_umma_workspace_bytes(int64_t M, int64_t N, int64_t K) {
     Plan P;
-    if (!fp6_shape_ok(M, N, K) || !make_plan(M, N, K, &P)) return 0;
+    if (!fp6_shape_ok(M, N, K) || !make_plan(M, N, K, &P, true)) return 0;
     return P.ws_bytes;
 }
 
@@ -144,7 +144,7 @@ size_t fp6_umma_workspace_bytes(int64_t M, int64_t N, int64_t K) {
 int fp6_umma_linear(int fmt, const void* x, int64_t ldx, const uint8_t* packed, const void* scale, int64_t M, int64_t N,
                     int64_t K, void* y, const void* bias, void* ws, size_t ws_bytes, cudaStream_t st) {
     Plan P;
-    if (!fp6_shape_ok(M, N, K) || !make_plan(M, N, K, &P)) return AO_ERR_UNSUPPORTED;
+    if (!fp6_shape_ok(M, N, K) || !make_plan(M, N, K, &P, true)) return AO_ERR_UNSUPPORTED;
     if (!aligned(x, 16) || (ldx * 2) % 16 != 0 || ldx < K || !aligned(packed, 16)) return AO_ERR_UNSUPPORTED;
     if (ws == nullptr || ws_bytes < P.ws_bytes || !aligned(ws, 256)) return AO_ERR_WORKSPACE;
     Params prm{};

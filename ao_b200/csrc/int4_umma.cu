@@ -130,7 +130,7 @@ static bool shape_ok(int64_t M, int64_t N, int64_t K, int g, int ikt) {
 // 0 when this kernel does not take the shape
 size_t int4_umma_workspace_bytes(int64_t M, int64_t N, int64_t K, int g, int ikt) {
     Plan P;
-    if (!shape_ok(M, N, K, g, ikt) || !make_plan(M, N, K, &P)) return 0;
+    if (!shape_ok(M, N, K, g, ikt) || !make_plan(M, N, K, &P, true)) return 0;
     return P.ws_bytes;
 }
 
@@ -139,7 +139,7 @@ int int4_umma_linear(const void* x, int64_t ldx, int64_t x_cols, const int32_t* 
                      int64_t N, int64_t K, int g, int ikt, void* y, const void* bias, void* ws, size_t ws_bytes,
                      cudaStream_t st) {
     Plan P;
-    if (!shape_ok(M, N, K, g, ikt) || !make_plan(M, N, K, &P)) return AO_ERR_UNSUPPORTED;
+    if (!shape_ok(M, N, K, g, ikt) || !make_plan(M, N, K, &P, true)) return AO_ERR_UNSUPPORTED;
     if (!aligned(x, 16) || (ldx * 2) % 16 != 0 || x_cols < 1 || x_cols > K || !aligned(packed, 16) || !aligned(sz, 16))
         return AO_ERR_UNSUPPORTED;
     if (ws == nullptr || ws_bytes < P.ws_bytes || !aligned(ws, 256)) return AO_ERR_WORKSPACE;

@@ -129,7 +129,10 @@ struct Plan {
     size_t ws_bytes;
 };
 
-inline bool make_plan(int64_t M, int64_t N, int64_t K, Plan* P) {
+// operand_in_tmem: the weight format runs token tiles of up to 128 columns with the dequantised operand in tensor memory
+// (umma_linear_ts.cuh); there a 128-column tile runs at the tensor pipe's pace (eight 64-cycle MMAs per iteration) and a
+// 256-column tile does not, so batches that do not get two token tiles per CTA are cut into 128-column tiles.
+inline bool make_plan(int64_t M, int64_t N, int64_t K, Plan* P, bool operand_in_tmem = false) {
     P->MT = M > 128 ? 256 : (M > 64 ? 128 : (M > 32 ? 64 : 32));
     P->row_tiles = (int)((N + kRows - 1) / kRows);
     // Two token tiles per CTA when that shortens the launch: a CTA with two tiles runs about 1.6 times as long as
@@ -142,6 +145,7 @@ inline bool make_plan(int64_t M, int64_t N, int64_t K, Plan* P) {
         const long long waves2 = (P->row_tiles * ((mt1 + 1) / 2) + kNumSMs - 1) / kNumSMs;
         if (waves2 * 16 < waves1 * 10) P->TT = 2;
     }
+    if (operand_in_tmem && P->MT == 256 && P->TT == 1) P->MT = 128;
     P->m_tiles = (int)((M + P->MT * P->TT - 1) / (P->MT * P->TT));
     const long long tiles = (long long)P->row_tiles * P->m_tiles;
     if (tiles > kMaxTiles) return false;
