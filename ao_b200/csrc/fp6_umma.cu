@@ -23,7 +23,8 @@ struct Fp6Policy {
     static constexpr bool kAMajorMN = false;
 
     static __device__ __forceinline__ void issue_raw(const Params& p, uint32_t dst, uint32_t bar, int k0, int n0) {
-        const int nblk = (p.N - n0) >= kRows ? 2 : 1;       // N is a multiple of 64
+        // N is a multiple of 64; a row tile entirely beyond N (the second tile of a CTA with two row tiles) copies nothing
+        const int nblk = (p.N - n0) >= kRows ? 2 : ((p.N - n0) > 0 ? 1 : 0);
         // the first plane (2 bits or 1 bit per code) of every 64-row block comes first, then the 4-bit plane; inside a
         // plane the k16 tiles of one block are contiguous
         const uint8_t* plane2 = static_cast<const uint8_t*>(p.w);

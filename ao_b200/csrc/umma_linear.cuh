@@ -126,6 +126,7 @@ struct Cfg {
 // work split of one call
 struct Plan {
     int MT, TT, nsplit, row_tiles, m_tiles;   // m_tiles: CTAs along M, each covering TT token tiles of MT rows
+    int RT;                                   // row tiles per CTA (2 only with the operand in tensor memory)
     size_t ws_bytes;
 };
 
@@ -146,6 +147,7 @@ inline bool make_plan(int64_t M, int64_t N, int64_t K, Plan* P, bool operand_in_
         if (waves2 * 16 < waves1 * 10) P->TT = 2;
     }
     if (operand_in_tmem && P->MT == 256 && P->TT == 1) P->MT = 128;
+    P->RT = 1;
     P->m_tiles = (int)((M + P->MT * P->TT - 1) / (P->MT * P->TT));
     const long long tiles = (long long)P->row_tiles * P->m_tiles;
     if (tiles > kMaxTiles) return false;
@@ -157,6 +159,10 @@ inline bool make_plan(int64_t M, int64_t N, int64_t K, Plan* P, bool operand_in_
     while (nsplit > 1 && nit / nsplit < 8) --nsplit;
     if (nsplit < 1) nsplit = 1;
     if (P->TT > 1) nsplit = 1;   // (that many tiles fill the machine by themselves)
+    // two row tiles per CTA against one activation stage, when the pairs still fill every SM: 128-column tiles on many
+    // row tiles are otherwise bound by re-reading the activation tile from L2
+    if (operand_in_tmem && P->MT == 128 && nsplit == 1 && (long long)((P->row_tiles + 1) / 2) * P->m_tiles >= kNumSMs)
+        P->RT = 2;
     P->nsplit = nsplit;
     P->ws_bytes = kHeaderBytes + (size_t)kMaxTiles * 4 + (nsplit > 1 ? (size_t)tiles * nsplit * kRows * P->MT * 4 : 0);
     return true;

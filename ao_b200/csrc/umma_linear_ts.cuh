@@ -24,6 +24,12 @@
 //     MMAs do not keep the order of the additions: MMAs of different threads are only ordered by completion.)
 // Either way the order of the additions is fixed: results are bit-reproducible.
 //
+// Two row tiles per CTA (RT = 2, chosen by make_plan for 128-column token tiles on layers with many row tiles): every
+// 128-row weight tile otherwise streams the whole activation tile from L2 (32 KB per iteration per SM at 128 columns,
+// 11 TB/s over 148 SMs - the bound of such shapes).  With RT = 2 a CTA owns 256 weight rows: the work units are (k
+// iteration, row tile) pairs, dequant group g and issuing warp g take row tile g of every iteration, accumulator g IS
+// row tile g's output, and both multiply against the same activation stage, which is released when both have committed.
+//
 // A weight format takes part by providing, besides what umma_linear.cuh lists,
 //   kRowDequant = true
 //   issue_raw_ts(p, dst, bar, k0, n0)       as issue_raw, into the layout dequant_row_half reads
@@ -56,9 +62,10 @@ struct CfgTS {
     static constexpr int SmemBytes = Fixed + R * Policy::kRawBytes;
 };
 
-template <int MT, class Policy>
+template <int MT, class Policy, int RT>
 __global__ void __launch_bounds__(kThreads, 1) umma_linear_ts_kernel(const __grid_constant__ Params p) {
     using C = CfgTS<MT, Policy>;
+    static_assert(RT == 1 || (RT == 2 && C::NACC == 2 && C::XK == kRawK), "two row tiles: one issuing warp and accumulator each");
     constexpr int R = C::R, SX = C::SX;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = ptx::smem_addr(smem_raw);
@@ -70,11 +77,12 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_ts_kernel(const __gri
     const uint32_t x_empty = full_x + 8 * SX, raw_full = x_empty + 8 * SX, raw_empty = raw_full + 8 * 8;
     const uint32_t acc_full = raw_empty + 8 * 8, tmem_slot = acc_full + 8, flag_slot = tmem_slot + 4;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int n0 = blockIdx.x * kRows, m0 = blockIdx.y * MT;
+    const int n0 = blockIdx.x * (kRows * RT), m0 = blockIdx.y * MT;
     const int nsplit = gridDim.z, z = blockIdx.z;
     const int nit_all = p.K / kRawK;
     const int it_begin = (int)(((long long)z * nit_all) / nsplit), it_end = (int)(((long long)(z + 1) * nit_all) / nsplit);
     const int nit = it_end - it_begin;     // iterations of 128 k for this CTA
+    const int nunits = nit * RT;           // work units: unit u = (iteration u / RT, row tile u % RT)
     int* status = reinterpret_cast<int*>(p.ws);
 
     AO_UTR(tid == 0, 160);
@@ -85,7 +93,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_ts_kernel(const __gri
         }
         for (int s = 0; s < SX; ++s) {
             ptx::mbar_init(full_x + 8 * s, 1);
-            ptx::mbar_init(x_empty + 8 * s, 1);
+            ptx::mbar_init(x_empty + 8 * s, RT);   // every issuing warp that reads the stage commits to it
         }
         for (int b = 0; b < R; ++b) {
             ptx::mbar_init(raw_full + 8 * b, 1);
@@ -113,12 +121,13 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_ts_kernel(const __gri
         if (lane == 0) {
             int rb = 0;
             uint32_t ph = 1;   // a fresh barrier counts as "previous phase complete"
-            for (int it = 0; it < nit; ++it) {
+            for (int u = 0; u < nunits; ++u) {
                 if (!ptx::mbar_wait_bounded(raw_empty + 8 * rb, ph, kWaitPolls)) {
                     ok = false;
                     break;
                 }
-                Policy::issue_raw_ts(p, raw_base + rb * Policy::kRawBytes, raw_full + 8 * rb, (it_begin + it) * kRawK, n0);
+                Policy::issue_raw_ts(p, raw_base + rb * Policy::kRawBytes, raw_full + 8 * rb, (it_begin + u / RT) * kRawK,
+                                     n0 + (u % RT) * kRows);
                 if (++rb == R) {
                     rb = 0;
                     ph ^= 1u;
@@ -145,7 +154,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_ts_kernel(const __gri
             }
         }
     } else if (warp == 2 || warp == kMmaWarp2) {
-        // ---------------- MMA issue: issuer w takes the iterations w, w + NACC, ... ----------------
+        // ---------------- MMA issue: issuer w takes the units w, w + NACC, ... ----------------
         const int w = warp == 2 ? 0 : 1;
         constexpr uint32_t idesc = ptx::umma_idesc(kRows, MT, Policy::kBF16, false);
 #ifndef AO_UMMA_ELECT
@@ -154,12 +163,13 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_ts_kernel(const __gri
         // The whole warp walks the loop (waits, descriptors: warp-uniform values) and one elected lane issues, so that
         // the operands of the MMAs can stay in uniform registers.
         if (w < C::NACC && (AO_UMMA_ELECT || lane == 0)) {
-            for (int it = w; it < nit && ok; it += C::NACC) {
-                // everything this iteration reads has to be there
-                const int slot = it & (C::NSLOT - 1);
+            for (int u = w; u < nunits && ok; u += C::NACC) {
+                // everything this unit reads has to be there
+                const int it = u / RT;
+                const int slot = u & (C::NSLOT - 1);
                 const int xi0 = C::XK == kKB ? 2 * it : it;          // first activation stage of the iteration
                 const int sx0 = xi0 & (SX - 1), sx1 = (xi0 + 1) & (SX - 1);
-                bool got = ptx::mbar_wait_bounded(full_a + 8 * slot, static_cast<uint32_t>(it >> 2) & 1u, kWaitPolls) &&
+                bool got = ptx::mbar_wait_bounded(full_a + 8 * slot, static_cast<uint32_t>(u >> 2) & 1u, kWaitPolls) &&
                            ptx::mbar_wait_bounded(full_x + 8 * sx0, static_cast<uint32_t>(xi0 >> C::SXShift) & 1u, kWaitPolls) &&
                            (C::XK != kKB ||
                             ptx::mbar_wait_bounded(full_x + 8 * sx1, static_cast<uint32_t>((xi0 + 1) >> C::SXShift) & 1u, kWaitPolls));
@@ -176,13 +186,13 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_ts_kernel(const __gri
                                                   : ptx::umma_desc_k_sw128(x_base + sx0 * C::XStage + C::XBytes);
                 ptx::tcgen05_fence_after_thread_sync();
                 const uint32_t d_cols = tmem_base + w * MT;
-                const bool first = it < C::NACC;
+                const bool first = u < C::NACC;
 #if AO_UMMA_ELECT
                 if (ptx::elect_one()) {
 #else
                 {
 #endif
-                AO_UTR(it < 32, 64 + it);
+                AO_UTR(u < 32, 64 + u);
 #pragma unroll
                 for (int k4 = 0; k4 < kKB / 16; ++k4)
                     ptx::umma_f16_ts(d_cols, a_cols + k4 * 8, db0 + 2 * k4, idesc, (!first || k4 != 0) ? 1u : 0u);
@@ -192,7 +202,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_ts_kernel(const __gri
                     ptx::umma_f16_ts(d_cols, a_cols + kKB / 2 + k4 * 8, db1 + 2 * k4, idesc, 1u);
                 ptx::umma_commit(x_empty + 8 * (C::XK == kKB ? sx1 : sx0));
                 ptx::umma_commit(a_empty + 8 * slot);
-                AO_UTR(it < 32, 96 + it);
+                AO_UTR(u < 32, 96 + u);
                 }
 #if AO_UMMA_ELECT
                 __syncwarp();
@@ -206,23 +216,23 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_ts_kernel(const __gri
 #endif
         }
     } else {
-        // ---------------- dequantise: group grp takes the iterations grp, grp + 2, ... (operand slot it % 4); every thread
+        // ---------------- dequantise: group grp takes the units grp, grp + 2, ... (operand slot u % 4); every thread
         // one 64-k half of the weight row of its tensor-memory lane; then the epilogue ----------------
         const int dw = warp - 3;
         const int grp = dw >> 3, h = (dw >> 2) & 1, q = warp & 3;
         const int row = Policy::out_row(q * 32 + lane);
         const uint32_t t_lane_a = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + C::ACol0 + h * (kKB / 2);
-        for (int it = grp; it < nit && ok; it += C::NG) {
-            const int rb = it % R, slot = it & (C::NSLOT - 1);
-            const uint32_t rph = static_cast<uint32_t>(it / R) & 1u;
-            const uint32_t eph = (static_cast<uint32_t>(it >> 2) & 1u) ^ 1u;
+        for (int u = grp; u < nunits && ok; u += C::NG) {
+            const int rb = u % R, slot = u & (C::NSLOT - 1);
+            const uint32_t rph = static_cast<uint32_t>(u / R) & 1u;
+            const uint32_t eph = (static_cast<uint32_t>(u >> 2) & 1u) ^ 1u;
             if (!ptx::mbar_wait_bounded(raw_full + 8 * rb, rph, kWaitPolls) ||
                 !ptx::mbar_wait_bounded(a_empty + 8 * slot, eph, kWaitPolls)) {
                 ok = false;
                 break;
             }
             ptx::tcgen05_fence_after_thread_sync();
-            AO_UTR(dw == 8 * grp && lane == 0 && (it >> 1) < 8, 16 * grp + 2 * (it >> 1));
+            AO_UTR(dw == 8 * grp && lane == 0 && (u >> 1) < 8, 16 * grp + 2 * (u >> 1));
             Policy::dequant_row_half(raw_base + rb * Policy::kRawBytes, row, h, t_lane_a + slot * C::AColsPerIt);
             ptx::tmem_st_wait();
             ptx::tcgen05_fence_before_thread_sync();
@@ -231,13 +241,19 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_ts_kernel(const __gri
                 ptx::mbar_arrive(full_a + 8 * slot);
                 ptx::mbar_arrive(raw_empty + 8 * rb);
             }
-            AO_UTR(dw == 8 * grp && lane == 0 && (it >> 1) < 8, 16 * grp + 2 * (it >> 1) + 1);
+            AO_UTR(dw == 8 * grp && lane == 0 && (u >> 1) < 8, 16 * grp + 2 * (u >> 1) + 1);
         }
         if (ok && !ptx::mbar_wait_bounded(acc_full, 0u, kWaitPolls)) ok = false;
         AO_UTR(dw == 0 && lane == 0, 161);
-        const int nacc_used = nit < C::NACC ? nit : C::NACC;   // (a single iteration leaves the second accumulator unwritten)
-        epilogue<MT, Policy, C::NACC, 1>(p, tmem_base, warp, lane, n0, m0, nacc_used, ok,
-                                         reinterpret_cast<volatile int*>(sbase + (flag_slot - base)));
+        volatile int* flag = reinterpret_cast<volatile int*>(sbase + (flag_slot - base));
+        if constexpr (RT == 2) {
+            // accumulator r is row tile r's output (no K slabs in this form)
+            epilogue<MT, Policy, 1, 1>(p, tmem_base, warp, lane, n0, m0, 1, ok, flag);
+            epilogue<MT, Policy, 1, 1>(p, tmem_base + MT, warp, lane, n0 + kRows, m0, 1, ok, flag);
+        } else {
+            const int nacc_used = nit < C::NACC ? nit : C::NACC;   // (a single iteration leaves the second accumulator unwritten)
+            epilogue<MT, Policy, C::NACC, 1>(p, tmem_base, warp, lane, n0, m0, nacc_used, ok, flag);
+        }
     }
     if (!ok && lane == 0) atomicExch(status, AO_ERR_TIMEOUT);
     AO_UTR(tid == 3 * 32, 162);
@@ -249,12 +265,12 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_ts_kernel(const __gri
     }
 }
 
-template <int MT, class Policy>
+template <int MT, class Policy, int RT = 1>
 int launch_ts(const Plan& P, const Params& prm, cudaStream_t st) {
-    auto kern = umma_linear_ts_kernel<MT, Policy>;
+    auto kern = umma_linear_ts_kernel<MT, Policy, RT>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, CfgTS<MT, Policy>::SmemBytes) != cudaSuccess)
         return AO_ERR_LAUNCH;
-    return launch_pdl(kern, dim3(P.row_tiles, P.m_tiles, P.nsplit), CfgTS<MT, Policy>::SmemBytes, prm, st);
+    return launch_pdl(kern, dim3((P.row_tiles + RT - 1) / RT, P.m_tiles, P.nsplit), CfgTS<MT, Policy>::SmemBytes, prm, st);
 }
 
 // one token tile per CTA: operand in tensor memory; two token tiles per CTA (both accumulators fill tensor memory):
@@ -265,7 +281,7 @@ int launch_mt_ts(const Plan& P, const Params& prm, cudaStream_t st) {
     switch (P.MT) {
         case 32: return launch_ts<32, Policy>(P, prm, st);
         case 64: return launch_ts<64, Policy>(P, prm, st);
-        case 128: return launch_ts<128, Policy>(P, prm, st);
+        case 128: return P.RT == 2 ? launch_ts<128, Policy, 2>(P, prm, st) : launch_ts<128, Policy>(P, prm, st);
         default: return P.TT == 2 ? launch<256, Policy, 2>(P, prm, st) : launch_ts<256, Policy>(P, prm, st);
     }
 }

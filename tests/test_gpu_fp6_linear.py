@@ -122,6 +122,24 @@ def test_fp6_prefill_vs_oracle(N, K):
     assert _cabi.workspace_status("cuda") == 0
 
 
+def test_fp6_prefill_two_row_tiles_per_block():
+    """1024 x 4736 (37 row tiles of 128, the last one half full: N % 128 = 0 is not required, N % 64 is): 128-column
+    token tiles with two row tiles per thread block; the last block's second row tile lies beyond N."""
+    from ao_b200 import _cabi, ops
+    from ao_b200.prototype.quant_llm.quant_llm import to_scaled_tc_fpx
+    N, K, M = 4672, 512, 1024
+    w = tu.make_weight((N, K), seed=N + K, dtype=torch.float16, outliers=False)
+    packed_ref, scale_ref = orc.to_scaled_tc_fp6(w.float().numpy())
+    wd = orc.from_scaled_tc_fp6(packed_ref, scale_ref)
+    packed, scale = to_scaled_tc_fpx(w.cuda(), 3, 2)
+    x = torch.randn(M, K, generator=torch.Generator().manual_seed(1)).half()
+    y = ops.fp6_llm_linear(x.cuda(), packed, scale)
+    y_ref = np.ascontiguousarray(x.float().numpy()) @ wd.T
+    assert rel_err(tu.f32(y), y_ref) <= TOL
+    assert torch.equal(y, ops.fp6_llm_linear(x.cuda(), packed, scale))
+    assert _cabi.workspace_status("cuda") == 0
+
+
 def test_e2m3_codec_bit_exact_vs_reference_fixture():
     from ao_b200.prototype.quant_llm.quant_llm import from_scaled_tc_fpx, to_scaled_tc_fpx
     A = gu.load("e2m3.npz")

@@ -64,6 +64,25 @@ def test_prefill_two_token_tiles_per_block(M, g):
     assert _cabi.workspace_status("cuda") == 0
 
 
+@pytest.mark.parametrize("g", [32, 128])
+@pytest.mark.parametrize("M,N,K", [(1024, 4736, 512), (200, 19072, 256)], ids=["1024x4736x512", "200x19072x256"])
+def test_prefill_two_row_tiles_per_block(M, N, K, g):
+    """128-column token tiles on layers with many row tiles run with two row tiles (256 weight rows) per thread block
+    against one activation stage.  Both shapes have an odd number of row tiles (37, 149): the last block's second row
+    tile lies entirely beyond N."""
+    from ao_b200 import _cabi, ops
+    packed, sz, wd = _quantized(N, K, g, seed=M + N + g)
+    x = torch.randn(M, K, generator=torch.Generator().manual_seed(N)).bfloat16()
+    y = ops.weight_int4pack_mm(x.cuda(), packed, g, sz)
+    assert y.shape == (M, N)
+    _check(y, np.ascontiguousarray(x.float().numpy()) @ wd.T, f"M={M}")
+    # the same rows in batches of 64 (one row tile per block, 64-column tiles): within tolerance of each other
+    y64 = torch.cat([ops.weight_int4pack_mm(x[i:i + 64].cuda(), packed, g, sz) for i in range(0, M, 64)])
+    _check(y64, tu.f32(y), "64 rows at a time")
+    assert torch.equal(y, ops.weight_int4pack_mm(x.cuda(), packed, g, sz)), "two runs must give identical bits"
+    assert _cabi.workspace_status("cuda") == 0
+
+
 def test_prefill_matches_decode_kernel_rows():
     """The same activation rows through the decode kernel (16 at a time) and through the prefill kernel."""
     from ao_b200 import ops
