@@ -6,7 +6,7 @@
 // a thread takes 8 bytes (8 consecutive n of one k pair), reorders the bytes with one prmt so that a masked
 // shift yields (n, n+1) pairs, turns codes into 16-bit floats with one logic op per pair, applies
 // (q - z) * s as q * s - z * s with two fp16x2/bf16x2 FMAs and stores one 16-byte chunk per k.
-#include "umma_linear.cuh"
+#include "umma_linear_ts.cuh"
 
 namespace ao {
 namespace umma {
@@ -97,17 +97,62 @@ struct HqqPolicy {
         }
     }
 
+    // Operand in tensor memory (forward orientation only): the raw stage as above.
+    static constexpr bool kRowDequant = !TRANSPOSED;
+    static __device__ __forceinline__ void issue_raw_ts(const Params& p, uint32_t dst, uint32_t bar, int k0, int n0) {
+        issue_raw(p, dst, bar, k0, n0);
+    }
+    // One thread: k = 64 h .. 64 h + 63 of weight row (column of the packed matrix) n = `row` of the CTA's 128.  Byte
+    // row r of the raw stage holds, at byte n, the codes of k = 2r (low nibble) and 2r + 1 (high nibble): exactly one
+    // column of the operand in tensor memory.  b * 0x1001 puts the low nibble at bits 3..0 and the high one at 19..16.
+    // A warp's 32 threads read 32 consecutive bytes: one shared-memory wavefront per load, 32 loads per thread.
+    static __device__ __forceinline__ void dequant_row_half(uint32_t raw, int row, int h, uint32_t t_addr) {
+        const uint32_t nib = 0x000F000Fu;
+        const uint32_t magic = BF16 ? 0x43004300u : 0x64006400u;
+        const uint32_t one2 = BF16 ? 0x3F803F80u : 0x3C003C00u;
+        const uint32_t moff = BF16 ? 0xC300C300u : 0xE400E400u;
+        const uint32_t baddr = raw + (32 * h) * 128 + row;
+        const uint32_t sc_addr = raw + kWBytes + row * 2;
+        uint32_t col[32];
+        uint32_t s2 = 0, nzs2 = 0;
+#pragma unroll
+        for (int kk = 0; kk < 32; ++kk) {
+            // (scale, -(zero * scale)) of the group that holds k = 64 h + 2 kk, both halves of the register alike
+            if (kk == 0 || (GSHIFT == 5 && (kk & 15) == 0)) {
+                const int gi = GSHIFT >= 7 ? 0 : (64 * h + 2 * kk) >> GSHIFT;
+                const uint32_t sv = ptx::lds_u16(sc_addr + gi * 256), zv = ptx::lds_u16(sc_addr + 1024 + gi * 256);
+                s2 = sv | (sv << 16);
+                const uint32_t z2 = zv | (zv << 16);
+                nzs2 = fma2<BF16>(z2, s2, 0u) ^ 0x80008000u;   // -(z * s), rounded once
+            }
+            const uint32_t b = ptx::lds_u8(baddr + kk * 128);
+            const uint32_t qv = ptx::and_or(b * 0x1001u, nib, magic);
+            col[kk] = fma2<BF16>(fma2<BF16>(qv, one2, moff), s2, nzs2);   // (q - z) * s as q * s - z * s
+        }
+        ptx::tmem_st_32x32b_x32(t_addr, col);
+    }
+
     static __device__ __forceinline__ int out_row(int row) { return row; }
     static __device__ __forceinline__ float row_scale(const Params&, int) { return 1.f; }
 };
 
+// forward orientation: operand in tensor memory (one token tile per CTA) or the shared-memory ring (two token tiles);
+// transposed: the shared-memory ring
+template <class Policy>
+static int launch_hqq(const Plan& P, const Params& prm, cudaStream_t st) {
+    if constexpr (Policy::kRowDequant)
+        return launch_mt_ts<Policy>(P, prm, st);
+    else
+        return launch_mt<Policy>(P, prm, st);
+}
+
 template <bool BF16, bool TRANSPOSED>
 static int launch_g(const Plan& P, int g, const Params& prm, cudaStream_t st) {
     switch (g) {
-        case 32: return launch_mt<HqqPolicy<5, BF16, TRANSPOSED>>(P, prm, st);
-        case 64: return launch_mt<HqqPolicy<6, BF16, TRANSPOSED>>(P, prm, st);
-        case 128: return launch_mt<HqqPolicy<7, BF16, TRANSPOSED>>(P, prm, st);
-        default: return launch_mt<HqqPolicy<8, BF16, TRANSPOSED>>(P, prm, st);
+        case 32: return launch_hqq<HqqPolicy<5, BF16, TRANSPOSED>>(P, prm, st);
+        case 64: return launch_hqq<HqqPolicy<6, BF16, TRANSPOSED>>(P, prm, st);
+        case 128: return launch_hqq<HqqPolicy<7, BF16, TRANSPOSED>>(P, prm, st);
+        default: return launch_hqq<HqqPolicy<8, BF16, TRANSPOSED>>(P, prm, st);
     }
 }
 
@@ -133,7 +178,7 @@ using namespace ao;
 
 extern "C" size_t ao_hqq_int4_linear_workspace_bytes(int64_t M, int64_t N, int64_t K, int group) {
     umma::Plan P;
-    if (!umma::hqq_shape_ok(M, N, K, group) || !umma::make_plan(M, N, K, &P)) return 0;
+    if (!umma::hqq_shape_ok(M, N, K, group) || !umma::make_plan(M, N, K, &P, true)) return 0;
     return P.ws_bytes;
 }
 
@@ -144,7 +189,7 @@ extern "C" int ao_hqq_int4_linear(const void* a, int a_dtype, int64_t a_row_stri
     if (a_dtype != AO_BF16 && a_dtype != AO_F16) return AO_ERR_DTYPE;
     umma::Plan P;
     if (!umma::hqq_shape_ok(M, N, K, group)) return AO_ERR_SHAPE;
-    if (!umma::make_plan(M, N, K, &P)) return AO_ERR_UNSUPPORTED;
+    if (!umma::make_plan(M, N, K, &P, true)) return AO_ERR_UNSUPPORTED;
     if (!aligned(a, 16) || (a_row_stride * 2) % 16 != 0 || a_row_stride < K || !aligned(b_packed, 16) ||
         !aligned(scales, 16) || !aligned(zeros, 16) || !aligned(c, 2))
         return AO_ERR_ALIGN;
