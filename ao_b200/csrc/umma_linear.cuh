@@ -52,7 +52,7 @@ namespace umma {
 // thread has the activation stage; 288 + kb: MMAs issued, before the commits.
 #if defined(AO_UMMA_TRACE) && AO_UMMA_TRACE
 static __device__ unsigned long long g_utrace[512];
-#define AO_UTR(cond, slot) do { if ((cond) && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (slot) < 512) g_utrace[(slot)] = ptx::globaltimer_ns(); } while (0)
+#define AO_UTR(cond, slot) do { if ((cond) && blockIdx.x == 0 && (slot) < 512) g_utrace[(slot)] = ptx::globaltimer_ns(); } while (0)
 #else
 #define AO_UTR(cond, slot) do { } while (0)
 #endif
@@ -81,7 +81,35 @@ struct alignas(64) Params {
     uint8_t* ws;
     int M, N, K;
     const void* bias;    // optional [N] in the output dtype: y = round(round(acc) + bias), the bits of an unfused add
+    int grid_x, full_tiles, tail_split;   // the launch's schedule (Plan), filled in by launch()
 };
+
+// What a CTA works on.  The grid is one-dimensional: CTA b < full_tiles takes output tile b with the whole K range;
+// after them every remaining tile appears tail_split times, once per K slab.  Tiles are numbered with the row-tile
+// index fastest (tile = bx + grid_x * by).
+struct Work {
+    int bx, by, z, nsplit, slot_tile;   // slot_tile: index among the tiles that have K slabs (workspace slots, counters)
+};
+__device__ __forceinline__ Work work_of_cta(const Params& p) {
+    Work w;
+    int tile;
+    const int b = blockIdx.x;
+    if (b < p.full_tiles) {
+        tile = b;
+        w.z = 0;
+        w.nsplit = 1;
+        w.slot_tile = 0;
+    } else {
+        const int j = b - p.full_tiles;
+        w.slot_tile = j / p.tail_split;
+        w.z = j - w.slot_tile * p.tail_split;
+        w.nsplit = p.tail_split;
+        tile = p.full_tiles + w.slot_tile;
+    }
+    w.by = tile / p.grid_x;
+    w.bx = tile - w.by * p.grid_x;
+    return w;
+}
 
 #ifndef AO_UMMA_NG_SMALL
 #define AO_UMMA_NG_SMALL 4
@@ -125,8 +153,10 @@ struct Cfg {
 
 // work split of one call
 struct Plan {
-    int MT, TT, nsplit, row_tiles, m_tiles;   // m_tiles: CTAs along M, each covering TT token tiles of MT rows
-    int RT;                                   // row tiles per CTA (2 only with the operand in tensor memory)
+    int MT, TT, row_tiles, m_tiles;   // m_tiles: CTAs along M, each covering TT token tiles of MT rows
+    int RT;                           // row tiles per CTA (2 only with the operand in tensor memory)
+    int grid_x;                       // CTAs along N = ceil(row_tiles / RT); output tiles = grid_x * m_tiles
+    int full_tiles, tail_tiles, tail_split;   // tiles run whole / tiles cut into tail_split K slabs (see work_of_cta)
     size_t ws_bytes;
 };
 
@@ -147,24 +177,45 @@ inline bool make_plan(int64_t M, int64_t N, int64_t K, Plan* P, bool operand_in_
         if (waves2 * 16 < waves1 * 10) P->TT = 2;
     }
     if (operand_in_tmem && P->MT == 256 && P->TT == 1) P->MT = 128;
-    P->RT = 1;
     P->m_tiles = (int)((M + P->MT * P->TT - 1) / (P->MT * P->TT));
-    const long long tiles = (long long)P->row_tiles * P->m_tiles;
-    if (tiles > kMaxTiles) return false;
-    // K slabs over gridDim.z when the tiles alone leave SMs idle; every slab keeps at least 8 iterations of 128 k
-    int nsplit = (int)(kNumSMs / tiles);
+    if ((long long)P->row_tiles * P->m_tiles > kMaxTiles) return false;
     const int nit = (int)(K / kRawK);
-    if (nsplit > kMaxSplit) nsplit = kMaxSplit;
-    if (P->MT == 256 && nsplit > 2) nsplit = 2;
-    while (nsplit > 1 && nit / nsplit < 8) --nsplit;
-    if (nsplit < 1) nsplit = 1;
-    if (P->TT > 1) nsplit = 1;   // (that many tiles fill the machine by themselves)
     // two row tiles per CTA against one activation stage, when the pairs still fill every SM: 128-column tiles on many
     // row tiles are otherwise bound by re-reading the activation tile from L2
-    if (operand_in_tmem && P->MT == 128 && nsplit == 1 && (long long)((P->row_tiles + 1) / 2) * P->m_tiles >= kNumSMs)
-        P->RT = 2;
-    P->nsplit = nsplit;
-    P->ws_bytes = kHeaderBytes + (size_t)kMaxTiles * 4 + (nsplit > 1 ? (size_t)tiles * nsplit * kRows * P->MT * 4 : 0);
+    P->RT = 1;
+    if (operand_in_tmem && P->MT == 128 && P->TT == 1 && (long long)((P->row_tiles + 1) / 2) * P->m_tiles >= kNumSMs) P->RT = 2;
+    P->grid_x = (P->row_tiles + P->RT - 1) / P->RT;
+    const int tiles = P->grid_x * P->m_tiles;
+    // K slabs.  The grid runs in waves of one CTA per SM, so what counts is the number of waves times the length of
+    // a CTA: in iterations of 128 k, nit / s plus a fixed part (set-up and epilogue; with slabs the fp32 partial tile
+    // goes through the workspace, which costs more the wider the tile).  Either every tile is cut into s slabs, or only
+    // the tiles of the last, partly filled wave are (the CTAs of the whole waves come first in the grid).
+    P->full_tiles = tiles;
+    P->tail_tiles = 0;
+    P->tail_split = 1;
+    if (P->TT == 1 && P->RT == 1) {
+        const int smax = P->MT == 256 ? 2 : kMaxSplit;
+        const double fixed1 = 6.0, fixed_s = 8.0 + P->MT / 16.0;
+        const int whole = (tiles / kNumSMs) * kNumSMs;
+        double best = (double)((tiles + kNumSMs - 1) / kNumSMs) * (nit + fixed1);
+        for (int full = 0; full <= whole; full += (whole > 0 ? whole : 1)) {
+            const int rem = tiles - full;
+            if (rem == 0) continue;
+            for (int sp = 2; sp <= smax && nit / sp >= 8; ++sp) {
+                const double cost = (double)(full / kNumSMs) * (nit + fixed1) +
+                                    (double)((rem * sp + kNumSMs - 1) / kNumSMs) * ((double)nit / sp + fixed_s);
+                if (cost < best - 1e-9) {
+                    best = cost;
+                    P->full_tiles = full;
+                    P->tail_tiles = rem;
+                    P->tail_split = sp;
+                }
+            }
+            if (whole == 0) break;
+        }
+    }
+    P->ws_bytes = kHeaderBytes + (size_t)kMaxTiles * 4 +
+                  (P->tail_split > 1 ? (size_t)P->tail_tiles * P->tail_split * kRows * P->MT * 4 : 0);
     return true;
 }
 
@@ -216,10 +267,10 @@ __device__ __forceinline__ float load_bias(const void* bias, int n) {
 // ((warp - 3) / 4) of the accumulator(s) -> y, or, with K slabs, -> this slab's workspace slot, after which the CTA that
 // completes the tile adds the slabs in order.  flag: a word of shared memory for the "last slab" broadcast.
 template <int MT, class Policy, int NACC, int TT>
-__device__ __forceinline__ void epilogue(const Params& p, uint32_t tmem_base, int warp, int lane, int n0, int m0,
-                                         int nacc_used, bool ok, volatile int* flag) {
+__device__ __forceinline__ void epilogue(const Params& p, const Work& wk, uint32_t tmem_base, int warp, int lane, int n0,
+                                         int m0, int nacc_used, bool ok, volatile int* flag) {
     const int M = p.M, N = p.N;
-    const int nsplit = gridDim.z, z = blockIdx.z;
+    const int nsplit = wk.nsplit, z = wk.z;
     const int tid = threadIdx.x, dw = warp - 3;
     const int q = warp & 3, part = dw >> 2;
     const int row = q * 32 + lane;              // tensor-memory lane
@@ -256,7 +307,7 @@ __device__ __forceinline__ void epilogue(const Params& p, uint32_t tmem_base, in
     } else {
         // K slabs: fp32 partial tile [column][lane] into this slab's workspace slot; the CTA that completes the
         // tile (atomic counter) adds the slabs in order and stores; the counter is left at zero.
-        const int tile_id = blockIdx.y * gridDim.x + blockIdx.x;
+        const int tile_id = wk.slot_tile;
         float* slots = reinterpret_cast<float*>(p.ws + kHeaderBytes + (size_t)kMaxTiles * 4);
         const size_t slot_elems = (size_t)kRows * MT;
         float* mine = slots + ((size_t)tile_id * nsplit + z) * slot_elems;
@@ -324,8 +375,9 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_kernel(const __grid_c
     const uint32_t raw_full = x_empty + 8 * SX, raw_empty = raw_full + 8 * 8, acc_full = raw_empty + 8 * 8;
     const uint32_t tmem_slot = acc_full + 8, flag_slot = tmem_slot + 4;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int n0 = blockIdx.x * kRows, m0 = blockIdx.y * (MT * TT);   // first row of the CTA's first token tile
-    const int nsplit = gridDim.z, z = blockIdx.z;
+    const Work wk = work_of_cta(p);
+    const int n0 = wk.bx * kRows, m0 = wk.by * (MT * TT);   // first row of the CTA's first token tile
+    const int nsplit = wk.nsplit, z = wk.z;
     const int nit_all = p.K / kRawK;
     const int it_begin = (int)(((long long)z * nit_all) / nsplit), it_end = (int)(((long long)(z + 1) * nit_all) / nsplit);
     const int nit = it_end - it_begin;     // iterations of 128 k for this CTA
@@ -530,7 +582,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_kernel(const __grid_c
         if (ok && !ptx::mbar_wait_bounded(acc_full, 0u, kWaitPolls)) ok = false;
         AO_UTR(dw == 0 && lane == 0, 161);
         const int nacc_used = C::kIter ? (nit < C::NACC ? nit : C::NACC) : C::NACC;
-        epilogue<MT, Policy, C::NACC, TT>(p, tmem_base, warp, lane, n0, m0, nacc_used, ok,
+        epilogue<MT, Policy, C::NACC, TT>(p, wk, tmem_base, warp, lane, n0, m0, nacc_used, ok,
                                           reinterpret_cast<volatile int*>(sbase + (flag_slot - base)));
     }
     if (!ok && lane == 0) atomicExch(status, AO_ERR_TIMEOUT);
@@ -545,9 +597,13 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_kernel(const __grid_c
 
 // launch with programmatic stream serialization allowed (see the kernels' griddepcontrol calls)
 template <class Kern>
-int launch_pdl(Kern kern, dim3 grid, int smem_bytes, const Params& prm, cudaStream_t st) {
+int launch_pdl(Kern kern, const Plan& P, int smem_bytes, const Params& prm_in, cudaStream_t st) {
+    Params prm = prm_in;
+    prm.grid_x = P.grid_x;
+    prm.full_tiles = P.full_tiles;
+    prm.tail_split = P.tail_split;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid;
+    cfg.gridDim = dim3(P.full_tiles + P.tail_tiles * P.tail_split);
     cfg.blockDim = dim3(kThreads);
     cfg.dynamicSmemBytes = smem_bytes;
     cfg.stream = st;
@@ -568,7 +624,7 @@ int launch(const Plan& P, const Params& prm, cudaStream_t st) {
     auto kern = umma_linear_kernel<MT, Policy, TT>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<MT, Policy, TT>::SmemBytes) != cudaSuccess)
         return AO_ERR_LAUNCH;
-    return launch_pdl(kern, dim3(P.row_tiles, P.m_tiles, P.nsplit), Cfg<MT, Policy, TT>::SmemBytes, prm, st);
+    return launch_pdl(kern, P, Cfg<MT, Policy, TT>::SmemBytes, prm, st);
 }
 
 template <class Policy>

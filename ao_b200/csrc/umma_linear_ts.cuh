@@ -77,8 +77,9 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_ts_kernel(const __gri
     const uint32_t x_empty = full_x + 8 * SX, raw_full = x_empty + 8 * SX, raw_empty = raw_full + 8 * 8;
     const uint32_t acc_full = raw_empty + 8 * 8, tmem_slot = acc_full + 8, flag_slot = tmem_slot + 4;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int n0 = blockIdx.x * (kRows * RT), m0 = blockIdx.y * MT;
-    const int nsplit = gridDim.z, z = blockIdx.z;
+    const Work wk = work_of_cta(p);
+    const int n0 = wk.bx * (kRows * RT), m0 = wk.by * MT;
+    const int nsplit = wk.nsplit, z = wk.z;
     const int nit_all = p.K / kRawK;
     const int it_begin = (int)(((long long)z * nit_all) / nsplit), it_end = (int)(((long long)(z + 1) * nit_all) / nsplit);
     const int nit = it_end - it_begin;     // iterations of 128 k for this CTA
@@ -248,11 +249,11 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_ts_kernel(const __gri
         volatile int* flag = reinterpret_cast<volatile int*>(sbase + (flag_slot - base));
         if constexpr (RT == 2) {
             // accumulator r is row tile r's output (no K slabs in this form)
-            epilogue<MT, Policy, 1, 1>(p, tmem_base, warp, lane, n0, m0, 1, ok, flag);
-            epilogue<MT, Policy, 1, 1>(p, tmem_base + MT, warp, lane, n0 + kRows, m0, 1, ok, flag);
+            epilogue<MT, Policy, 1, 1>(p, wk, tmem_base, warp, lane, n0, m0, 1, ok, flag);
+            epilogue<MT, Policy, 1, 1>(p, wk, tmem_base + MT, warp, lane, n0 + kRows, m0, 1, ok, flag);
         } else {
             const int nacc_used = nit < C::NACC ? nit : C::NACC;   // (a single iteration leaves the second accumulator unwritten)
-            epilogue<MT, Policy, C::NACC, 1>(p, tmem_base, warp, lane, n0, m0, nacc_used, ok, flag);
+            epilogue<MT, Policy, C::NACC, 1>(p, wk, tmem_base, warp, lane, n0, m0, nacc_used, ok, flag);
         }
     }
     if (!ok && lane == 0) atomicExch(status, AO_ERR_TIMEOUT);
@@ -270,7 +271,7 @@ int launch_ts(const Plan& P, const Params& prm, cudaStream_t st) {
     auto kern = umma_linear_ts_kernel<MT, Policy, RT>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, CfgTS<MT, Policy>::SmemBytes) != cudaSuccess)
         return AO_ERR_LAUNCH;
-    return launch_pdl(kern, dim3((P.row_tiles + RT - 1) / RT, P.m_tiles, P.nsplit), CfgTS<MT, Policy>::SmemBytes, prm, st);
+    return launch_pdl(kern, P, CfgTS<MT, Policy>::SmemBytes, prm, st);
 }
 
 // one token tile per CTA: operand in tensor memory; two token tiles per CTA (both accumulators fill tensor memory):
