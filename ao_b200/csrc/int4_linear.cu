@@ -1,5 +1,10 @@
-// Dispatcher of the int4 tensor_core_tiled linear: decode shapes (M <= 8) go to the GEMV kernel, larger
-// batches to the tcgen05 kernel; shapes that kernel does not take run as row blocks of 16 through the GEMV.
+// Dispatcher of the int4 tensor_core_tiled linear: a single row and the smallest batches go to the GEMV kernel,
+// larger batches to the tcgen05 kernel; shapes that kernel does not take run as row blocks of 16 through the GEMV.
+// Where the line is (measured on B200, both kernels on the same weights): the tcgen05 kernel at 16 columns costs
+// 8.3 / 7.2 / 23.5 / 13.3 us on the Llama-3-8B layers (qkv, o, gate_up, down) whatever M <= 16 is; the GEMV costs
+// 7.3 / 6.2 / 19.2 / 16.3 us at M = 2, 8.7 / 7.4 / 20.5 / 20.2 at M = 4 and 11.0 / 9.8 / 24.1 / 21.2 at M = 8.  So: M >= 5
+// always, and from M = 2 where the reduction is long against the number of rows (K >= 2 N: the GEMV then needs K
+// slabs or long activation prologues).
 #include "common.cuh"
 
 namespace ao {
@@ -11,9 +16,11 @@ int int4_umma_linear(const void* x, int64_t ldx, int64_t x_cols, const int32_t* 
 }
 }  // namespace ao
 
+static bool prefers_tcgen05(int64_t M, int64_t N, int64_t K) { return M >= 5 || (M >= 2 && K >= 2 * N); }
+
 extern "C" size_t ao_int4_tinygemm_linear_workspace_bytes(int64_t M, int64_t N, int64_t K, int group,
                                                           int inner_k_tiles) {
-    if (M <= 8) return ao_int4_gemv_workspace_bytes(M, N, K, group, inner_k_tiles);
+    if (M <= 8 && !prefers_tcgen05(M, N, K)) return ao_int4_gemv_workspace_bytes(M, N, K, group, inner_k_tiles);
     // larger batches: the tcgen05 kernel's need, and the decode kernel's for shapes that fall back to row blocks
     size_t need = ao::umma::int4_umma_workspace_bytes(M, N, K, group, inner_k_tiles);
     for (int m = 1; m <= 16; m *= 2) {
@@ -35,7 +42,7 @@ extern "C" int ao_int4_tinygemm_linear_bias(const void* x_bf16, int64_t x_row_st
                                             const void* bias_bf16, void* workspace, size_t workspace_bytes,
                                             ao_stream_t stream) {
     if (M < 0 || N < 0) return AO_ERR_SHAPE;
-    if (M <= 8)
+    if (M <= 8 && !prefers_tcgen05(M, N, K))
         return ao_int4_gemv_bias(x_bf16, x_row_stride, x_cols, packed, scale_and_zero, M, N, K, group, inner_k_tiles, y_bf16,
                                  bias_bf16, workspace, workspace_bytes, stream);
     if (workspace == nullptr || workspace_bytes < 256 || !ao::aligned(workspace, 256)) return AO_ERR_WORKSPACE;

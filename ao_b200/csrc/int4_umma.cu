@@ -1,4 +1,4 @@
-// Prefill-shaped int4 weight-only linear (M > 8) on the tensor_core_tiled weight layout, replacing
+// Batched int4 weight-only linear (M >= 2; the dispatcher sends M >= 5 here) on the tensor_core_tiled weight layout, replacing
 // aten::_weight_int4pack_mm as called at torchao/dtypes/affine_quantized_tensor.py:631 for large batches.
 // The pipeline is umma_linear.cuh; this file is the weight format's policy and the host entry.
 //
@@ -121,7 +121,7 @@ struct TinygemmPolicy {
 };
 
 static bool shape_ok(int64_t M, int64_t N, int64_t K, int g, int ikt) {
-    if (ikt != 8 || M <= 8 || N < kRows || N % 8 != 0 || K % 128 != 0 || K < 128) return false;
+    if (ikt != 8 || M < 2 || N < kRows || N % 8 != 0 || K % 128 != 0 || K < 128) return false;
     if (!(g == 32 || g == 64 || g == 128 || g == 256) || K % g != 0) return false;
     if (M > (1 << 30) || N > (1 << 30) || K > (1 << 24)) return false;
     return true;
