@@ -667,9 +667,14 @@ int gemv(int fmt, const void* x_f16, int64_t x_row_stride, const uint8_t* packed
     return AO_ERR_UNSUPPORTED;
 }
 
-// decode shapes go to the GEMV kernel, larger batches to the tcgen05 kernel, the rest in row blocks of 16
+// A single row and the smallest batches go to the GEMV kernel, larger batches to the tcgen05 kernel, the rest in row
+// blocks of 16.  Measured on B200 (e3m2, 12288x4096 / 4096x4096 / 11008x4096 / 4096x11008): the tcgen05 kernel at 16
+// columns takes 17.1 / 8.4 / 17.0 / 15.2 us whatever M <= 16 is, the GEMV 16.4 / 9.3 / 16.5 / 17.6 at M = 4 and 17.7 /
+// 10.6 / 17.6 / 25.2 at M = 8: so M >= 5 always, and from M = 2 on long reductions (K >= 2 N).
+bool prefers_tcgen05(int64_t M, int64_t N, int64_t K) { return M >= 5 || (M >= 2 && K >= 2 * N); }
+
 size_t linear_workspace_bytes(int64_t M, int64_t N, int64_t K) {
-    if (M <= 8) return gemv_workspace_bytes(M, N, K);
+    if (M <= 8 && !prefers_tcgen05(M, N, K)) return gemv_workspace_bytes(M, N, K);
     size_t need = umma::fp6_umma_workspace_bytes(M, N, K);
     for (int m = 1; m <= 16; m *= 2) {
         const size_t b = gemv_workspace_bytes(m, N, K);
@@ -683,7 +688,7 @@ int linear(int fmt, const void* x_f16, int64_t x_row_stride, const uint8_t* pack
            int64_t N, int64_t K, void* y_f16, const void* bias_f16, void* workspace, size_t workspace_bytes,
            ao_stream_t stream) {
     if (M < 0 || N < 0) return AO_ERR_SHAPE;
-    if (M <= 8)
+    if (M <= 8 && !prefers_tcgen05(M, N, K))
         return gemv(fmt, x_f16, x_row_stride, packed, scale_f16, M, N, K, y_f16, bias_f16, workspace, workspace_bytes, stream);
     if (workspace == nullptr || workspace_bytes < 256 || !aligned(workspace, 256)) return AO_ERR_WORKSPACE;
     {

@@ -130,7 +130,7 @@ struct Fp6Policy {
 };
 
 static bool fp6_shape_ok(int64_t M, int64_t N, int64_t K) {
-    if (M <= 8 || N < kRows || N % 64 != 0 || K % 128 != 0 || K < 128) return false;
+    if (M < 2 || N < kRows || N % 64 != 0 || K % 128 != 0 || K < 128) return false;
     if (M > (1 << 30) || N > (1 << 30) || K > (1 << 22)) return false;
     return true;
 }
