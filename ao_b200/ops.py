@@ -53,12 +53,16 @@ def unpack_int4pack(packed: Tensor) -> Tensor:
 
 
 def weight_int4pack_mm(x: Tensor, packed: Tensor, group_size: int, scale_and_zero: Tensor, x_cols=None, *,
-                       out: Tensor = None, workspace: Tensor = None) -> Tensor:
+                       out: Tensor = None, workspace: Tensor = None, decode_kernel: bool = False) -> Tensor:
     """y[M][N] = x[M][K] @ dequant(W)^T for a tensor_core_tiled weight; bf16 in, bf16 out.
 
     x may have fewer columns than the (padded) weight: the missing ones count as zero.
     `out` (bf16 [M][N], contiguous) and `workspace` (uint8, zero-filled once, see int4_workspace_bytes) let a
-    caller that replays the call in a CUDA graph keep every buffer it touches fixed."""
+    caller that replays the call in a CUDA graph keep every buffer it touches fixed.
+    `decode_kernel=True` (M <= 16) runs the decode GEMV whatever the batch size, i.e. the kernel the peer-memory
+    exchange path uses (weight_int4pack_mm_gather): its results then match that path bit for bit; by default batches
+    of 5 rows and more (2 and more on long reductions) go to the tcgen05 kernel, whose fp32 sums are taken in another
+    order."""
     _cabi.require_cuda(x, packed, scale_and_zero)
     torch._check(x.dim() == 2 and x.dtype == torch.bfloat16, lambda: "x must be a 2-D bfloat16 tensor")
     torch._check(packed.dim() == 4 and packed.dtype == torch.int32 and packed.shape[2] == 32,
@@ -84,7 +88,10 @@ def weight_int4pack_mm(x: Tensor, packed: Tensor, group_size: int, scale_and_zer
     if M == 0:
         return y
     lib = _cabi.lib()
-    nbytes = lib.ao_int4_tinygemm_linear_workspace_bytes(M, N, K, group_size, ikt)
+    torch._check(not decode_kernel or M <= 16, lambda: f"the decode kernel takes at most 16 rows, got {M}")
+    ws_fn, fn = ((lib.ao_int4_gemv_workspace_bytes, lib.ao_int4_gemv) if decode_kernel else
+                 (lib.ao_int4_tinygemm_linear_workspace_bytes, lib.ao_int4_tinygemm_linear))
+    nbytes = ws_fn(M, N, K, group_size, ikt)
     torch._check(nbytes > 0, lambda: f"unsupported int4 linear shape M={M} N={N} K={K} group={group_size}")
     with torch.cuda.device(x.device):
         if workspace is None:
@@ -93,9 +100,8 @@ def weight_int4pack_mm(x: Tensor, packed: Tensor, group_size: int, scale_and_zer
             torch._check(workspace.dtype == torch.uint8 and workspace.numel() >= nbytes and workspace.device == x.device,
                          lambda: f"workspace must be a uint8 tensor of at least {nbytes} bytes on x's device")
             ws = workspace
-        rc = lib.ao_int4_tinygemm_linear(_cabi.ptr(x), x.stride(0), x.shape[1], _cabi.ptr(packed),
-                                         _cabi.ptr(scale_and_zero), M, N, K, group_size, ikt, _cabi.ptr(y),
-                                         _cabi.ptr(ws), ws.numel(), _stream(x))
+        rc = fn(_cabi.ptr(x), x.stride(0), x.shape[1], _cabi.ptr(packed), _cabi.ptr(scale_and_zero), M, N, K, group_size,
+                ikt, _cabi.ptr(y), _cabi.ptr(ws), ws.numel(), _stream(x))
     _cabi.check(rc, "weight_int4pack_mm")
     return y
 

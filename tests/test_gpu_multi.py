@@ -46,7 +46,7 @@ def _worker(rank, world, port, out_path):
             xs, refs = [], []
             for rep in range(3):                                          # different activations per repetition
                 x = torch.randn(M, K, generator=torch.Generator().manual_seed(10 * it + rep)).bfloat16().to(dev)   # replicated
-                y_local = ops.weight_int4pack_mm(x, packed, g, sz)
+                y_local = ops.weight_int4pack_mm(x, packed, g, sz, decode_kernel=True)   # the kernel the exchange path runs
                 ref = [torch.empty_like(y_local) for _ in range(world)]
                 dist.all_gather(ref, y_local)
                 xs.append(x)
@@ -71,7 +71,7 @@ def _worker(rank, world, port, out_path):
         # (3) plain GEMV into this rank's block, then one exchange kernel that pushes and waits for all layers
         for rep in range(3):
             for packed, sz, site, xs, refs in layers:
-                ops.weight_int4pack_mm(xs[rep], packed, g, sz, out=site.y[rank])
+                ops.weight_int4pack_mm(xs[rep], packed, g, sz, out=site.y[rank], decode_kernel=True)
             ops.gather_exchange(exch, [ly[2] for ly in layers], push=True)
             for packed, sz, site, xs, refs in layers:
                 outs.append((site.y.clone(), refs[rep], f"gemv.. exchange rep {rep} shape {tuple(refs[rep].shape)}"))
