@@ -393,6 +393,8 @@ def run_ours(args):
     device = torch.device("cuda", local_rank)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        # stdout carries the one JSON line: NCCL's own messages (its version banner under NCCL_DEBUG=VERSION) go to stderr
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         import datetime
         dist.init_process_group("nccl", device_id=device, timeout=datetime.timedelta(seconds=90))
     M, g, copies = args.m, args.group, args.copies
