@@ -393,7 +393,10 @@ def run_ours(args):
     device = torch.device("cuda", local_rank)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        # stdout carries the one JSON line: NCCL's own messages (its version banner under NCCL_DEBUG=VERSION) go to stderr
+        # stdout carries the one JSON line: no NCCL version banner on it (NCCL_DEBUG=VERSION prints one to stdout), and
+        # NCCL's other messages go to stderr
+        if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"
         os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         import datetime
         dist.init_process_group("nccl", device_id=device, timeout=datetime.timedelta(seconds=90))
