@@ -326,7 +326,7 @@ extern "C" int ao_gather_exchange(int nsites, void* const* peer_landing, void* c
     gather::Args A = {};
     for (int s = 0; s < nsites; ++s) {
         if (!y_gathered[s] || !state[s]) return AO_ERR_ARG;
-        if (M[s] < 1 || M[s] > 16 || N[s] < 8 || N[s] % 8 != 0) return AO_ERR_SHAPE;
+        if (M[s] < 1 || M[s] > 64 || N[s] < 8 || N[s] % 8 != 0) return AO_ERR_SHAPE;
         if (!aligned(y_gathered[s], 16) || !aligned(state[s], 16)) return AO_ERR_ALIGN;
         for (int r = 0; r < nranks; ++r) {
             void* p = peer_landing[s * nranks + r];

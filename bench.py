@@ -646,7 +646,7 @@ def time_kernel_to_beat(ls, args, barrier):
 # ----------------------------------------------------------------------------------------------
 def run_config5(args, world, rank, device, dist, barrier):
     """Every rank holds rows [r*N/p, (r+1)*N/p) of each 70B layer, quantised on its own device; the outputs are
-    gathered on every rank: by one gather-exchange kernel per step at M <= 8, by an NCCL all-gather per layer above.  Enough copies of the shard rotate that the weights of consecutive steps never sit in L2."""
+    gathered on every rank: by one gather-exchange kernel per step at M <= 64, by an NCCL all-gather per layer above.  Enough copies of the shard rotate that the weights of consecutive steps never sit in L2."""
     g = 128
     packed_mb = sum(N * K // 2 for _, N, K in LAYERS_70B) / 1e6
     out = {"workload": "llama3-70b layer set, int4 weight-only, tensor_core_tiled, group 128, rows sharded over "
@@ -682,7 +682,7 @@ def _config5_one(args, world, rank, device, dist, barrier, shard, copies, g, M):
         def gather(i, y):
             dist.all_gather_into_tensor(gathered[i], y)
 
-        if M <= 8 and args.exchange == "fused":
+        if M <= 64 and args.exchange == "fused":   # (above that the 8-byte words' factor 2 on the wire outweighs the latency saved)
             from ao_b200.comm import PeerExchange
             exchange = PeerExchange(ls.exchange_bytes(world))
             ls.use_exchange(exchange, world)

@@ -215,7 +215,8 @@ int ao_int4_gemv(const void* x_bf16, int64_t x_row_stride, int64_t x_cols, const
  *   when other work follows the GEMV that does not need its completion.)
  * ao_int4_gemv_gather: ao_int4_gemv_push + ao_gather_exchange(push = 0) for one call site.
  *
- * Per call site (one per sharded layer and batch size), the same on every rank:
+ * Per call site (one per sharded layer and batch size; ao_gather_exchange takes 1 <= M <= 64, the GEMV forms M <= 8), the
+ * same on every rank:
  *   peer_landing[r]  rank r's landing area of the site: 2 * nranks * M * N / 2 words of 8 bytes (two buffers, used
  *                    alternately by the parity of the call number), zero before the first call; the entry of `rank`
  *                    is this rank's own area.  ao_gather_exchange takes nsites * nranks pointers, site-major
