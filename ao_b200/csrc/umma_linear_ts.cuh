@@ -7,11 +7,11 @@
 // 128 - the row whose tensor-memory lane it can address (lane = 32 * (warp % 4) + lane id) - turns that row's 128 k of an
 // iteration into 64 registers of 16-bit pairs and stores them with tcgen05.st into 64 columns of its lane: row i in lane
 // i, column c = (k = 2c, 2c + 1), exactly the layout the MMA reads for an operand in tensor memory.
-// Tensor memory (512 columns): accumulators in columns [0, 256) (one of 256 columns, or two of up to 128 for the two
-// issuing threads), four operand slots of 64 columns (one iteration each) in [256, 512).
-// What that buys: no operand ring in shared memory (the activation ring and the raw ring get the room: 8 raw stages in
-// flight per SM), no stmatrix address arithmetic, no proxy fence, per-row scale loads instead of byte permutes; and
-// more operand slots (4) than dequant groups (2 groups of 8 warps: two warps per lane quarter, one per 64-k half), so
+// Tensor memory (512 columns): accumulators first (two of up to 128 columns for the two issuing warps), then operand
+// slots of 64 columns (one iteration each): four in [256, 512), or six in [128, 512) for token tiles of up to 64 columns.
+// What that buys: no operand ring in shared memory (the activation ring and the raw ring get the room: up to 16 raw
+// stages in flight per SM), no stmatrix address arithmetic, no proxy fence, per-row scale loads instead of byte permutes;
+// and more operand slots (4 or 6) than dequant groups (2 groups of 8 warps: two warps per lane quarter, one per 64-k half), so
 // a group never waits for the MMAs that read the slot it has just filled - it goes on with its other slot.
 // MMA issue.  Measured: the tensor pipe runs an MMA for max(N / 2, 45) cycles and a commit for about 50.  The issuing
 // WARP walks its loop converged - waits, descriptors: warp-uniform values - and one elected lane (elect.sync) issues; a
@@ -48,14 +48,20 @@ struct CfgTS {
     static constexpr int XK = MT <= 128 ? 128 : 64;           // k per activation stage
     static constexpr int XBytes = MT * kKB * 2;               // one 64-k activation tile
     static constexpr int XStage = XBytes * (XK / kKB);
-    static constexpr int SX = MT <= 64 ? 8 : 4;               // activation stages (a power of two)
-    static constexpr int SXShift = MT <= 64 ? 3 : 2;
+    static constexpr int SX = 4, SXShift = 2;                 // activation stages (a power of two)
     static constexpr int NG = 2, GW = kDequantWarps / NG;     // dequant groups: (lane quarter, 64-k half) per warp
-    static constexpr int NSLOT = 4;                           // operand slots in tensor memory: iteration it uses it % 4
-    static constexpr int ACol0 = 256, AColsPerIt = kRawK / 2;
+    // Operand slots in tensor memory (unit u uses slot u % NSLOT) behind the accumulators.  A dequant group can run
+    // NSLOT / NG units ahead of the MMAs; with narrow token tiles (short MMAs, but a commit's round trip of ~0.5 us
+    // before a slot is free again) four slots made the groups wait for their slot one unit in two: six there.
+    static constexpr int NSLOT = MT <= 64 ? 6 : 4;
+    static constexpr int ACol0 = MT <= 64 ? 128 : 256, AColsPerIt = kRawK / 2;
+    static_assert(ACol0 + NSLOT * AColsPerIt <= 512, "tensor memory has 512 columns");
     static constexpr int Fixed = 1024 + SX * XStage + 512;
     static constexpr int Rfit = (kSmemLimit - Fixed) / Policy::kRawBytes;
-    static constexpr int R = Rfit > 8 ? 8 : Rfit;
+    // raw stages: as many as fit, up to 16.  With narrow token tiles the kernel streams weights at several TB/s and
+    // the raw ring is what is in flight from HBM: 8 stages (80 KB per SM, 12 MB in all) held it to about 3.3 TB/s.
+    static constexpr int kMaxRaw = 16;
+    static constexpr int R = Rfit > kMaxRaw ? kMaxRaw : Rfit;
     static_assert(GW == 8, "a dequant group has two warps per lane quarter of tensor memory");
     static_assert(NSLOT % NG == 0 && R >= NG, "slots and raw stages per dequant group");
     static_assert(NACC * MT <= ACol0, "the accumulators and the operand slots share the 512 columns");
@@ -74,8 +80,8 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_ts_kernel(const __gri
     const uint32_t x_base = base, raw_base = x_base + SX * C::XStage;
     const uint32_t bar_base = raw_base + R * Policy::kRawBytes;
     const uint32_t full_a = bar_base, a_empty = full_a + 8 * C::NSLOT, full_x = a_empty + 8 * C::NSLOT;
-    const uint32_t x_empty = full_x + 8 * SX, raw_full = x_empty + 8 * SX, raw_empty = raw_full + 8 * 8;
-    const uint32_t acc_full = raw_empty + 8 * 8, tmem_slot = acc_full + 8, flag_slot = tmem_slot + 4;
+    const uint32_t x_empty = full_x + 8 * SX, raw_full = x_empty + 8 * SX, raw_empty = raw_full + 8 * C::kMaxRaw;
+    const uint32_t acc_full = raw_empty + 8 * C::kMaxRaw, tmem_slot = acc_full + 8, flag_slot = tmem_slot + 4;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const Work wk = work_of_cta(p);
     const int n0 = wk.bx * (kRows * RT), m0 = wk.by * MT;
@@ -167,10 +173,10 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_ts_kernel(const __gri
             for (int u = w; u < nunits && ok; u += C::NACC) {
                 // everything this unit reads has to be there
                 const int it = u / RT;
-                const int slot = u & (C::NSLOT - 1);
+                const int slot = u % C::NSLOT;
                 const int xi0 = C::XK == kKB ? 2 * it : it;          // first activation stage of the iteration
                 const int sx0 = xi0 & (SX - 1), sx1 = (xi0 + 1) & (SX - 1);
-                bool got = ptx::mbar_wait_bounded(full_a + 8 * slot, static_cast<uint32_t>(u >> 2) & 1u, kWaitPolls) &&
+                bool got = ptx::mbar_wait_bounded(full_a + 8 * slot, static_cast<uint32_t>(u / C::NSLOT) & 1u, kWaitPolls) &&
                            ptx::mbar_wait_bounded(full_x + 8 * sx0, static_cast<uint32_t>(xi0 >> C::SXShift) & 1u, kWaitPolls) &&
                            (C::XK != kKB ||
                             ptx::mbar_wait_bounded(full_x + 8 * sx1, static_cast<uint32_t>((xi0 + 1) >> C::SXShift) & 1u, kWaitPolls));
@@ -224,9 +230,9 @@ __global__ void __launch_bounds__(kThreads, 1) umma_linear_ts_kernel(const __gri
         const int row = Policy::out_row(q * 32 + lane);
         const uint32_t t_lane_a = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + C::ACol0 + h * (kKB / 2);
         for (int u = grp; u < nunits && ok; u += C::NG) {
-            const int rb = u % R, slot = u & (C::NSLOT - 1);
+            const int rb = u % R, slot = u % C::NSLOT;
             const uint32_t rph = static_cast<uint32_t>(u / R) & 1u;
-            const uint32_t eph = (static_cast<uint32_t>(u >> 2) & 1u) ^ 1u;
+            const uint32_t eph = (static_cast<uint32_t>(u / C::NSLOT) & 1u) ^ 1u;
             if (!ptx::mbar_wait_bounded(raw_full + 8 * rb, rph, kWaitPolls) ||
                 !ptx::mbar_wait_bounded(a_empty + 8 * slot, eph, kWaitPolls)) {
                 ok = false;
