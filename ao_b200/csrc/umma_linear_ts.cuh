@@ -7,11 +7,11 @@
 // 128 - the row whose tensor-memory lane it can address (lane = 32 * (warp % 4) + lane id) - turns that row's 128 k of an
 // iteration into 64 registers of 16-bit pairs and stores them with tcgen05.st into 64 columns of its lane: row i in lane
 // i, column c = (k = 2c, 2c + 1), exactly the layout the MMA reads for an operand in tensor memory.
-// Tensor memory (512 columns): accumulators first (two of up to 128 columns for the two issuing warps), then operand
-// slots of 64 columns (one iteration each): four in [256, 512), or six in [128, 512) for token tiles of up to 64 columns.
+// Tensor memory (512 columns): accumulators in [0, 256) (two of up to 128 columns for the two issuing warps, or one of
+// 256), four operand slots of 64 columns (one iteration each) in [256, 512).
 // What that buys: no operand ring in shared memory (the activation ring and the raw ring get the room: up to 16 raw
 // stages in flight per SM), no stmatrix address arithmetic, no proxy fence, per-row scale loads instead of byte permutes;
-// and more operand slots (4 or 6) than dequant groups (2 groups of 8 warps: two warps per lane quarter, one per 64-k half), so
+// and more operand slots (4) than dequant groups (2 groups of 8 warps: two warps per lane quarter, one per 64-k half), so
 // a group never waits for the MMAs that read the slot it has just filled - it goes on with its other slot.
 // MMA issue.  Measured: the tensor pipe runs an MMA for max(N / 2, 45) cycles and a commit for about 50.  The issuing
 // WARP walks its loop converged - waits, descriptors: warp-uniform values - and one elected lane (elect.sync) issues; a
@@ -50,11 +50,10 @@ struct CfgTS {
     static constexpr int XStage = XBytes * (XK / kKB);
     static constexpr int SX = 4, SXShift = 2;                 // activation stages (a power of two)
     static constexpr int NG = 2, GW = kDequantWarps / NG;     // dequant groups: (lane quarter, 64-k half) per warp
-    // Operand slots in tensor memory (unit u uses slot u % NSLOT) behind the accumulators.  A dequant group can run
-    // NSLOT / NG units ahead of the MMAs; with narrow token tiles (short MMAs, but a commit's round trip of ~0.5 us
-    // before a slot is free again) four slots made the groups wait for their slot one unit in two: six there.
-    static constexpr int NSLOT = MT <= 64 ? 6 : 4;
-    static constexpr int ACol0 = MT <= 64 ? 128 : 256, AColsPerIt = kRawK / 2;
+    // Operand slots in tensor memory (unit u uses slot u % NSLOT) behind the accumulators: a dequant group can run
+    // NSLOT / NG units ahead of the MMAs.  (Six slots for the narrow token tiles were measured: no gain.)
+    static constexpr int NSLOT = 4;
+    static constexpr int ACol0 = 256, AColsPerIt = kRawK / 2;
     static_assert(ACol0 + NSLOT * AColsPerIt <= 512, "tensor memory has 512 columns");
     static constexpr int Fixed = 1024 + SX * XStage + 512;
     static constexpr int Rfit = (kSmemLimit - Fixed) / Policy::kRawBytes;
