@@ -808,15 +808,6 @@ int4_gemv_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int Kx, con
     if (!ok && lane == 0) atomicExch(status, AO_ERR_TIMEOUT);
 }
 
-// AO_B200_NO_PDL=1 turns programmatic dependent launch off (plain stream order)
-inline bool pdl_enabled() {
-    static const bool on = []() {
-        const char* e = getenv("AO_B200_NO_PDL");
-        return !(e && e[0] == '1');
-    }();
-    return on;
-}
-
 template <int IKT, int NB, int MR, int G32>
 int launch_one(const Plan& P, const void* x, long long ldx, int Kx, const void* wq, const void* sz, void* y,
                void* ws, cudaStream_t st) {
@@ -832,7 +823,7 @@ int launch_one(const Plan& P, const void* x, long long ldx, int Kx, const void* 
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     if (cudaLaunchKernelEx(&cfg, kern, static_cast<const __nv_bfloat16*>(x), ldx, Kx, static_cast<const uint8_t*>(wq),

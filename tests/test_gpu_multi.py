@@ -1,7 +1,8 @@
 """Multi-GPU tests of the output exchange over peer memory (ao_int4_gemv_push / ao_gather_exchange): every rank's
 gathered buffer must equal the concatenation of all ranks' single-GPU results, bit for bit, over repeated calls that are
 NOT separated by host barriers: as push + wait per layer, as several GEMV pushes followed by one wait for all of them,
-and as plain GEMVs followed by one exchange kernel that pushes and waits.
+as plain GEMVs followed by one exchange kernel that pushes and waits, and as a 32-row batch (tcgen05 kernel) followed by
+the exchange kernel.
 Runs for every world size in {2, 4, 8} that the box has GPUs for; skipped on a single GPU.
 Ranks are child processes; they leave only after a barrier, with nothing in flight.  NVLS is switched off in NCCL
 (the test's collectives are only the reference all-gather and the handle exchange)."""
@@ -37,7 +38,8 @@ def _worker(rank, world, port, out_path):
         from tests import gpu_util as tu
         g = 64
         shapes = [(1, 1024, 4096), (4, 2048, 4096), (1, 14336 // 2, 4096), (8, 512, 2048)]
-        exch = PeerExchange(sum(ops.gather_slot_bytes(world, M, N) for M, N, K in shapes))
+        big = (32, 1024, 2048)    # a batch of the tcgen05 kernel: exchanged by the exchange kernel alone (mode 3)
+        exch = PeerExchange(sum(ops.gather_slot_bytes(world, M, N) for M, N, K in shapes + [big]))
         layers = []
         for it, (M, N, K) in enumerate(shapes):
             w = tu.make_weight((N, K), seed=100 * rank + it).to(dev)      # every rank has its own rows
@@ -75,6 +77,20 @@ def _worker(rank, world, port, out_path):
             ops.gather_exchange(exch, [ly[2] for ly in layers], push=True)
             for packed, sz, site, xs, refs in layers:
                 outs.append((site.y.clone(), refs[rep], f"gemv.. exchange rep {rep} shape {tuple(refs[rep].shape)}"))
+        # (4) a 32-row batch: the local product by whatever kernel the dispatcher picks, straight into this rank's block,
+        # then the exchange kernel; twice, so that both landing buffers are used
+        M, N, K = big
+        wb = tu.make_weight((N, K), seed=977 + rank).to(dev)
+        packed_b, sz_b = ops.int4_quantize_pack(wb, g, 8)
+        site_b = exch.reserve(M, N)
+        for rep in range(2):
+            xb = torch.randn(M, K, generator=torch.Generator().manual_seed(500 + rep)).bfloat16().to(dev)
+            y_local = ops.weight_int4pack_mm(xb, packed_b, g, sz_b)
+            ref = [torch.empty_like(y_local) for _ in range(world)]
+            dist.all_gather(ref, y_local)
+            ops.weight_int4pack_mm(xb, packed_b, g, sz_b, out=site_b.y[rank])
+            ops.gather_exchange(exch, [site_b], push=True)
+            outs.append((site_b.y.clone(), torch.stack(ref), f"32-row batch + exchange rep {rep}"))
         torch.cuda.synchronize()
         for out, ref, what in outs:
             if not torch.equal(out, ref):
