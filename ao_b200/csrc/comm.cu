@@ -98,7 +98,7 @@ static __device__ unsigned long long g_comm_trace[16];
 constexpr int kMaxSites = 8;
 constexpr int kMaxRanks = 8;
 constexpr int kThreads = 256;
-constexpr int kCtas = 64;
+constexpr int kCtas = 64;   // at least; see the launch
 
 struct Site {
     uint2* peer_landing[kMaxRanks];   // the site's landing area in every rank's buffer: [parity][source rank][M][N/2] words
@@ -345,7 +345,13 @@ extern "C" int ao_gather_exchange(int nsites, void* const* peer_landing, void* c
     A.push = push ? 1 : 0;
     A.status = static_cast<int*>(workspace);
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(gather::kCtas);
+    // CTAs: a thread polls up to eight words per round, and a round costs one memory latency, so as many CTAs as give
+    // every word a thread in the first round, between kCtas and one per SM
+    long long wait_words = 0;
+    for (int s = 0; s < nsites; ++s) wait_words += (long long)(nranks - 1) * M[s] * (N[s] / 2);
+    long long ctas = (wait_words + gather::kThreads * 8 - 1) / (gather::kThreads * 8);
+    ctas = ctas < gather::kCtas ? gather::kCtas : (ctas > kNumSMs ? kNumSMs : ctas);
+    cfg.gridDim = dim3((unsigned)ctas);
     cfg.blockDim = dim3(gather::kThreads);
     cfg.stream = as_stream(stream);
     cudaLaunchAttribute attr[1];

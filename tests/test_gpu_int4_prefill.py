@@ -83,6 +83,23 @@ def test_prefill_two_row_tiles_per_block(M, N, K, g):
     assert _cabi.workspace_status("cuda") == 0
 
 
+@pytest.mark.parametrize("g", [32, 64, 128])
+@pytest.mark.parametrize("K", [128, 384])
+def test_prefill_single_and_odd_iteration_counts(K, g):
+    """K = 128 is one iteration of the tcgen05 kernels (only one of the two issuing warps has work, only one accumulator
+    is written), K = 384 an odd number of them."""
+    from ao_b200 import _cabi, ops
+    N = 384
+    packed, sz, wd = _quantized(N, K, g, seed=K + g)
+    gen = torch.Generator().manual_seed(K)
+    for M in (5, 17, 64, 100, 200, 600):
+        x = torch.randn(M, K, generator=gen).bfloat16()
+        y = ops.weight_int4pack_mm(x.cuda(), packed, g, sz)
+        _check(y, np.ascontiguousarray(x.float().numpy()) @ wd.T, f"M={M}")
+        assert torch.equal(y, ops.weight_int4pack_mm(x.cuda(), packed, g, sz)), "two runs must give identical bits"
+    assert _cabi.workspace_status("cuda") == 0
+
+
 def test_prefill_matches_decode_kernel_rows():
     """The same activation rows through the decode kernel (16 at a time) and through the prefill kernel."""
     from ao_b200 import ops
