@@ -178,7 +178,7 @@ inline bool make_plan(int64_t M, int64_t N, int64_t K, Plan* P, bool operand_in_
     }
     if (operand_in_tmem && P->MT == 256 && P->TT == 1) P->MT = 128;
     P->m_tiles = (int)((M + P->MT * P->TT - 1) / (P->MT * P->TT));
-    if ((long long)P->row_tiles * P->m_tiles > kMaxTiles) return false;
+    if ((long long)P->row_tiles * P->m_tiles > (1ll << 30)) return false;   // (the grid is one-dimensional)
     const int nit = (int)(K / kRawK);
     // two row tiles per CTA against one activation stage, when the pairs still fill every SM: 128-column tiles on many
     // row tiles are otherwise bound by re-reading the activation tile from L2
@@ -200,7 +200,7 @@ inline bool make_plan(int64_t M, int64_t N, int64_t K, Plan* P, bool operand_in_
         double best = (double)((tiles + kNumSMs - 1) / kNumSMs) * (nit + fixed1);
         for (int full = 0; full <= whole; full += (whole > 0 ? whole : 1)) {
             const int rem = tiles - full;
-            if (rem == 0) continue;
+            if (rem == 0 || rem > kMaxTiles) continue;   // (one completion counter per tile that has slabs)
             for (int sp = 2; sp <= smax && nit / sp >= 8; ++sp) {
                 const double cost = (double)(full / kNumSMs) * (nit + fixed1) +
                                     (double)((rem * sp + kNumSMs - 1) / kNumSMs) * ((double)nit / sp + fixed_s);

@@ -81,3 +81,17 @@ def test_reciprocal_multiply_matches_division_for_bf16_operands():
             exact = rbf16(r / s)
             fast = rbf16(r * (np.float32(1.0) / s))
             assert np.array_equal(exact, fast), (er, es)
+
+
+def test_linear_plans_exist_for_a_sweep_of_shapes():
+    """The workspace queries run the same host-side planning as the launches (tile sizes, K slabs over waves of CTAs):
+    every supported shape of a sweep over batch sizes, rows and reductions gets a plan with a sane workspace size."""
+    lib = _cabi.lib()
+    for M in (1, 2, 4, 5, 8, 9, 16, 17, 32, 33, 64, 65, 128, 129, 200, 256, 257, 300, 512, 1000, 1024, 1536, 1700, 4096, 20000):
+        for N in (128, 256, 384, 1024, 4096, 4736, 6144, 10240, 28672, 57344):
+            for K in (128, 256, 384, 2048, 4096, 8192, 14336, 28672):
+                for g in (32, 128):
+                    nbytes = lib.ao_int4_tinygemm_linear_workspace_bytes(M, N, K, g, 8)
+                    assert 0 < nbytes < (1 << 32), (M, N, K, g, nbytes)
+                assert 0 < lib.ao_hqq_int4_linear_workspace_bytes(M, N, K, 64) < (1 << 32), (M, N, K)
+                assert 0 < lib.ao_fp6_linear_workspace_bytes(M, N, K) < (1 << 32), (M, N, K)
