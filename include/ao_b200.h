@@ -162,8 +162,10 @@ int ao_from_scaled_tc_fp6(const uint8_t* packed, int64_t M, int64_t N, const voi
  * stands in for the reference's per-call zero padding of the activation to the padded K,
  * affine_quantized_tensor.py:625-627), packed int32 tensor_core_tiled (inner_k_tiles 8/4/2),
  * scale_and_zero bf16 [K/group][N][2] -> y bf16 [M][N] contiguous.
- * M <= 8 runs the HBM-bound GEMV kernel; larger M the tcgen05 kernel (inner_k_tiles 8, N >= 128, 16-byte
- * aligned activation rows), anything else is processed in row blocks of 16 by the GEMV kernel.
+ * A single row and the smallest batches run the HBM-bound GEMV kernel; M >= 5 (M >= 2 when K >= 2 N) the tcgen05
+ * kernels (inner_k_tiles 8, N >= 128, 16-byte aligned activation rows), anything else is processed in row blocks of 16
+ * by the GEMV kernel.  The two kernels add their fp32 sums in different orders: results agree within the tolerance of
+ * the operator, not bit for bit; ao_int4_gemv is the GEMV alone.
  *
  * Workspace: ao_int4_tinygemm_linear_workspace_bytes(...) bytes, 256-byte aligned.  It holds a
  * status word (int at offset 0: AO_OK, or the code of a device-side failure such as a copy
